@@ -1,0 +1,186 @@
+/*
+ * libmdb200 -- C ABI of the B200 (sm_100a) block-diffusion decode kernels.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * (cudaStream_t passed as void*); nothing here names a torch type.  All
+ * buffers are owned by the caller.  Calls are asynchronous on `stream`, do
+ * not allocate and do not synchronise unless stated.  The return value is
+ * MDB_OK or a negative MDB_ERR_* detected on the host before any launch.
+ * Conditions only the device can see (a cache slot outside the pool, a
+ * bounded wait that ran out) set a bit in a device status word instead of
+ * trapping; read it with mdb_last_device_status().
+ *
+ * Paths in the comments are relative to the reference project root; NV/
+ * abbreviates engines/nano_dvlm/nanovllm/.  bf16 means __nv_bfloat16.
+ */
+#ifndef MDB200_H
+#define MDB200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* mdb_stream_t; /* cudaStream_t */
+
+enum {
+  MDB_OK = 0,
+  MDB_ERR_ARG = -1,         /* null pointer, non-positive size, inconsistent dims */
+  MDB_ERR_ALIGN = -2,       /* pointer or stride not 16-byte aligned */
+  MDB_ERR_UNSUPPORTED = -3, /* shape outside what the kernels are built for */
+  MDB_ERR_CUDA = -4,        /* the launch itself was refused by the runtime */
+  MDB_ERR_WORKSPACE = -5    /* workspace smaller than *_workspace_bytes() */
+};
+
+/* bits of the device status word */
+enum {
+  MDB_STATUS_BAD_SLOT = 1u,     /* slot_mapping entry outside [0, num_slots) and not -1: row skipped */
+  MDB_STATUS_BAD_PAGE = 2u,     /* page-table entry outside [0, num_pages): keys treated as absent */
+  MDB_STATUS_BAD_TOKEN = 4u,    /* token id outside the embedding table: row zeroed */
+  MDB_STATUS_BAD_POSITION = 8u, /* position outside the rotary table: row left unrotated */
+  MDB_STATUS_WAIT_TIMEOUT = 16u /* a bounded wait on a peer flag or barrier expired */
+};
+
+const char* mdb_strerror(int code);
+int mdb_version(void);
+
+/* Copies the status word of the current device to *out (host memory) after
+ * synchronising the device; clear != 0 resets it.  Plays the part of the
+ * reference's host asserts (NV/layers/attention.py:36-39). */
+int mdb_last_device_status(unsigned int* out, int clear);
+
+/* ---- paged KV write/commit --------------------------------------------- */
+
+/* Replaces store_kvcache / store_kvcache_kernel (NV/layers/attention.py:10-40).
+ * Row i of key/value (row_elems = Hkv*D bf16, row strides in elements) is
+ * copied to k_cache/v_cache row slot_mapping[i]; slot -1 skips the row. */
+int mdb_kv_commit(const void* key, int64_t key_stride, const void* value, int64_t value_stride, void* k_cache,
+                  void* v_cache, const int32_t* slot_mapping, int n_tokens, int row_elems, int64_t num_slots,
+                  mdb_stream_t stream);
+
+/* ---- block attention over the paged cache (decode / denoise step) -------- */
+
+/* Replaces flash_attn_with_kvcache(q, k_cache, v_cache, cache_seqlens,
+ * block_table, softmax_scale, causal=False) as called at
+ * NV/layers/sdar_attention.py:50-55.  q/out: [bs, block, hq, 128] bf16;
+ * caches: [num_pages, 256, hkv, 128] bf16; block_table: [bs, table_stride]
+ * int32 (-1 padded); ctx_lens: [bs] int32, 0 makes the request a no-op (its
+ * output rows are zeroed).  Every query row sees keys [0, ctx).  The key range
+ * of each request is cut into nsplit parts processed by different CTAs;
+ * nsplit > 1 needs the workspace. */
+int64_t mdb_attn_paged_workspace_bytes(int bs, int block, int hq, int nsplit);
+int mdb_attn_block_paged(const void* q, const void* k_cache, const void* v_cache, void* out,
+                         const int32_t* block_table, int table_stride, const int32_t* ctx_lens, int bs, int block,
+                         int hq, int hkv, int num_pages, float softmax_scale, int nsplit, void* workspace,
+                         int64_t workspace_bytes, mdb_stream_t stream);
+
+/* ---- staircase (block-causal, right-aligned) prefill attention ----------- */
+
+/* Replaces sparse_attn_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k,
+ * staircase_size) (NV/kernels/triton/attention/block_prefill_attention_v2.py:
+ * 17-202, call site NV/layers/sdar_attention.py:39-47).  Packed sequences:
+ * q/out rows of hq*128, k/v rows of hkv*128, row strides in elements;
+ * cu_seqlens: [nseq+1] int32 (queries and keys share it: self-attention).
+ * Query i of a T-token sequence sees keys j <= ((i+pad)/S+1)*S-1-pad with
+ * pad = ceil(T/S)*S - T.  stairs must be a power of two in [1,128]. */
+int mdb_attn_staircase_varlen(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
+                              int64_t v_stride, void* out, int64_t out_stride, const int32_t* cu_seqlens, int nseq,
+                              int max_seqlen, int hq, int hkv, int stairs, mdb_stream_t stream);
+
+/* ---- linear layers -------------------------------------------------------- */
+
+/* y[m,n] = x[m,k] * w[n,k]^T, bf16 in, fp32 accumulate, bf16 out: F.linear as
+ * used by NV/layers/linear.py:72-73,153-154 and NV/layers/embed_head.py:67. */
+int mdb_gemm_bf16(const void* x, int64_t ldx, const void* w, void* y, int64_t ldy, int m, int n, int k,
+                  mdb_stream_t stream);
+
+/* Same product for m <= 64 as a weight-streaming kernel that cuts k into
+ * ksplit slices and writes fp32 partial sums partials[ksplit][m][n]; the
+ * consumers below add the slices in index order, round to bf16 where F.linear
+ * would, and apply the layer that follows. */
+int64_t mdb_gemm_splitk_workspace_bytes(int m, int n, int ksplit);
+int mdb_gemm_splitk_partials(const void* x, int64_t ldx, const void* w, float* partials, int m, int n, int k,
+                             int ksplit, mdb_stream_t stream);
+
+/* gate_up projection fused with SiLU*mul (NV/models/sdar.py:109-111,
+ * NV/layers/activation.py:12-15) for m <= 64: w is [2*inter, k] with gate rows
+ * first; act[m, inter] = bf16(silu_fp32(bf16(gate))) * bf16(up). */
+int mdb_gemm_gateup_swiglu(const void* x, int64_t ldx, const void* w_gate_up, void* act, int64_t ld_act, int m,
+                           int inter, int k, mdb_stream_t stream);
+
+/* SiLU*mul on a materialised [m, 2*inter] bf16 matrix (large-m path). */
+int mdb_silu_mul(const void* gate_up, int64_t ld_in, void* act, int64_t ld_act, int m, int inter,
+                 mdb_stream_t stream);
+
+/* ---- fused reductions / element-wise layers -------------------------------- */
+
+/* RMSNorm with fused residual add (NV/layers/layernorm.py:16-40).  The input
+ * row is either x (bf16 [m,h]) or, when partials != NULL, the bf16-rounded
+ * sum of nparts fp32 slices [nparts][m][h].  residual_in == NULL selects the
+ * no-residual form (residual_out, if given, receives the input row). */
+int mdb_add_rmsnorm(const void* x, const float* partials, int nparts, const void* residual_in, const void* weight,
+                    float eps, void* y_out, void* residual_out, int m, int h, mdb_stream_t stream);
+
+/* What follows qkv_proj in SDARAttention.forward (NV/models/sdar.py:73-82):
+ * split q|k|v, per-head RMSNorm of q and k, NeoX rotary embedding from the
+ * fp32 cos|sin table (NV/layers/rotary_embedding.py:6-48), then the KV store
+ * of Attention.forward (NV/layers/sdar_attention.py:37-38).  Input row is
+ * qkv (bf16 [m, (hq+2hkv)*128], row stride ld_qkv) or fp32 partials as above.
+ * q_out [m, hq*128]; k_out/v_out [m, hkv*128] optional (prefill needs them
+ * contiguous); slot_mapping optional (NULL: no cache write). */
+int mdb_qknorm_rope_commit(const void* qkv, int64_t ld_qkv, const float* partials, int nparts,
+                           const int64_t* positions, const float* rope_table, int max_pos, const void* q_norm_w,
+                           const void* k_norm_w, float eps, const int32_t* slot_mapping, void* q_out, void* k_out,
+                           void* v_out, void* k_cache, void* v_cache, int64_t num_slots, int m, int hq, int hkv,
+                           mdb_stream_t stream);
+
+/* Row gather: out[i,:] = table[ids[i],:] (F.embedding at
+ * NV/layers/embed_head.py:38; also the last-block row pick of the LM head at
+ * NV/layers/embed_head.py:63-66). */
+int mdb_gather_rows(const void* table, int64_t num_rows, const int64_t* ids, void* out, int m, int h,
+                    mdb_stream_t stream);
+
+/* ---- LM head + sampler ------------------------------------------------------ */
+
+/* Replaces ParallelLMHead.forward + Sampler.prepare (NV/layers/embed_head.py:
+ * 61-72, NV/layers/sampler.py:11-22) without materialising logits: for each of
+ * the m rows, logit_v = bf16(hidden . w[v]) / T, x0 = argmax_v(logit_v +
+ * noise_v) (lowest index wins a tie), conf = softmax(logit)[x0].
+ * temperatures: [m / block] fp32, one per request.  noise_mode 0: none,
+ * 1: `noise` points to fp32 [m, vocab] Gumbel values, 2: counter-based Gumbel
+ * noise from (seed, step, row, column) -- mdb_gumbel_noise() writes out the
+ * same values.  step_dev, if not NULL, points to a uint32 in device memory
+ * that is added to `step` when the kernel runs, so a captured graph can be
+ * replayed with fresh noise.  m <= 64 streams the weight once; larger m goes
+ * through bf16 logits in the workspace. */
+int64_t mdb_lmhead_workspace_bytes(int m, int vocab);
+int mdb_lmhead_sample(const void* hidden, int64_t ld_hidden, const void* w, int m, int vocab, int h,
+                      const float* temperatures, int block, int noise_mode, const float* noise, uint32_t seed,
+                      uint32_t step, const uint32_t* step_dev, void* workspace, int64_t workspace_bytes,
+                      int32_t* x0_out, float* conf_out, mdb_stream_t stream);
+
+/* Same scan over already materialised bf16 logits [m, vocab] (row stride ld);
+ * a workspace of mdb_lmhead_workspace_bytes(m, vocab) always suffices. */
+int mdb_logits_sample(const void* logits, int64_t ld, int m, int vocab, const float* temperatures, int block,
+                      int noise_mode, const float* noise, uint32_t seed, uint32_t step, const uint32_t* step_dev,
+                      void* workspace, int64_t workspace_bytes, int32_t* x0_out, float* conf_out,
+                      mdb_stream_t stream);
+
+int mdb_gumbel_noise(float* out, int m, int vocab, uint32_t seed, uint32_t step, mdb_stream_t stream);
+
+/* The unmask rule of Sampler.forward (NV/layers/sampler.py:28-54) on device:
+ * per request, masked positions whose confidence is > threshold are replaced
+ * by x0; if fewer than `quota` qualify the `quota` most confident masked
+ * positions are taken instead (quota = 1 is the nano engine's rule, the HF
+ * twin's quota is mineru_diffusion/modeling_mineru_diffusion.py:518-532).
+ * block_ids [bs, block] int64 is updated in place; transfer_out [bs, block]
+ * uint8; count_out [bs] int32 = positions unmasked. Requests with no masked
+ * position are left untouched. */
+int mdb_unmask_decide(int64_t* block_ids, const int32_t* x0, const float* conf, int bs, int block, int64_t mask_id,
+                      float threshold, int quota, uint8_t* transfer_out, int32_t* count_out, mdb_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MDB200_H */

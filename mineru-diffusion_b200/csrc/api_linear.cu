@@ -1,0 +1,138 @@
+// C entry points of the linear layers and the LM-head sampler; picks the
+// weight-streaming kernel for short steps and the tiled kernel otherwise.
+#include "mdb_common.cuh"
+
+using namespace mdb;
+
+namespace {
+
+int64_t align256(int64_t v) { return (v + 255) / 256 * 256; }
+
+struct LmHeadLayout {
+  int64_t nparts, off_i, off_logits, total;
+};
+
+LmHeadLayout lmhead_layout(int m, int vocab) {
+  LmHeadLayout l;
+  const bool streaming = m <= 64;
+  l.nparts = streaming ? vocab / 32 : (vocab + kScanCols - 1) / kScanCols;
+  l.off_i = align256(l.nparts * m * 16);
+  l.off_logits = l.off_i + align256(l.nparts * m * 4);
+  l.total = l.off_logits + (streaming ? 0 : align256(static_cast<int64_t>(m) * vocab * 2));
+  return l;
+}
+
+int finalize_sampler(const float4* part_f, const int* part_i, int nparts, int m, int32_t* x0_out, float* conf_out,
+                     cudaStream_t st) {
+  const int threads = 128;
+  const int blocks = (m * 32 + threads - 1) / threads;
+  sampler_finalize_kernel<<<blocks, threads, 0, st>>>(part_f, part_i, nparts, m, x0_out, conf_out);
+  return mdb_check_launch();
+}
+
+int scan_logits(const bf16* logits, int64_t ld, int m, int vocab, const float* temperatures, int block, int noise_mode,
+                const float* noise, uint32_t seed, uint32_t step, const uint32_t* step_dev, unsigned char* ws,
+                int32_t* x0_out, float* conf_out, cudaStream_t st) {
+  const int nparts = (vocab + kScanCols - 1) / kScanCols;
+  float4* part_f = reinterpret_cast<float4*>(ws);
+  int* part_i = reinterpret_cast<int*>(ws + align256(static_cast<int64_t>(nparts) * m * 16));
+  dim3 grid(nparts, m);
+  logits_scan_kernel<<<grid, 256, 0, st>>>(logits, ld, m, vocab, temperatures, block, noise_mode, noise, seed, step,
+                                           step_dev, part_f, part_i);
+  int rc = mdb_check_launch();
+  if (rc != MDB_OK) return rc;
+  return finalize_sampler(part_f, part_i, nparts, m, x0_out, conf_out, st);
+}
+
+}  // namespace
+
+extern "C" {
+
+int mdb_gemm_bf16(const void* x, int64_t ldx, const void* w, void* y, int64_t ldy, int m, int n, int k,
+                  mdb_stream_t stream) {
+  MDB_REQUIRE(m >= 0 && n > 0 && k > 0, MDB_ERR_ARG);
+  if (m == 0) return MDB_OK;
+  MDB_REQUIRE(x && w && y && ldx >= k && ldy >= n, MDB_ERR_ARG);
+  MDB_REQUIRE(ldx % 8 == 0 && ldy % 2 == 0 && mdb_aligned16(x) && mdb_aligned16(w) && mdb_aligned16(y),
+              MDB_ERR_ALIGN);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (m <= 64 && n % 32 == 0 && k % 32 == 0) {
+    SkinnyArgs a = {};
+    a.x = static_cast<const bf16*>(x);
+    a.w = static_cast<const bf16*>(w);
+    a.ldx = ldx;
+    a.m = m; a.n = n; a.k = k;
+    a.y = static_cast<bf16*>(y);
+    a.ldy = ldy;
+    return launch_skinny<kEpiBf16>(a, 1, st);
+  }
+  MDB_REQUIRE(k % kGemmBK == 0 && n % 2 == 0, MDB_ERR_UNSUPPORTED);
+  return launch_gemm_tiled(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), static_cast<bf16*>(y), ldy,
+                           m, n, k, st);
+}
+
+int64_t mdb_lmhead_workspace_bytes(int m, int vocab) {
+  if (m <= 0 || vocab <= 0) return 0;
+  return lmhead_layout(m, vocab).total;
+}
+
+int mdb_lmhead_sample(const void* hidden, int64_t ld_hidden, const void* w, int m, int vocab, int h,
+                      const float* temperatures, int block, int noise_mode, const float* noise, uint32_t seed,
+                      uint32_t step, const uint32_t* step_dev, void* workspace, int64_t workspace_bytes,
+                      int32_t* x0_out, float* conf_out, mdb_stream_t stream) {
+  MDB_REQUIRE(m >= 0 && vocab > 0 && h > 0 && block > 0, MDB_ERR_ARG);
+  if (m == 0) return MDB_OK;
+  MDB_REQUIRE(hidden && w && temperatures && x0_out && conf_out && workspace, MDB_ERR_ARG);
+  MDB_REQUIRE(m % block == 0 && ld_hidden >= h, MDB_ERR_ARG);
+  MDB_REQUIRE(noise_mode >= 0 && noise_mode <= 2 && (noise_mode != 1 || noise != nullptr), MDB_ERR_ARG);
+  MDB_REQUIRE(ld_hidden % 8 == 0 && mdb_aligned16(hidden) && mdb_aligned16(w) && mdb_aligned16(workspace),
+              MDB_ERR_ALIGN);
+  const LmHeadLayout lay = lmhead_layout(m, vocab);
+  MDB_REQUIRE(workspace_bytes >= lay.total, MDB_ERR_WORKSPACE);
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (m <= 64) {
+    MDB_REQUIRE(vocab % 32 == 0 && h % 32 == 0, MDB_ERR_UNSUPPORTED);
+    SkinnyArgs a = {};
+    a.x = static_cast<const bf16*>(hidden);
+    a.w = static_cast<const bf16*>(w);
+    a.ldx = ld_hidden;
+    a.m = m; a.n = vocab; a.k = h;
+    a.temperatures = temperatures;
+    a.block = block;
+    a.noise_mode = noise_mode;
+    a.noise = noise;
+    a.seed = seed; a.step = step;
+    a.step_dev = step_dev;
+    a.part_f = reinterpret_cast<float4*>(ws);
+    a.part_i = reinterpret_cast<int*>(ws + lay.off_i);
+    int rc = launch_skinny<kEpiLmHead>(a, 1, st);
+    if (rc != MDB_OK) return rc;
+    return finalize_sampler(a.part_f, a.part_i, static_cast<int>(lay.nparts), m, x0_out, conf_out, st);
+  }
+  MDB_REQUIRE(h % kGemmBK == 0 && vocab % 2 == 0, MDB_ERR_UNSUPPORTED);
+  bf16* logits = reinterpret_cast<bf16*>(ws + lay.off_logits);
+  int rc = launch_gemm_tiled(static_cast<const bf16*>(hidden), ld_hidden, static_cast<const bf16*>(w), logits, vocab, m,
+                             vocab, h, st);
+  if (rc != MDB_OK) return rc;
+  return scan_logits(logits, vocab, m, vocab, temperatures, block, noise_mode, noise, seed, step, step_dev, ws, x0_out,
+                     conf_out, st);
+}
+
+int mdb_logits_sample(const void* logits, int64_t ld, int m, int vocab, const float* temperatures, int block,
+                      int noise_mode, const float* noise, uint32_t seed, uint32_t step, const uint32_t* step_dev,
+                      void* workspace, int64_t workspace_bytes, int32_t* x0_out, float* conf_out,
+                      mdb_stream_t stream) {
+  MDB_REQUIRE(m >= 0 && vocab > 0 && block > 0, MDB_ERR_ARG);
+  if (m == 0) return MDB_OK;
+  MDB_REQUIRE(logits && temperatures && x0_out && conf_out && workspace, MDB_ERR_ARG);
+  MDB_REQUIRE(m % block == 0 && ld >= vocab, MDB_ERR_ARG);
+  MDB_REQUIRE(noise_mode >= 0 && noise_mode <= 2 && (noise_mode != 1 || noise != nullptr), MDB_ERR_ARG);
+  MDB_REQUIRE(mdb_aligned16(workspace), MDB_ERR_ALIGN);
+  const int64_t nparts = (vocab + kScanCols - 1) / kScanCols;
+  MDB_REQUIRE(workspace_bytes >= align256(nparts * m * 16) + align256(nparts * m * 4), MDB_ERR_WORKSPACE);
+  return scan_logits(static_cast<const bf16*>(logits), ld, m, vocab, temperatures, block, noise_mode, noise, seed, step,
+                     step_dev, static_cast<unsigned char*>(workspace), x0_out, conf_out, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

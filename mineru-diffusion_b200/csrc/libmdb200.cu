@@ -1,0 +1,8 @@
+// Single translation unit of libmdb200.so: the kernels share one device status
+// word and a few launch helpers, so the parts are included here in order
+// rather than linked as relocatable device code.
+#include "elementwise.cu"
+#include "attention.cu"
+#include "gemm_skinny.cu"
+#include "gemm_tiled.cu"
+#include "api_linear.cu"

@@ -1,0 +1,140 @@
+// Shared device/host helpers for the block-diffusion decode kernels (sm_100a).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/mdb200.h"
+
+namespace mdb {
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int kHeadDim = 128;   // the only head size the SDAR decoder uses
+constexpr int kPage = 256;      // tokens per KV page
+
+// ---- device status word --------------------------------------------------
+// Kernels never trap.  A soft check that fails (slot out of range, bounded
+// wait expired) ORs a bit into this word and skips the access; the host reads
+// it with mdb_last_device_status().
+__device__ unsigned int g_device_status = 0;  // one definition: the library is a single translation unit
+
+__device__ __forceinline__ void report_status(unsigned int bit) { atomicOr(&g_device_status, bit); }
+
+// ---- small numeric helpers ------------------------------------------------
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
+  __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&u);
+  return __bfloat1622float2(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// ---- memory access helpers -------------------------------------------------
+// 16-byte streaming load that bypasses L1 allocation (weights are read once).
+__device__ __forceinline__ uint4 ldg_stream16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// 16-byte read-only load that may stay in L1 (activations re-read by many warps).
+__device__ __forceinline__ uint4 ldg_cached16(const void* p) {
+  return __ldg(reinterpret_cast<const uint4*>(p));
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// cp.async 16 bytes; src_bytes < 16 zero-fills the rest (0 = pure zero fill).
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3,
+                                                  uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+
+// D(16x8, fp32) += A(16x16, bf16 row) * B(16x8, bf16 col)
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Tile rows of 128 bytes (64 bf16) or 256 bytes (128 bf16) are stored with
+// their 16-byte chunks XOR-ed by the row index so that the 8 row addresses of
+// one ldmatrix phase fall in 8 distinct bank groups.
+__device__ __forceinline__ int swz_chunk(int row, int chunk) { return chunk ^ (row & 7); }
+
+// ---- counter-based Gumbel noise ---------------------------------------------
+// One value per (seed, step, row, column); the LM-head scan and the noise dump
+// entry point call the same function so a test can hand the exact noise to a
+// CPU checker.
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {
+  x ^= x >> 16; x *= 0x7feb352du;
+  x ^= x >> 15; x *= 0x846ca68bu;
+  x ^= x >> 16;
+  return x;
+}
+
+__device__ __forceinline__ float gumbel_noise(uint32_t seed, uint32_t step, uint32_t row, uint32_t col) {
+  uint32_t h = mix32(seed ^ 0x9e3779b9u);
+  h = mix32(h ^ (step * 0x85ebca6bu + 0xc2b2ae35u));
+  h = mix32(h ^ (row * 0x27d4eb2fu + 0x165667b1u));
+  h = mix32(h ^ col);
+  // uniform in (0,1): 24 random bits, centred
+  float u = (static_cast<float>(h >> 8) + 0.5f) * (1.0f / 16777216.0f);
+  float e = -__logf(u);          // Exp(1)
+  return -__logf(e);             // Gumbel(0,1), as -log(Exp(1)) in the reference sampler
+}
+
+}  // namespace mdb
+
+// ---- host-side argument checks ----------------------------------------------
+#define MDB_REQUIRE(cond, code) \
+  do {                          \
+    if (!(cond)) return (code); \
+  } while (0)
+
+static inline bool mdb_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static inline int mdb_check_launch() {
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? MDB_OK : MDB_ERR_CUDA;
+}

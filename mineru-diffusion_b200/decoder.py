@@ -1,0 +1,253 @@
+"""The SDAR decoder stack as a launch sequence over libmdb200.
+
+``DecoderEngine.forward`` is what ``SDARModel.forward`` is in the reference
+(nanovllm/models/sdar.py:167-181): token rows in, final-norm hidden rows out,
+K/V of the step written into the paged cache on the way.  Per layer it issues
+
+    add+RMSNorm -> qkv GEMM -> q/k norm + RoPE + KV store -> attention
+    -> o GEMM -> add+RMSNorm -> gate_up GEMM (+SiLU*mul) -> down GEMM
+
+For steps of at most 64 rows the GEMMs are the weight-streaming kernels: they
+leave fp32 split-k slices that the *next* kernel sums, rounds to bf16 and
+consumes, so no stand-alone reduction or activation pass exists.  Longer
+steps (prefill, big decode batches) use the tiled GEMM with bf16 outputs.
+All buffers are allocated once here; a step allocates nothing, which is what
+lets the decode step be captured in a CUDA graph.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import ops
+from .engine.config import DecoderConfig
+from .engine.context import Context
+
+PAGE = 256
+SKINNY_MAX_ROWS = 64
+
+
+@dataclass
+class LayerWeights:
+    input_ln: torch.Tensor
+    qkv: torch.Tensor       # [(Hq+2Hkv)*D, H] rows q|k|v, as QKVParallelLinear stores them
+    q_norm: torch.Tensor
+    k_norm: torch.Tensor
+    o: torch.Tensor         # [H, Hq*D]
+    post_ln: torch.Tensor
+    gate_up: torch.Tensor   # [2I, H] rows gate|up, as MergedColumnParallelLinear stores them
+    down: torch.Tensor      # [H, I]
+
+
+@dataclass
+class DecoderWeights:
+    embed: torch.Tensor
+    layers: list[LayerWeights]
+    final_ln: torch.Tensor
+    lm_head: torch.Tensor
+
+    @classmethod
+    def random_init(cls, cfg: DecoderConfig, seed: int, device, std: float = 0.02) -> "DecoderWeights":
+        """Seeded N(0, std) matrices generated on ``device`` (RMSNorm weights 1)."""
+        g = torch.Generator(device=device).manual_seed(seed)
+        bf = torch.bfloat16
+
+        def mat(r, c):
+            return (torch.randn(r, c, generator=g, device=device, dtype=torch.float32) * std).to(bf)
+
+        def ones(n):
+            return torch.ones(n, dtype=bf, device=device)
+
+        h, i, d = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
+        hq, hkv = cfg.num_attention_heads, cfg.num_key_value_heads
+        embed = mat(cfg.vocab_size, h)
+        layers = [LayerWeights(ones(h), mat((hq + 2 * hkv) * d, h), ones(d), ones(d), mat(h, hq * d), ones(h),
+                               mat(2 * i, h), mat(h, i)) for _ in range(cfg.num_hidden_layers)]
+        lm_head = embed if cfg.tie_word_embeddings else mat(cfg.vocab_size, h)
+        return cls(embed, layers, ones(h), lm_head)
+
+    @classmethod
+    def from_reference_layout(cls, src, device) -> "DecoderWeights":
+        """Copy a weight set held in the reference's tensor layout (any object
+        with the same attribute names, tensors on any device) to ``device``."""
+        def mv(t):
+            return t.detach().to(device=device, dtype=torch.bfloat16).contiguous()
+        layers = [LayerWeights(mv(l.input_ln), mv(l.qkv), mv(l.q_norm), mv(l.k_norm), mv(l.o), mv(l.post_ln),
+                               mv(l.gate_up), mv(l.down)) for l in src.layers]
+        return cls(mv(src.embed), layers, mv(src.final_ln), mv(src.lm_head))
+
+    def nbytes(self) -> int:
+        n = self.embed.numel() + self.final_ln.numel()
+        if self.lm_head.data_ptr() != self.embed.data_ptr():
+            n += self.lm_head.numel()
+        for l in self.layers:
+            n += sum(t.numel() for t in (l.input_ln, l.qkv, l.q_norm, l.k_norm, l.o, l.post_ln, l.gate_up, l.down))
+        return 2 * n
+
+
+def rope_table(max_pos: int, head_dim: int, base: float, device) -> torch.Tensor:
+    """fp32 [max_pos, head_dim] cos|sin table built the way the reference builds
+    its ``cos_sin_cache`` (nanovllm/layers/rotary_embedding.py:19-35)."""
+    inv_freq = 1.0 / (base ** (torch.arange(0, head_dim, 2, dtype=torch.float) / head_dim))
+    t = torch.arange(max_pos, dtype=torch.float)
+    freqs = torch.einsum("i,j -> ij", t, inv_freq)
+    return torch.cat((freqs.cos(), freqs.sin()), dim=-1).contiguous().to(device)
+
+
+def pick_ksplit(n: int, k: int, rows: int) -> int:
+    """Split-k factor of a weight-streaming GEMM: enough CTAs to cover the SMs
+    about twice, every slice a whole multiple of 256 columns."""
+    cols_per_cta = 32 if rows <= 32 else 16
+    ctas = max(1, n // cols_per_cta)
+    want = max(1, -(-256 // ctas))
+    most = max(1, k // 256)
+    s = min(want, most, 16)
+    while s > 1 and (-(-k // s) + 255) // 256 * 256 * (s - 1) >= k:
+        s -= 1
+    return s
+
+
+class DecoderEngine:
+
+    def __init__(self, cfg: DecoderConfig, weights: DecoderWeights, kv_cache: torch.Tensor, max_tokens: int,
+                 max_seqs: int, block_size: int):
+        self.cfg = cfg
+        self.w = weights
+        self.kv_cache = kv_cache    # [2, L, pages, 256, Hkv, D]
+        self.block_size = block_size
+        self.max_tokens = max_tokens
+        self.max_seqs = max_seqs
+        dev = kv_cache.device
+        self.device = dev
+        bf = torch.bfloat16
+        h, i, d = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
+        hq, hkv = cfg.num_attention_heads, cfg.num_key_value_heads
+        if d != 128:
+            raise ValueError("the attention kernels are built for head_dim 128")
+        self.nqkv = (hq + 2 * hkv) * d
+        self.num_pages = kv_cache.shape[2]
+        self.rope = rope_table(cfg.max_position_embeddings, d, cfg.rope_theta, dev)
+        self.scale = d ** -0.5
+        t = max_tokens
+
+        def buf(*shape, dtype=bf):
+            return torch.empty(shape, dtype=dtype, device=dev)
+
+        self.embeds = buf(t, h)
+        self.x = buf(t, h)
+        self.res = buf(t, h)
+        self.q = buf(t, hq, d)
+        self.kbuf = buf(t, hkv, d)
+        self.vbuf = buf(t, hkv, d)
+        self.attn = buf(t, hq, d)
+        self.act = buf(t, i)
+        self.final = buf(t, h)
+        self.lm_rows = buf(max_seqs * block_size, h)
+        # weight-streaming path: fp32 split-k slices shared by all four GEMMs
+        rows = min(t, SKINNY_MAX_ROWS)
+        self.ks_qkv = pick_ksplit(self.nqkv, h, rows)
+        self.ks_o = pick_ksplit(h, hq * d, rows)
+        self.ks_down = pick_ksplit(h, i, rows)
+        part_elems = rows * max(self.ks_qkv * self.nqkv, self.ks_o * h, self.ks_down * h)
+        self.partials = buf(part_elems, dtype=torch.float32)
+        # tiled path: materialised bf16 GEMM outputs
+        if t > SKINNY_MAX_ROWS:
+            self.qkv_out = buf(t, self.nqkv)
+            self.h_out = buf(t, h)
+            self.gu_out = buf(t, 2 * i)
+        self.max_nsplit = 64
+        ws = ops._lib.lib().mdb_attn_paged_workspace_bytes(max_seqs, block_size, hq, self.max_nsplit)
+        # attention partials are only needed while CTAs are scarce: cap at what 64 requests use
+        ws = min(ws, ops._lib.lib().mdb_attn_paged_workspace_bytes(min(max_seqs, 64), block_size, hq, self.max_nsplit))
+        self.attn_ws = buf(max(int(ws), 16), dtype=torch.uint8)
+        self.lm_ws = buf(max(ops.lmhead_workspace_bytes(max_seqs * block_size, cfg.vocab_size), 16), dtype=torch.uint8)
+        self.x0 = buf(max_seqs * block_size, dtype=torch.int32)
+        self.conf = buf(max_seqs * block_size, dtype=torch.float32)
+
+    # ------------------------------------------------------------------
+    def attn_nsplit(self, bs: int, max_ctx: int) -> int:
+        cfg = self.cfg
+        n = ops.default_nsplit(bs, self.block_size, cfg.num_attention_heads, cfg.num_key_value_heads, max_ctx)
+        while n > 1 and ops._lib.lib().mdb_attn_paged_workspace_bytes(
+                bs, self.block_size, cfg.num_attention_heads, n) > self.attn_ws.numel():
+            n -= 1
+        return n
+
+    def forward(self, m: int, positions: torch.Tensor, ctx: Context, nsplit: int = 1,
+                max_seqlen: int = 0) -> torch.Tensor:
+        """Runs the layer stack over rows [0, m) of ``self.embeds``; returns
+        the final-norm hidden rows (a view of an internal buffer)."""
+        cfg = self.cfg
+        h, inter = cfg.hidden_size, cfg.intermediate_size
+        hq, hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        eps = cfg.rms_norm_eps
+        skinny = m <= SKINNY_MAX_ROWS
+        x, res = self.x[:m], self.res[:m]
+        q, attn, act = self.q[:m], self.attn[:m], self.act[:m]
+        pos = positions.reshape(-1)
+        slots = ctx.slot_mapping.reshape(-1) if ctx.slot_mapping is not None and ctx.slot_mapping.numel() else None
+        prev = None  # output of the previous layer's down projection: ("bf16", t) or ("parts", t)
+        for li, lw in enumerate(self.w.layers):
+            k_cache, v_cache = self.kv_cache[0, li], self.kv_cache[1, li]
+            if prev is None:
+                ops.add_rms_norm(self.embeds[:m], None, lw.input_ln, eps, out=x, residual_out=res)
+            elif prev[0] == "parts":
+                ops.add_rms_norm(None, res, lw.input_ln, eps, partials=prev[1], out=x, residual_out=res)
+            else:
+                ops.add_rms_norm(prev[1], res, lw.input_ln, eps, out=x, residual_out=res)
+
+            kb = self.kbuf[:m] if ctx.is_prefill else None
+            vb = self.vbuf[:m] if ctx.is_prefill else None
+            if skinny:
+                parts = self.partials[:self.ks_qkv * m * self.nqkv].view(self.ks_qkv, m, self.nqkv)
+                ops.gemm_splitk_partials(x, lw.qkv, self.ks_qkv, parts)
+                ops.qknorm_rope_commit(None, pos, self.rope, lw.q_norm, lw.k_norm, eps, hq, hkv, slots, k_cache,
+                                       v_cache, partials=parts, q_out=q, k_out=kb, v_out=vb)
+            else:
+                qkv = self.qkv_out[:m]
+                ops.linear(x, lw.qkv, out=qkv)
+                ops.qknorm_rope_commit(qkv, pos, self.rope, lw.q_norm, lw.k_norm, eps, hq, hkv, slots, k_cache,
+                                       v_cache, q_out=q, k_out=kb, v_out=vb)
+
+            if ctx.is_prefill:
+                ops.sparse_attn_varlen(q, kb, vb, ctx.cu_seqlens_q, ctx.cu_seqlens_k, ctx.block_size,
+                                       max_seqlen=max_seqlen, out=attn)
+            else:
+                bs = m // self.block_size
+                ops.block_attn_with_kvcache(q.view(bs, self.block_size, hq, d), k_cache, v_cache, ctx.context_lens,
+                                            ctx.block_tables, self.scale, nsplit=nsplit, workspace=self.attn_ws,
+                                            out=attn.view(bs, self.block_size, hq, d))
+            attn2 = attn.view(m, hq * d)
+            if skinny:
+                parts = self.partials[:self.ks_o * m * h].view(self.ks_o, m, h)
+                ops.gemm_splitk_partials(attn2, lw.o, self.ks_o, parts)
+                ops.add_rms_norm(None, res, lw.post_ln, eps, partials=parts, out=x, residual_out=res)
+                ops.gateup_swiglu(x, lw.gate_up, out=act)
+                parts = self.partials[:self.ks_down * m * h].view(self.ks_down, m, h)
+                ops.gemm_splitk_partials(act, lw.down, self.ks_down, parts)
+                prev = ("parts", parts)
+            else:
+                ho = self.h_out[:m]
+                ops.linear(attn2, lw.o, out=ho)
+                ops.add_rms_norm(ho, res, lw.post_ln, eps, out=x, residual_out=res)
+                gu = self.gu_out[:m]
+                ops.linear(x, lw.gate_up, out=gu)
+                ops.silu_and_mul(gu, out=act)
+                ops.linear(act, lw.down, out=ho)
+                prev = ("bf16", ho)
+        out = self.final[:m]
+        if prev[0] == "parts":
+            ops.add_rms_norm(None, res, self.w.final_ln, eps, partials=prev[1], out=out, residual_out=res)
+        else:
+            ops.add_rms_norm(prev[1], res, self.w.final_ln, eps, out=out, residual_out=res)
+        return out
+
+    def sample(self, rows: torch.Tensor, temperatures: torch.Tensor, noise=None, seed=None, step: int = 0,
+               step_dev=None):
+        """LM head + sampler statistics over ``rows`` [m, H]; returns views of
+        the internal x0 / confidence buffers."""
+        m = rows.shape[0]
+        return ops.lm_head_sample(rows, self.w.lm_head, temperatures, self.block_size, noise=noise, seed=seed,
+                                  step=step, step_dev=step_dev, workspace=self.lm_ws, x0=self.x0[:m],
+                                  conf=self.conf[:m])

@@ -1,0 +1,328 @@
+"""Drop-in for the reference's ``ModelRunner`` on one B200.
+
+Same constructor shape, ``call("run", seqs, is_prefill) -> int`` contract and
+side effects on the ``Sequence`` objects as
+``engines/nano_dvlm/nanovllm/engine/model_runner.py:15-219`` of the reference;
+the decoder underneath is ``DecoderEngine`` (hand-written sm_100a kernels via
+libmdb200).  The sampler's statistics and the unmask rule run on the device;
+one packed host->device copy feeds a step and one device->host copy returns
+the new block ids, transfer mask and counts.
+
+The vision tower is outside this path: a request carries the rows that stand
+for its output in ``Sequence.inputs_embeds`` and they overwrite the token
+embeddings of the first prompt positions, which is what
+``DMLLM._prepare_inputs_embeds`` does with the projector's rows
+(``nanovllm/models/dmllm.py:136-157``).
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..decoder import DecoderEngine, DecoderWeights
+from .config import Config
+from .context import Context
+from .sequence import Sequence
+
+
+def _round_up(v: int, a: int) -> int:
+    return (v + a - 1) // a * a
+
+
+class _StepInputs:
+    """One pinned host buffer and its device twin holding every per-step input
+    of the decode form, so a step costs a single host->device copy.
+
+    Layout (all offsets 16-byte aligned): ids int64 [bs*B] | positions int64
+    [bs*B] | slots int32 [bs*B] | ctx_lens int32 [bs] | block_tables int32
+    [bs*max_pages] | temperatures fp32 [bs] | step uint32 [4]."""
+
+    def __init__(self, max_bs: int, block: int, max_pages: int, device):
+        self.max_bs, self.block, self.max_pages = max_bs, block, max_pages
+        n = max_bs * block
+        off = 0
+        self.o_ids = off; off += _round_up(n * 8, 16)
+        self.o_pos = off; off += _round_up(n * 8, 16)
+        self.o_slots = off; off += _round_up(n * 4, 16)
+        self.o_ctx = off; off += _round_up(max_bs * 4, 16)
+        self.o_tab = off; off += _round_up(max_bs * max_pages * 4, 16)
+        self.o_temp = off; off += _round_up(max_bs * 4, 16)
+        self.o_step = off; off += 16
+        self.nbytes = off
+        self.host = torch.zeros(off, dtype=torch.uint8, pin_memory=True)
+        self.dev = torch.zeros(off, dtype=torch.uint8, device=device)
+
+    def _view(self, base, off, count, dtype):
+        return base[off:off + count * torch.empty(0, dtype=dtype).element_size()].view(dtype)
+
+    def views(self, base):
+        n = self.max_bs * self.block
+        return dict(
+            ids=self._view(base, self.o_ids, n, torch.int64).view(self.max_bs, self.block),
+            pos=self._view(base, self.o_pos, n, torch.int64).view(self.max_bs, self.block),
+            slots=self._view(base, self.o_slots, n, torch.int32).view(self.max_bs, self.block),
+            ctx=self._view(base, self.o_ctx, self.max_bs, torch.int32),
+            tab=self._view(base, self.o_tab, self.max_bs * self.max_pages, torch.int32).view(self.max_bs, self.max_pages),
+            temp=self._view(base, self.o_temp, self.max_bs, torch.float32),
+            step=self._view(base, self.o_step, 4, torch.int32),
+        )
+
+
+class ModelRunner:
+
+    def __init__(self, config: Config, rank: int = 0, event=None, weights: DecoderWeights | None = None,
+                 weight_seed: int = 20260320, noise: str = "gumbel", noise_seed: int = 0, device: str | None = None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("ModelRunner needs a CUDA device: the decode path has no CPU implementation")
+        if config.tensor_parallel_size != 1:
+            raise NotImplementedError("this runner drives one GPU; tensor_parallel_size must be 1")
+        if noise not in ("gumbel", "none", "explicit"):
+            raise ValueError("noise must be 'gumbel', 'none' or 'explicit'")
+        self.config = config
+        self.rank = rank
+        self.event = event
+        self.world_size = config.tensor_parallel_size
+        self.block_size = config.block_size
+        self.kvcache_block_size = config.kvcache_block_size
+        if self.kvcache_block_size != Sequence.kvcache_block_size:
+            raise AssertionError("only 256-token pages are consistent end to end")
+        self.enforce_eager = config.enforce_eager
+        self.device = torch.device(device or f"cuda:{rank}")
+        torch.cuda.set_device(self.device)
+        self.dcfg = config.decoder_config
+        self.weights = weights if weights is not None else DecoderWeights.random_init(self.dcfg, weight_seed, self.device)
+        self.noise = noise
+        self.noise_seed = noise_seed
+        self.noise_fn = None          # explicit mode: fn(step_index, m, vocab) -> fp32 [m, vocab] CUDA tensor
+        self.step_index = 0
+        self.allocate_kv_cache()
+        b = self.block_size
+        self.max_bs = min(config.max_num_seqs, 512)
+        max_tokens = max(config.max_num_batched_tokens + config.max_num_seqs * b, self.max_bs * b)
+        max_tokens = min(max_tokens, config.max_model_len * config.max_num_seqs + config.max_num_seqs * b)
+        self.engine = DecoderEngine(self.dcfg, self.weights, self.kv_cache, max_tokens, self.max_bs, b)
+        self.max_pages = (config.max_model_len + b + self.kvcache_block_size - 1) // self.kvcache_block_size
+        self.inputs = _StepInputs(self.max_bs, b, self.max_pages, self.device)
+        self.hv = self.inputs.views(self.inputs.host)
+        self.hn = {k: v.numpy() for k, v in self.hv.items()}   # numpy views of the pinned buffer
+        self.dv = self.inputs.views(self.inputs.dev)
+        # sampler state on the device and its pinned mirror: ids int64 | transfer u8 | counts i32
+        n = self.max_bs * b
+        self.block_ids = torch.zeros(self.max_bs, b, dtype=torch.int64, device=self.device)
+        self.transfer = torch.zeros(self.max_bs, b, dtype=torch.uint8, device=self.device)
+        self.counts = torch.zeros(self.max_bs, dtype=torch.int32, device=self.device)
+        self.h_block_ids = torch.zeros(self.max_bs, b, dtype=torch.int64, pin_memory=True)
+        self.h_transfer = torch.zeros(self.max_bs, b, dtype=torch.uint8, pin_memory=True)
+        self.h_counts = torch.zeros(self.max_bs, dtype=torch.int32, pin_memory=True)
+        self.graphs: dict[int, tuple[torch.cuda.CUDAGraph, int]] = {}
+        self.graph_bs: list[int] = []
+        self.last: dict = {}
+        self.keep_last = False        # tests: keep x0 / confidence / hidden of the last step
+        if not self.enforce_eager:
+            self.capture_cudagraph()
+
+    # ------------------------------------------------------------------ control plane
+    def call(self, method_name, *args):
+        return getattr(self, method_name)(*args)
+
+    def exit(self):
+        self.graphs.clear()
+        torch.cuda.synchronize(self.device)
+
+    # ------------------------------------------------------------------ memory
+    def allocate_kv_cache(self):
+        """kv_cache[2, L, pages, 256, Hkv, D] bf16, pages from the free-memory
+        budget unless ``config.num_kvcache_blocks`` is preset (> 0)."""
+        config, d = self.config, self.dcfg
+        block_bytes = 2 * d.num_hidden_layers * self.kvcache_block_size * d.num_key_value_heads * d.head_dim * 2
+        if config.num_kvcache_blocks <= 0:
+            free, total = torch.cuda.mem_get_info(self.device)
+            used = total - free
+            budget = int(total * config.gpu_memory_utilization) - used
+            # leave room for the activation buffers allocated after the cache
+            reserve = 6 << 30
+            config.num_kvcache_blocks = (budget - reserve) // block_bytes
+        if config.num_kvcache_blocks <= 0:
+            raise AssertionError("no memory left for the KV cache")
+        self.kv_cache = torch.zeros(2, d.num_hidden_layers, config.num_kvcache_blocks, self.kvcache_block_size,
+                                    d.num_key_value_heads, d.head_dim, dtype=torch.bfloat16, device=self.device)
+
+    # ------------------------------------------------------------------ host -> step tensors
+    def prepare_block_tables(self, seqs: list[Sequence]) -> list[list[int]]:
+        width = max(len(seq.block_table) for seq in seqs)
+        return [seq.block_table + [-1] * (width - len(seq.block_table)) for seq in seqs]
+
+    def prepare_prefill(self, seqs: list[Sequence]):
+        b = self.block_size
+        ids: list[int] = []
+        pos: list[int] = []
+        slots: list[int] = []
+        cu = [0]
+        max_len = 0
+        for seq in seqs:
+            seqlen = len(seq) + b
+            ids.extend(seq[seq.num_cached_tokens:] + seq.current_denoising_block.tolist())
+            pos.extend(range(seq.num_cached_tokens, seqlen))
+            cu.append(cu[-1] + seqlen - seq.num_cached_tokens)
+            max_len = max(max_len, seqlen)
+            if not seq.block_table:     # warm-up sequences hold no pages
+                continue
+            slots.extend(seq.get_slots(seq.num_cached_tokens, len(seq)) + [-1] * b)
+        dev = self.device
+        input_ids = torch.tensor(ids, dtype=torch.int64, pin_memory=True).to(dev, non_blocking=True)
+        positions = torch.tensor(pos, dtype=torch.int64, pin_memory=True).to(dev, non_blocking=True)
+        cu_q = torch.tensor(cu, dtype=torch.int32, pin_memory=True).to(dev, non_blocking=True)
+        slot_mapping = torch.tensor(slots, dtype=torch.int32, pin_memory=True).to(dev, non_blocking=True)
+        ctx = Context(True, cu_q, cu_q, max_len, max_len, slot_mapping, None, None, b)
+        return input_ids, positions, ctx, cu
+
+    def prepare_decode(self, seqs: list[Sequence]):
+        """Fills the packed pinned buffer; returns the device views of a step."""
+        b, bs = self.block_size, len(seqs)
+        tables = self.prepare_block_tables(seqs)
+        width = len(tables[0])
+        if width > self.max_pages:
+            raise AssertionError("page table wider than max_model_len allows")
+        hn = self.hn
+        hn["slots"].fill(-1)
+        hn["ctx"].fill(0)
+        hn["tab"][:bs, :width] = np.asarray(tables, dtype=np.int32)
+        for i, seq in enumerate(seqs):
+            n = len(seq)
+            hn["ids"][i] = seq.current_denoising_block.numpy()
+            hn["pos"][i] = np.arange(n, n + b, dtype=np.int64)
+            hn["slots"][i] = seq.get_slots(n, n + b)
+            hn["ctx"][i] = n + b
+            hn["temp"][i] = seq.temperature
+        hn["step"][0] = self.step_index
+        self.inputs.dev.copy_(self.inputs.host, non_blocking=True)
+        return max(len(seq) for seq in seqs) + b
+
+    def prepare_sample(self, seqs: list[Sequence]) -> torch.Tensor:
+        t = torch.tensor([seq.temperature for seq in seqs], dtype=torch.float32, pin_memory=True)
+        return t.to(self.device, non_blocking=True)
+
+    # ------------------------------------------------------------------ forward passes
+    def _noise_args(self, m: int):
+        if self.noise == "gumbel":
+            return dict(seed=self.noise_seed)
+        if self.noise == "explicit":
+            if self.noise_fn is None:
+                raise RuntimeError("noise='explicit' needs runner.noise_fn")
+            return dict(noise=self.noise_fn(self.step_index, m, self.dcfg.vocab_size))
+        return {}
+
+    def _decode_body(self, bs: int, nsplit: int):
+        """Everything of a decode step that depends only on device buffers:
+        embedding gather, layer stack, LM head + sampler statistics."""
+        b = self.block_size
+        m = bs * b
+        dv, eng = self.dv, self.engine
+        ops.gather_rows(self.weights.embed, dv["ids"][:bs].reshape(-1), out=eng.embeds[:m])
+        ctx = Context(False, slot_mapping=dv["slots"][:bs], context_lens=dv["ctx"][:bs],
+                      block_tables=dv["tab"][:bs], block_size=b)
+        hidden = eng.forward(m, dv["pos"][:bs], ctx, nsplit=nsplit)
+        kw = self._noise_args(m)
+        if "seed" in kw:
+            kw["step_dev"] = dv["step"]
+        eng.sample(hidden, dv["temp"][:bs], **kw)
+        return hidden
+
+    @torch.inference_mode()
+    def run_model_decode(self, seqs: list[Sequence]):
+        bs = len(seqs)
+        max_ctx = self.prepare_decode(seqs)
+        use_graph = (not self.enforce_eager) and self.noise != "explicit" and bs <= self.max_bs and self.graph_bs
+        if use_graph:
+            gbs = next(x for x in self.graph_bs if x >= bs)
+            graph, _ = self.graphs[gbs]
+            graph.replay()
+            return None
+        return self._decode_body(bs, self.engine.attn_nsplit(bs, max_ctx))
+
+    @torch.inference_mode()
+    def run_model_prefill(self, seqs: list[Sequence]):
+        b = self.block_size
+        input_ids, positions, ctx, cu = self.prepare_prefill(seqs)
+        m = input_ids.numel()
+        eng = self.engine
+        if m > eng.max_tokens:
+            raise AssertionError("prefill batch exceeds the activation buffers")
+        ops.gather_rows(self.weights.embed, input_ids, out=eng.embeds[:m])
+        for i, seq in enumerate(seqs):
+            if seq.inputs_embeds is not None and seq.num_cached_tokens == 0:
+                rows = seq.inputs_embeds
+                eng.embeds[cu[i]:cu[i] + rows.shape[0]].copy_(rows.to(self.device, non_blocking=True))
+        hidden = eng.forward(m, positions, ctx, max_seqlen=ctx.max_seqlen_q)
+        # the LM head sees the last B rows of every sequence (embed_head.py:63-66 of the reference)
+        last = torch.tensor([cu[i + 1] - b + j for i in range(len(seqs)) for j in range(b)], dtype=torch.int64,
+                            pin_memory=True).to(self.device, non_blocking=True)
+        rows = ops.gather_rows(hidden, last, out=eng.lm_rows[:len(seqs) * b])
+        temps = self.prepare_sample(seqs)
+        eng.sample(rows, temps, step=self.step_index, **self._noise_args(rows.shape[0]))
+        return rows
+
+    # ------------------------------------------------------------------ entry point
+    def run(self, seqs: list[Sequence], is_prefill: bool) -> int:
+        bs, b = len(seqs), self.block_size
+        if bs > self.max_bs:
+            raise AssertionError("batch larger than max_num_seqs")
+        hidden = self.run_model_prefill(seqs) if is_prefill else self.run_model_decode(seqs)
+        with torch.inference_mode():
+            # sampler state: the host copy of each block is the source of truth, as in the reference
+            for i, seq in enumerate(seqs):
+                self.h_block_ids[i] = seq.current_denoising_block
+            self.block_ids[:bs].copy_(self.h_block_ids[:bs], non_blocking=True)
+            sp = seqs[0].sampling_params
+            if sp.denoising_strategy != "low_confidence_dynamic":
+                raise NotImplementedError(f"Denoising strategy {sp.denoising_strategy} not implemented")
+            quota = 1
+            if sp.denoising_steps:
+                quota = max(1, b // sp.denoising_steps)
+            m = bs * b
+            ops.unmask_decide(self.block_ids[:bs], self.engine.x0[:m], self.engine.conf[:m], seqs[0].mask_token_id,
+                              sp.dynamic_threshold, quota, transfer=self.transfer[:bs], counts=self.counts[:bs])
+            self.h_block_ids[:bs].copy_(self.block_ids[:bs], non_blocking=True)
+            self.h_transfer[:bs].copy_(self.transfer[:bs], non_blocking=True)
+            self.h_counts[:bs].copy_(self.counts[:bs], non_blocking=True)
+            if self.keep_last:
+                self.last = dict(x0=self.engine.x0[:m].clone(), conf=self.engine.conf[:m].clone(),
+                                 hidden=None if hidden is None else hidden.clone())
+            torch.cuda.current_stream().synchronize()
+        total = 0
+        for i, seq in enumerate(seqs):
+            seq.current_denoising_block = self.h_block_ids[i].clone()
+            moved = self.h_transfer[i].bool()
+            seq.current_step_map[moved] = seq.current_denoise_step
+            seq.current_denoise_step += 1
+            total += int(self.h_counts[i])
+        self.step_index += 1
+        return total
+
+    # ------------------------------------------------------------------ CUDA graphs
+    @torch.inference_mode()
+    def capture_cudagraph(self):
+        """One graph per batch-size bucket covering embedding gather, all
+        layers, the LM head and the sampler statistics.  Padded rows carry
+        slot -1 and context length 0, which every kernel treats as a no-op."""
+        if self.noise == "explicit":
+            return
+        max_bs = self.max_bs
+        self.graph_bs = [x for x in (1, 2, 4, 8) if x <= max_bs] + list(range(16, max_bs + 1, 16))
+        hv = self.hv
+        hv["ids"].zero_(); hv["pos"].zero_(); hv["slots"].fill_(-1); hv["ctx"].zero_(); hv["tab"].fill_(-1)
+        hv["temp"].fill_(1.0)
+        self.inputs.dev.copy_(self.inputs.host)
+        pool = None
+        for bs in reversed(self.graph_bs):
+            nsplit = self.engine.attn_nsplit(bs, self.config.max_model_len)
+            self._decode_body(bs, nsplit)   # warm-up: sets kernel attributes outside capture
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, pool):
+                self._decode_body(bs, nsplit)
+            if pool is None:
+                pool = graph.pool()
+            self.graphs[bs] = (graph, nsplit)
+        torch.cuda.synchronize()

@@ -1,0 +1,348 @@
+"""Benchmark of the block-diffusion decode path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload at N=1 ("config2"): the full decoder at the reference's configuration
+defaults (28 layers, hidden 2048, 16 query / 8 KV heads, vocabulary 151936,
+bf16), seeded N(0, 0.02) weights with RMSNorm weights 1, one request whose
+prompt is 1024 synthetic visual embedding rows N(0, 1) plus 32 random text
+ids; 1024 tokens are generated in blocks of 32, threshold 0.9, temperature 1,
+Gumbel noise on.  A step is one pass of the hot path (``ModelRunner.run`` in
+decode form: a denoising pass or the KV-commit pass of a finished block).
+With N > 1 every rank runs its own request of the same shape (request-level
+data parallelism, no data-path collective).
+
+Printed JSON line: ``value`` = tokens committed in the K timed steps divided by
+the device time of those steps (inputs resident, CUDA events around the GPU
+work of each step); ``e2e`` = the same tokens divided by the bracketed wall
+time of the K calls through the public API, host->device and device->host
+copies included.  ``roofline`` is measured live for the dominant kernel (the
+weight-streaming gate/up projection with fused SiLU*mul) by launching it over
+the 28 layers' distinct weights (1.4 GB > L2) between CUDA events.
+``cpu_baseline`` times the CPU oracle (the reference's torch ops on the host
+cores) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+BLOCK = 32
+VISUAL_ROWS = 1024
+TEXT_IDS = 32
+NEW_TOKENS = 1024
+THRESHOLD = 0.9
+WEIGHT_SEED = 20260320
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples nvidia-smi SM clocks and throttle reasons while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------- workload
+def make_request(pkg, dcfg, seed: int, device):
+    g = torch.Generator().manual_seed(seed)
+    visual = torch.randn(VISUAL_ROWS, dcfg.hidden_size, generator=g).to(torch.bfloat16)
+    text = torch.randint(0, 151000, (TEXT_IDS,), generator=g).tolist()
+    ids = [0] * VISUAL_ROWS + text          # the visual positions' ids are never embedded
+    sp = pkg.SamplingParams(temperature=1.0, max_new_tokens=NEW_TOKENS, ignore_eos=True, dynamic_threshold=THRESHOLD)
+    return pkg.Sequence(ids, sp, denoising_block_size=BLOCK, mask_token_id=151669,
+                        inputs_embeds=visual.pin_memory() if device != "cpu" else visual)
+
+
+def run_ours(args, rank: int, world: int, local_rank: int):
+    pkg = importlib.import_module("mineru-diffusion_b200")
+    device = f"cuda:{local_rank}"
+    torch.cuda.set_device(device)
+    dcfg = pkg.DecoderConfig()
+    total_len = VISUAL_ROWS + TEXT_IDS + NEW_TOKENS + BLOCK
+    cfg = pkg.Config(max_num_batched_tokens=4096, max_num_seqs=1, max_model_len=4096, enforce_eager=False,
+                     num_kvcache_blocks=(total_len + 255) // 256 + 1, decoder_config=dcfg)
+    runner = pkg.ModelRunner(cfg, rank=0, weight_seed=WEIGHT_SEED, noise="gumbel", noise_seed=2 + rank, device=device)
+    engine = pkg.LLMEngine(cfg, runner)
+    engine.add_sequence(make_request(pkg, dcfg, seed=2 + rank, device=device))
+    stream = torch.cuda.current_stream()
+
+    # prefill (first denoising pass of the first block) + warm-up decode steps, untimed
+    engine.step()
+    for _ in range(args.warmup):
+        engine.step()
+    torch.cuda.synchronize()
+
+    # per-step device time: events around the GPU work of each step
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    sampler = ClockSampler(local_rank)
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    tokens = 0
+    steps_done = 0
+    launches_per_step = runner.launches_per_decode_step()
+    wall0 = time.perf_counter()
+    e_all0 = torch.cuda.Event(enable_timing=True)
+    e_all1 = torch.cuda.Event(enable_timing=True)
+    e_all0.record(stream)
+    for i in range(args.steps):
+        if engine.is_finished():
+            break
+        runner.step_events = ev[i]
+        _, n = engine.step()
+        tokens += -n if n < 0 else 0
+        steps_done += 1
+    e_all1.record(stream)
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - wall0
+    if world > 1:
+        torch.distributed.barrier()
+    clocks = sampler.stop()
+    runner.step_events = None
+    dev_ms = sum(a.elapsed_time(b) for a, b in ev[:steps_done])
+    e2e_ms = e_all0.elapsed_time(e_all1)
+    h2d = runner.inputs.nbytes + BLOCK * 8
+    d2h = BLOCK * 8 + BLOCK + 4
+
+    roof = measure_dominant_kernel(pkg, runner) if rank == 0 else None
+    return dict(tokens=tokens, steps=steps_done, dev_ms=dev_ms, e2e_ms=max(e2e_ms, wall * 1e3), clocks=clocks,
+                h2d=h2d, d2h=d2h, launches=launches_per_step * steps_done, roofline=roof,
+                ctx_end=len(engine.scheduler.running[0]) if engine.scheduler.running else total_len)
+
+
+def measure_dominant_kernel(pkg, runner, iters: int = 5):
+    """Live roofline of the gate/up projection kernel: one launch per layer over
+    distinct weights (28 x 50 MB, far beyond L2), CUDA events around the loop."""
+    peaks = {}
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            peaks = json.load(f)
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    eng = runner.engine
+    dcfg = runner.dcfg
+    m = BLOCK
+    x = eng.x[:m]
+    act = eng.act[:m]
+    layers = runner.weights.layers
+    ops = pkg.ops
+    for lw in layers:                      # warm-up pass
+        ops.gateup_swiglu(x, lw.gate_up, out=act)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        for lw in layers:
+            ops.gateup_swiglu(x, lw.gate_up, out=act)
+    e1.record()
+    torch.cuda.synchronize()
+    launches = iters * len(layers)
+    ms = e0.elapsed_time(e1) / launches
+    h, inter = dcfg.hidden_size, dcfg.intermediate_size
+    alg_bytes = 2 * inter * h * 2 + m * h * 2 + m * inter * 2     # weights once + activations in/out
+    achieved = alg_bytes / (ms * 1e-3) / 1e9
+    return {"bound": "hbm", "kernel": "gemm_skinny_kernel<2,4,swiglu> (gate_up + SiLU*mul, m=32)",
+            "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
+            "traffic": None, "peak_source": "measured" if peaks else "fallback",
+            "bytes_per_launch": alg_bytes, "us_per_launch": round(ms * 1e3, 2)}
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def run_cpu_sample(steps: int, warmup: int, threads: int | None = None):
+    """The reference's torch CPU path (restated in oracle/) on a bounded sample
+    of the workload: decode-form denoising passes of the full-size decoder at
+    the context length reached half way through generation, KV cache filled
+    with seeded noise instead of a CPU prefill."""
+    from oracle import nano_oracle as orc
+    if threads:
+        torch.set_num_threads(threads)
+    orc.use_native_linear(True)
+    cfg = orc.DecoderConfig()
+    g = torch.Generator().manual_seed(WEIGHT_SEED)
+    bf = torch.bfloat16
+
+    def mat(r, c):
+        return (torch.randn(r, c, generator=g) * 0.02).to(bf)
+
+    h, i, d = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
+    hq, hkv = cfg.num_attention_heads, cfg.num_key_value_heads
+    base = orc.LayerWeights(torch.ones(h, dtype=bf), mat((hq + 2 * hkv) * d, h), torch.ones(d, dtype=bf),
+                            torch.ones(d, dtype=bf), mat(h, hq * d), torch.ones(h, dtype=bf), mat(2 * i, h), mat(h, i))
+    layers = [base]
+    for _ in range(cfg.num_hidden_layers - 1):     # distinct memory per layer, same distribution
+        layers.append(orc.LayerWeights(base.input_ln, base.qkv.roll(1, 0).contiguous(), base.q_norm, base.k_norm,
+                                       base.o.roll(1, 0).contiguous(), base.post_ln,
+                                       base.gate_up.roll(1, 0).contiguous(), base.down.roll(1, 0).contiguous()))
+    embed = mat(cfg.vocab_size, h)
+    weights = orc.DecoderWeights(embed, layers, torch.ones(h, dtype=bf), embed.roll(1, 0).contiguous())
+    prefix = VISUAL_ROWS + TEXT_IDS + NEW_TOKENS // 2
+    pages = (prefix + BLOCK + 255) // 256
+    runner = orc.OracleModelRunner(cfg, weights, num_pages=pages, block_size=BLOCK, mask_token_id=151669,
+                                   noise_fn=lambda step, shape: -torch.empty(shape).exponential_(generator=g).log())
+    runner.decoder.kv_cache.normal_(generator=g)
+
+    class Req:
+        def __init__(self):
+            from types import SimpleNamespace
+            self.seq_id = 0
+            self.token_ids = [1] * prefix
+            self.block_table = list(range(pages))
+            self.num_cached_tokens = 0
+            self.temperature = 1.0
+            self.mask_token_id = 151669
+            self.sampling_params = SimpleNamespace(dynamic_threshold=THRESHOLD)
+            self.current_denoising_block = torch.full((BLOCK,), 151669, dtype=torch.int64)
+            self.current_step_map = torch.zeros(BLOCK, dtype=torch.int32)
+            self.current_denoise_step = 0
+
+        def __len__(self):
+            return len(self.token_ids)
+
+        def __getitem__(self, k):
+            return self.token_ids[k]
+
+    req = Req()
+    with torch.inference_mode():
+        for _ in range(warmup):
+            runner.run([req], False)
+        t0 = time.perf_counter()
+        tokens = 0
+        for _ in range(steps):
+            tokens += runner.run([req], False)
+        dt = time.perf_counter() - t0
+    orc.use_native_linear(False)
+    return tokens, dt, torch.get_num_threads(), prefix
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=330)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    config = {"workload": "config2: full decoder (28 layers, hidden 2048, 16q/8kv heads, vocab 151936), 1 request per "
+                          "GPU, 1024 synthetic visual rows + 32 text ids, 1024 new tokens, block 32, threshold 0.9, "
+                          "temperature 1.0",
+              "block_size": BLOCK, "requests_per_gpu": 1, "parallelism": f"dp{args.gpus}",
+              "l2_policy": "per-step weight traffic (3.4 GB) exceeds L2 (126 MB); no explicit flush"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        steps = min(args.steps, 6)
+        tokens, dt, threads, prefix = run_cpu_sample(steps, min(args.warmup, 1))
+        value = tokens / dt
+        line = {"impl": "reference", "metric": "decoded tokens/sec per B200 (block diffusion, bf16)",
+                "value": round(value, 4), "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps,
+                "warmup": min(args.warmup, 1), "ms_per_step": round(dt / steps * 1e3, 2), "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
+                "cpu_baseline": {"value": round(value, 4), "unit": "tokens/s", "cores": threads, "kind": "port",
+                                 "sample": f"{steps} denoising passes at context {prefix + BLOCK} (mid-generation), "
+                                           "full-size decoder, reference torch CPU ops restated in oracle/"},
+                "e2e": {"value": round(value, 4), "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                        "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+    res = run_ours(args, rank, world, local_rank)
+    tokens, dev_ms, e2e_ms = res["tokens"], res["dev_ms"], res["e2e_ms"]
+    if world > 1:
+        t = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=f"cuda:{local_rank}")
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        dev_ms, e2e_ms = float(t[0]), float(t[1])
+        c = torch.tensor([tokens, res["launches"]], dtype=torch.int64, device=f"cuda:{local_rank}")
+        torch.distributed.all_reduce(c)
+        tokens, launches = int(c[0]), int(c[1])
+    else:
+        launches = res["launches"]
+    if rank == 0:
+        cpu = None
+        if args.gpus == 1 and not args.no_cpu_baseline:
+            ctok, cdt, threads, prefix = run_cpu_sample(3, 1)
+            cpu = {"value": round(ctok / cdt, 4), "unit": "tokens/s", "cores": threads, "kind": "port",
+                   "sample": f"3 denoising passes at context {prefix + BLOCK} (mid-generation), full-size decoder, "
+                             "reference torch CPU ops restated in oracle/"}
+        line = {"metric": "decoded tokens/sec per B200 (block diffusion, bf16)",
+                "value": round(tokens / (dev_ms * 1e-3), 2), "unit": "tokens/s", "n_gpus": args.gpus,
+                "steps": res["steps"], "warmup": args.warmup, "ms_per_step": round(dev_ms / max(res["steps"], 1), 4),
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+                "data": "synthetic", "config": config,
+                "e2e": {"value": round(tokens / (e2e_ms * 1e-3), 2), "unit": "tokens/s",
+                        "h2d_bytes_per_step": res["h2d"], "d2h_bytes_per_step": res["d2h"],
+                        "ms_per_step": round(e2e_ms / max(res["steps"], 1), 4)},
+                "gpu_launches": launches, "clocks": res["clocks"], "roofline": res["roofline"], "cpu_baseline": cpu,
+                "tokens": tokens}
+        print(json.dumps(line))
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -45,6 +45,15 @@ enum {
 const char* mdb_strerror(int code);
 int mdb_version(void);
 
+/* Process-wide switches (no counterpart in the reference; for measurement and
+ * fault isolation).  MDB_OPT_STREAM_KERNEL: 0 = short steps (m <= 64) use the
+ * tcgen05/TMA weight-streaming kernel where the shape allows (default), 1 =
+ * always the register-streaming kernel.  MDB_OPT_PDL: 1 = kernels are chained
+ * with programmatic dependent launch (default), 0 = plain stream order. */
+enum { MDB_OPT_STREAM_KERNEL = 0, MDB_OPT_PDL = 1 };
+int mdb_set_option(int option, int value);
+int mdb_get_option(int option);
+
 /* Copies the status word of the current device to *out (host memory) after
  * synchronising the device; clear != 0 resets it.  Plays the part of the
  * reference's host asserts (NV/layers/attention.py:36-39). */
@@ -99,6 +108,7 @@ int mdb_gemm_bf16(const void* x, int64_t ldx, const void* w, void* y, int64_t ld
  * ksplit slices and writes fp32 partial sums partials[ksplit][m][n]; the
  * consumers below add the slices in index order, round to bf16 where F.linear
  * would, and apply the layer that follows. */
+int mdb_gemm_pick_ksplit(int m, int n, int k); /* a ksplit that suits the kernel these shapes will run on */
 int64_t mdb_gemm_splitk_workspace_bytes(int m, int n, int ksplit);
 int mdb_gemm_splitk_partials(const void* x, int64_t ldx, const void* w, float* partials, int m, int n, int k,
                              int ksplit, mdb_stream_t stream);

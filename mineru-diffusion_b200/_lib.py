@@ -20,12 +20,15 @@ _f = C.c_float
 SIGNATURES = {
     "mdb_strerror": (C.c_char_p, [_i]),
     "mdb_version": (_i, []),
+    "mdb_set_option": (_i, [_i, _i]),
+    "mdb_get_option": (_i, [_i]),
     "mdb_last_device_status": (_i, [C.POINTER(C.c_uint), _i]),
     "mdb_kv_commit": (_i, [_p, _i64, _p, _i64, _p, _p, _p, _i, _i, _i64, _p]),
     "mdb_attn_paged_workspace_bytes": (_i64, [_i, _i, _i, _i]),
     "mdb_attn_block_paged": (_i, [_p, _p, _p, _p, _p, _i, _p, _i, _i, _i, _i, _i, _f, _i, _p, _i64, _p]),
     "mdb_attn_staircase_varlen": (_i, [_p, _i64, _p, _i64, _p, _i64, _p, _i64, _p, _i, _i, _i, _i, _i, _p]),
     "mdb_gemm_bf16": (_i, [_p, _i64, _p, _p, _i64, _i, _i, _i, _p]),
+    "mdb_gemm_pick_ksplit": (_i, [_i, _i, _i]),
     "mdb_gemm_splitk_workspace_bytes": (_i64, [_i, _i, _i]),
     "mdb_gemm_splitk_partials": (_i, [_p, _i64, _p, _p, _i, _i, _i, _i, _p]),
     "mdb_gemm_gateup_swiglu": (_i, [_p, _i64, _p, _p, _i64, _i, _i, _i, _p]),

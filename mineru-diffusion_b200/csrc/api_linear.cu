@@ -15,7 +15,7 @@ struct LmHeadLayout {
 LmHeadLayout lmhead_layout(int m, int vocab) {
   LmHeadLayout l;
   const bool streaming = m <= 64;
-  l.nparts = streaming ? vocab / 32 : (vocab + kScanCols - 1) / kScanCols;
+  l.nparts = streaming ? (vocab + 31) / 32 : (vocab + kScanCols - 1) / kScanCols;
   l.off_i = align256(l.nparts * m * 16);
   l.off_logits = l.off_i + align256(l.nparts * m * 4);
   l.total = l.off_logits + (streaming ? 0 : align256(static_cast<int64_t>(m) * vocab * 2));
@@ -24,10 +24,8 @@ LmHeadLayout lmhead_layout(int m, int vocab) {
 
 int finalize_sampler(const float4* part_f, const int* part_i, int nparts, int m, int32_t* x0_out, float* conf_out,
                      cudaStream_t st) {
-  const int threads = 128;
-  const int blocks = (m * 32 + threads - 1) / threads;
-  sampler_finalize_kernel<<<blocks, threads, 0, st>>>(part_f, part_i, nparts, m, x0_out, conf_out);
-  return mdb_check_launch();
+  return mdb_launch(sampler_finalize_kernel, dim3(m), dim3(kFinalizeThreads), 0, st, part_f, part_i, nparts, m, x0_out,
+                    conf_out);
 }
 
 int scan_logits(const bf16* logits, int64_t ld, int m, int vocab, const float* temperatures, int block, int noise_mode,
@@ -37,16 +35,109 @@ int scan_logits(const bf16* logits, int64_t ld, int m, int vocab, const float* t
   float4* part_f = reinterpret_cast<float4*>(ws);
   int* part_i = reinterpret_cast<int*>(ws + align256(static_cast<int64_t>(nparts) * m * 16));
   dim3 grid(nparts, m);
-  logits_scan_kernel<<<grid, 256, 0, st>>>(logits, ld, m, vocab, temperatures, block, noise_mode, noise, seed, step,
-                                           step_dev, part_f, part_i);
-  int rc = mdb_check_launch();
+  int rc = mdb_launch(logits_scan_kernel, grid, dim3(256), 0, st, logits, ld, m, vocab, temperatures, block, noise_mode,
+                      noise, seed, step, step_dev, part_f, part_i);
   if (rc != MDB_OK) return rc;
   return finalize_sampler(part_f, part_i, nparts, m, x0_out, conf_out, st);
+}
+
+bool use_ws(int epi, int m, int n, int k, int64_t ldx) {
+  return g_opt_stream_kernel == 0 && ws_supported(epi, m, n, k, ldx);
+}
+
+// k slices of the tensor-core streaming kernel: about one task per SM, at least four 64-wide chunks per slice
+int ws_pick_ksplit(int n, int k) {
+  const int tiles = n / kWsTileRows;
+  const int chunks = k / kWsBK;
+  int s = tiles > 0 ? 148 / tiles : 1;
+  if (s < 1) s = 1;
+  if (s > chunks / 4) s = chunks / 4 > 0 ? chunks / 4 : 1;
+  if (s > 32) s = 32;
+  // every slice must be non-empty
+  while (s > 1 && ((chunks + s - 1) / s) * (s - 1) >= chunks) --s;
+  return s;
+}
+
+int skinny_pick_ksplit(int m, int n, int k) {
+  const int cols_per_cta = m <= 32 ? 32 : 16;
+  const int ctas = n / cols_per_cta > 0 ? n / cols_per_cta : 1;
+  int s = (256 + ctas - 1) / ctas;
+  if (s > k / 256) s = k / 256;
+  if (s > 16) s = 16;
+  if (s < 1) s = 1;
+  while (s > 1 && static_cast<int64_t>(skinny_k_per_cta(k, s)) * (s - 1) >= k) --s;
+  return s;
 }
 
 }  // namespace
 
 extern "C" {
+
+int mdb_gemm_pick_ksplit(int m, int n, int k) {
+  if (m < 1 || n < 1 || k < 1) return 1;
+  if (use_ws(kWsPartial, m, n, k, k)) return ws_pick_ksplit(n, k);
+  return skinny_pick_ksplit(m, n, k);
+}
+
+int64_t mdb_gemm_splitk_workspace_bytes(int m, int n, int ksplit) {
+  if (m <= 0 || n <= 0 || ksplit <= 0) return 0;
+  return static_cast<int64_t>(ksplit) * m * n * 4;
+}
+
+int mdb_gemm_splitk_partials(const void* x, int64_t ldx, const void* w, float* partials, int m, int n, int k,
+                             int ksplit, mdb_stream_t stream) {
+  if (m == 0) return MDB_OK;
+  int rc = check_skinny_common(x, ldx, w, m, n, k);
+  if (rc != MDB_OK) return rc;
+  MDB_REQUIRE(partials != nullptr && ksplit >= 1 && ksplit <= 64, MDB_ERR_ARG);
+  MDB_REQUIRE(mdb_aligned16(partials), MDB_ERR_ALIGN);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (use_ws(kWsPartial, m, n, k, ldx)) {
+    const int chunks = k / kWsBK;
+    const int per = (chunks + ksplit - 1) / ksplit;
+    MDB_REQUIRE(per * (ksplit - 1) < chunks, MDB_ERR_ARG);   // no empty slice: every partial row is written
+    WsArgs a = {};
+    a.m = m; a.n = n; a.k = k; a.ksplit = ksplit;
+    a.partials = partials;
+    return launch_ws<kWsPartial>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), a, st);
+  }
+  MDB_REQUIRE(static_cast<int64_t>(skinny_k_per_cta(k, ksplit)) * (ksplit - 1) < k, MDB_ERR_ARG);
+  SkinnyArgs a = {};
+  a.x = static_cast<const bf16*>(x);
+  a.w = static_cast<const bf16*>(w);
+  a.ldx = ldx;
+  a.m = m; a.n = n; a.k = k;
+  a.partials = partials;
+  return launch_skinny<kEpiPartial>(a, ksplit, st);
+}
+
+int mdb_gemm_gateup_swiglu(const void* x, int64_t ldx, const void* w_gate_up, void* act, int64_t ld_act, int m,
+                           int inter, int k, mdb_stream_t stream) {
+  if (m == 0) return MDB_OK;
+  int rc = check_skinny_common(x, ldx, w_gate_up, m, 2 * inter, k);
+  if (rc != MDB_OK) return rc;
+  MDB_REQUIRE(act != nullptr && ld_act >= inter, MDB_ERR_ARG);
+  MDB_REQUIRE(inter % 16 == 0, MDB_ERR_UNSUPPORTED);
+  MDB_REQUIRE(ld_act % 2 == 0 && mdb_aligned16(act), MDB_ERR_ALIGN);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (use_ws(kWsSwiglu, m, 2 * inter, k, ldx)) {
+    WsArgs a = {};
+    a.m = m; a.n = 2 * inter; a.k = k; a.ksplit = 1;
+    a.inter = inter;
+    a.y = static_cast<bf16*>(act);
+    a.ldy = ld_act;
+    return launch_ws<kWsSwiglu>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w_gate_up), a, st);
+  }
+  SkinnyArgs a = {};
+  a.x = static_cast<const bf16*>(x);
+  a.w = static_cast<const bf16*>(w_gate_up);
+  a.ldx = ldx;
+  a.m = m; a.n = 2 * inter; a.k = k;
+  a.y = static_cast<bf16*>(act);
+  a.ldy = ld_act;
+  a.inter = inter;
+  return launch_skinny<kEpiSwiglu>(a, 1, st);
+}
 
 int mdb_gemm_bf16(const void* x, int64_t ldx, const void* w, void* y, int64_t ldy, int m, int n, int k,
                   mdb_stream_t stream) {
@@ -56,6 +147,13 @@ int mdb_gemm_bf16(const void* x, int64_t ldx, const void* w, void* y, int64_t ld
   MDB_REQUIRE(ldx % 8 == 0 && ldy % 2 == 0 && mdb_aligned16(x) && mdb_aligned16(w) && mdb_aligned16(y),
               MDB_ERR_ALIGN);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (use_ws(kWsBf16, m, n, k, ldx)) {
+    WsArgs a = {};
+    a.m = m; a.n = n; a.k = k; a.ksplit = 1;
+    a.y = static_cast<bf16*>(y);
+    a.ldy = ldy;
+    return launch_ws<kWsBf16>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), a, st);
+  }
   if (m <= 64 && n % 32 == 0 && k % 32 == 0) {
     SkinnyArgs a = {};
     a.x = static_cast<const bf16*>(x);
@@ -91,6 +189,21 @@ int mdb_lmhead_sample(const void* hidden, int64_t ld_hidden, const void* w, int 
   MDB_REQUIRE(workspace_bytes >= lay.total, MDB_ERR_WORKSPACE);
   unsigned char* ws = static_cast<unsigned char*>(workspace);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (use_ws(kWsLmHead, m, vocab, h, ld_hidden)) {
+    WsArgs a = {};
+    a.m = m; a.n = vocab; a.k = h; a.ksplit = 1;
+    a.temperatures = temperatures;
+    a.block = block;
+    a.noise_mode = noise_mode;
+    a.noise = noise;
+    a.seed = seed; a.step = step;
+    a.step_dev = step_dev;
+    a.part_f = reinterpret_cast<float4*>(ws);
+    a.part_i = reinterpret_cast<int*>(ws + lay.off_i);
+    int rc = launch_ws<kWsLmHead>(static_cast<const bf16*>(hidden), ld_hidden, static_cast<const bf16*>(w), a, st);
+    if (rc != MDB_OK) return rc;
+    return finalize_sampler(a.part_f, a.part_i, vocab / kWsTileRows, m, x0_out, conf_out, st);
+  }
   if (m <= 64) {
     MDB_REQUIRE(vocab % 32 == 0 && h % 32 == 0, MDB_ERR_UNSUPPORTED);
     SkinnyArgs a = {};
@@ -108,7 +221,7 @@ int mdb_lmhead_sample(const void* hidden, int64_t ld_hidden, const void* w, int 
     a.part_i = reinterpret_cast<int*>(ws + lay.off_i);
     int rc = launch_skinny<kEpiLmHead>(a, 1, st);
     if (rc != MDB_OK) return rc;
-    return finalize_sampler(a.part_f, a.part_i, static_cast<int>(lay.nparts), m, x0_out, conf_out, st);
+    return finalize_sampler(a.part_f, a.part_i, vocab / 32, m, x0_out, conf_out, st);
   }
   MDB_REQUIRE(h % kGemmBK == 0 && vocab % 2 == 0, MDB_ERR_UNSUPPORTED);
   bf16* logits = reinterpret_cast<bf16*>(ws + lay.off_logits);

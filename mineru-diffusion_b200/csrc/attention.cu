@@ -158,6 +158,8 @@ __device__ __forceinline__ void attn_tile_step(const uint32_t (&qf)[8][4], uint3
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(kAttnWarps * 32)
 attn_block_paged_kernel(const AttnPagedArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const uint32_t smem = smem_u32(smem_raw);
   const int split = blockIdx.x;
@@ -269,8 +271,13 @@ attn_block_paged_kernel(const AttnPagedArgs a) {
 }
 
 // Merge the nsplit partials of one (request, head, token) row; one warp per row.
+// Lanes first take one split each (running max and weighted sum across the
+// warp), then every lane accumulates its 4 output columns over the splits
+// with the weights broadcast by shuffle; the O loads are independent.
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     bf16* __restrict__ out, int bs, int block, int hq, int nsplit) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const int rows = bs * hq * block;
@@ -278,23 +285,38 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
   const int tok = warp_global % block;
   const int head = (warp_global / block) % hq;
   const int req = warp_global / (block * hq);
-  float mmax = -INFINITY;
-  for (int s = 0; s < nsplit; ++s) {
-    const int64_t p = ((static_cast<int64_t>(req) * nsplit + s) * hq + head) * block + tok;
-    mmax = fmaxf(mmax, part_ml[p * 2]);
-  }
+  const int64_t p0 = (static_cast<int64_t>(req) * nsplit * hq + head) * block + tok;   // split 0
+  const int64_t pstride = static_cast<int64_t>(hq) * block;                             // between splits
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  float mmax = -INFINITY;
+  for (int s0 = 0; s0 < nsplit; s0 += 32) {   // running max over all splits
+    const int s = s0 + lane;
+    const float ms = s < nsplit ? part_ml[(p0 + s * pstride) * 2] : -INFINITY;
+    mmax = fmaxf(mmax, ms);
+  }
+  mmax = warp_max(mmax);
   float lsum = 0.f;
   if (mmax != -INFINITY) {
-    for (int s = 0; s < nsplit; ++s) {
-      const int64_t p = ((static_cast<int64_t>(req) * nsplit + s) * hq + head) * block + tok;
-      const float ms = part_ml[p * 2];
-      if (ms == -INFINITY) continue;
-      const float w = exp2f(ms - mmax);
-      lsum += w * part_ml[p * 2 + 1];
-      const float4 v = *reinterpret_cast<const float4*>(part_o + p * kHeadDim + lane * 4);
-      acc[0] += w * v.x; acc[1] += w * v.y; acc[2] += w * v.z; acc[3] += w * v.w;
+    for (int s0 = 0; s0 < nsplit; s0 += 32) {
+      const int s = s0 + lane;
+      float w = 0.f, l = 0.f;
+      if (s < nsplit) {
+        const float2 ml = *reinterpret_cast<const float2*>(part_ml + (p0 + s * pstride) * 2);
+        w = ml.x == -INFINITY ? 0.f : exp2f(ml.x - mmax);
+        l = ml.y;
+      }
+      lsum += w * l;
+      const int cnt = min(32, nsplit - s0);
+#pragma unroll 4
+      for (int j = 0; j < cnt; ++j) {
+        const float wj = __shfl_sync(0xffffffffu, w, j);
+        if (wj != 0.f) {
+          const float4 v = *reinterpret_cast<const float4*>(part_o + (p0 + (s0 + j) * pstride) * kHeadDim + lane * 4);
+          acc[0] += wj * v.x; acc[1] += wj * v.y; acc[2] += wj * v.z; acc[3] += wj * v.w;
+        }
+      }
     }
+    lsum = warp_sum(lsum);
   }
   const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
   bf16* dst = out + ((static_cast<int64_t>(req) * block + tok) * hq + head) * kHeadDim + lane * 4;
@@ -309,6 +331,8 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(kAttnWarps * 32)
 attn_staircase_kernel(const AttnStairArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const uint32_t smem = smem_u32(smem_raw);
   const int seq = blockIdx.z;
@@ -454,15 +478,14 @@ int mdb_attn_block_paged(const void* q, const void* k_cache, const void* v_cache
   const int row_blocks = (rows_total + kAttnRows - 1) / kAttnRows;
   dim3 grid(nsplit, hkv * row_blocks, bs);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  attn_block_paged_kernel<<<grid, kAttnWarps * 32, kAttnSmemBytes, st>>>(a);
-  int rc = mdb_check_launch();
+  int rc = mdb_launch(attn_block_paged_kernel, grid, dim3(kAttnWarps * 32), kAttnSmemBytes, st, a);
   if (rc != MDB_OK) return rc;
   if (nsplit > 1) {
     const int rows = bs * hq * block;
     const int threads = 256;
     const int blocks = (rows * 32 + threads - 1) / threads;
-    attn_combine_kernel<<<blocks, threads, 0, st>>>(a.part_o, a.part_ml, a.out, bs, block, hq, nsplit);
-    rc = mdb_check_launch();
+    rc = mdb_launch(attn_combine_kernel, dim3(blocks), dim3(threads), 0, st, a.part_o, a.part_ml, a.out, bs, block, hq,
+                    nsplit);
   }
   return rc;
 }
@@ -506,8 +529,8 @@ int mdb_attn_staircase_varlen(const void* q, int64_t q_stride, const void* k, in
   a.log2_stairs = lg;
   a.q_scale = 1.0f / sqrtf(static_cast<float>(kHeadDim)) * 1.44269504f;
   dim3 grid((max_seqlen + kAttnRows - 1) / kAttnRows, hq, nseq);
-  attn_staircase_kernel<<<grid, kAttnWarps * 32, kAttnSmemBytes, static_cast<cudaStream_t>(stream)>>>(a);
-  return mdb_check_launch();
+  return mdb_launch(attn_staircase_kernel, grid, dim3(kAttnWarps * 32), kAttnSmemBytes,
+                    static_cast<cudaStream_t>(stream), a);
 }
 
 }  // extern "C"

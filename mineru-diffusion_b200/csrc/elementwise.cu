@@ -12,6 +12,8 @@ namespace mdb {
 __global__ void kv_commit_kernel(const bf16* __restrict__ key, int64_t key_stride, const bf16* __restrict__ value,
                                  int64_t value_stride, bf16* __restrict__ k_cache, bf16* __restrict__ v_cache,
                                  const int32_t* __restrict__ slot_mapping, int row_elems, int64_t num_slots) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int i = blockIdx.x;
   const int slot = slot_mapping[i];
   if (slot == -1) return;
@@ -40,6 +42,8 @@ __global__ void __launch_bounds__(kNormThreads)
 add_rmsnorm_kernel(const bf16* __restrict__ x, const float* __restrict__ partials, int nparts,
                    const bf16* __restrict__ residual_in, const bf16* __restrict__ weight, float eps,
                    bf16* __restrict__ y_out, bf16* __restrict__ residual_out, int m, int h) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x;
   const int chunks = h >> 3;
   const int64_t row_off = static_cast<int64_t>(row) * h;
@@ -135,6 +139,8 @@ qknorm_rope_commit_kernel(const bf16* __restrict__ qkv, int64_t ld_qkv, const fl
                           const int32_t* __restrict__ slot_mapping, bf16* __restrict__ q_out,
                           bf16* __restrict__ k_out, bf16* __restrict__ v_out, bf16* __restrict__ k_cache,
                           bf16* __restrict__ v_cache, int64_t num_slots, int m, int hq, int hkv) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int token = blockIdx.x;
   const int head = blockIdx.y * kRopeWarps + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -229,6 +235,8 @@ __device__ __forceinline__ float silu_mul_bf16(float g, float u) {
 
 __global__ void silu_mul_kernel(const bf16* __restrict__ gate_up, int64_t ld_in, bf16* __restrict__ act,
                                 int64_t ld_act, int m, int inter) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int chunks = inter >> 3;
   const int64_t total = static_cast<int64_t>(m) * chunks;
   for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
@@ -256,6 +264,8 @@ __global__ void silu_mul_kernel(const bf16* __restrict__ gate_up, int64_t ld_in,
 // ---------------------------------------------------------------------------
 __global__ void gather_rows_kernel(const bf16* __restrict__ table, int64_t num_rows, const int64_t* __restrict__ ids,
                                    bf16* __restrict__ out, int h) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int i = blockIdx.x;
   const int64_t id = ids[i];
   const int chunks = h >> 3;
@@ -287,7 +297,23 @@ const char* mdb_strerror(int code) {
   }
 }
 
-int mdb_version(void) { return 100; }
+int mdb_version(void) { return 101; }
+
+int mdb_set_option(int option, int value) {
+  switch (option) {
+    case MDB_OPT_STREAM_KERNEL: g_opt_stream_kernel = value ? 1 : 0; return MDB_OK;
+    case MDB_OPT_PDL: g_opt_pdl = value ? 1 : 0; return MDB_OK;
+    default: return MDB_ERR_ARG;
+  }
+}
+
+int mdb_get_option(int option) {
+  switch (option) {
+    case MDB_OPT_STREAM_KERNEL: return g_opt_stream_kernel;
+    case MDB_OPT_PDL: return g_opt_pdl;
+    default: return MDB_ERR_ARG;
+  }
+}
 
 int mdb_last_device_status(unsigned int* out, int clear) {
   MDB_REQUIRE(out != nullptr, MDB_ERR_ARG);
@@ -312,10 +338,9 @@ int mdb_kv_commit(const void* key, int64_t key_stride, const void* value, int64_
   MDB_REQUIRE(mdb_aligned16(key) && mdb_aligned16(value) && mdb_aligned16(k_cache) && mdb_aligned16(v_cache),
               MDB_ERR_ALIGN);
   const int threads = row_elems / 8 >= 128 ? 128 : 64;
-  kv_commit_kernel<<<n_tokens, threads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const bf16*>(key), key_stride, static_cast<const bf16*>(value), value_stride,
-      static_cast<bf16*>(k_cache), static_cast<bf16*>(v_cache), slot_mapping, row_elems, num_slots);
-  return mdb_check_launch();
+  return mdb_launch(kv_commit_kernel, dim3(n_tokens), dim3(threads), 0, static_cast<cudaStream_t>(stream),
+                    static_cast<const bf16*>(key), key_stride, static_cast<const bf16*>(value), value_stride,
+                    static_cast<bf16*>(k_cache), static_cast<bf16*>(v_cache), slot_mapping, row_elems, num_slots);
 }
 
 int mdb_add_rmsnorm(const void* x, const float* partials, int nparts, const void* residual_in, const void* weight,
@@ -329,10 +354,10 @@ int mdb_add_rmsnorm(const void* x, const float* partials, int nparts, const void
   MDB_REQUIRE(mdb_aligned16(x) && mdb_aligned16(partials) && mdb_aligned16(residual_in) && mdb_aligned16(weight) &&
                   mdb_aligned16(y_out) && mdb_aligned16(residual_out),
               MDB_ERR_ALIGN);
-  add_rmsnorm_kernel<<<m, kNormThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const bf16*>(x), partials, nparts, static_cast<const bf16*>(residual_in),
-      static_cast<const bf16*>(weight), eps, static_cast<bf16*>(y_out), static_cast<bf16*>(residual_out), m, h);
-  return mdb_check_launch();
+  return mdb_launch(add_rmsnorm_kernel, dim3(m), dim3(kNormThreads), 0, static_cast<cudaStream_t>(stream),
+                    static_cast<const bf16*>(x), partials, nparts, static_cast<const bf16*>(residual_in),
+                    static_cast<const bf16*>(weight), eps, static_cast<bf16*>(y_out),
+                    static_cast<bf16*>(residual_out), m, h);
 }
 
 int mdb_qknorm_rope_commit(const void* qkv, int64_t ld_qkv, const float* partials, int nparts,
@@ -354,12 +379,11 @@ int mdb_qknorm_rope_commit(const void* qkv, int64_t ld_qkv, const float* partial
               MDB_ERR_ALIGN);
   const int nheads = hq + 2 * hkv;
   dim3 grid(m, (nheads + kRopeWarps - 1) / kRopeWarps);
-  qknorm_rope_commit_kernel<<<grid, kRopeWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const bf16*>(qkv), ld_qkv, partials, nparts, positions, rope_table, max_pos,
-      static_cast<const bf16*>(q_norm_w), static_cast<const bf16*>(k_norm_w), eps, slot_mapping,
-      static_cast<bf16*>(q_out), static_cast<bf16*>(k_out), static_cast<bf16*>(v_out), static_cast<bf16*>(k_cache),
-      static_cast<bf16*>(v_cache), num_slots, m, hq, hkv);
-  return mdb_check_launch();
+  return mdb_launch(qknorm_rope_commit_kernel, grid, dim3(kRopeWarps * 32), 0, static_cast<cudaStream_t>(stream),
+                    static_cast<const bf16*>(qkv), ld_qkv, partials, nparts, positions, rope_table, max_pos,
+                    static_cast<const bf16*>(q_norm_w), static_cast<const bf16*>(k_norm_w), eps, slot_mapping,
+                    static_cast<bf16*>(q_out), static_cast<bf16*>(k_out), static_cast<bf16*>(v_out),
+                    static_cast<bf16*>(k_cache), static_cast<bf16*>(v_cache), num_slots, m, hq, hkv);
 }
 
 int mdb_silu_mul(const void* gate_up, int64_t ld_in, void* act, int64_t ld_act, int m, int inter,
@@ -373,9 +397,8 @@ int mdb_silu_mul(const void* gate_up, int64_t ld_in, void* act, int64_t ld_act, 
   const int64_t total = static_cast<int64_t>(m) * (inter / 8);
   int blocks = static_cast<int>((total + 255) / 256);
   if (blocks > 148 * 8) blocks = 148 * 8;
-  silu_mul_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const bf16*>(gate_up), ld_in, static_cast<bf16*>(act), ld_act, m, inter);
-  return mdb_check_launch();
+  return mdb_launch(silu_mul_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                    static_cast<const bf16*>(gate_up), ld_in, static_cast<bf16*>(act), ld_act, m, inter);
 }
 
 int mdb_gather_rows(const void* table, int64_t num_rows, const int64_t* ids, void* out, int m, int h,
@@ -385,9 +408,8 @@ int mdb_gather_rows(const void* table, int64_t num_rows, const int64_t* ids, voi
   MDB_REQUIRE(table && ids && out, MDB_ERR_ARG);
   MDB_REQUIRE(h % 8 == 0, MDB_ERR_UNSUPPORTED);
   MDB_REQUIRE(mdb_aligned16(table) && mdb_aligned16(out), MDB_ERR_ALIGN);
-  gather_rows_kernel<<<m, 128, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const bf16*>(table), num_rows, ids,
-                                                                     static_cast<bf16*>(out), h);
-  return mdb_check_launch();
+  return mdb_launch(gather_rows_kernel, dim3(m), dim3(128), 0, static_cast<cudaStream_t>(stream),
+                    static_cast<const bf16*>(table), num_rows, ids, static_cast<bf16*>(out), h);
 }
 
 }  // extern "C"

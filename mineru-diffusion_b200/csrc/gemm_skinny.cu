@@ -51,6 +51,8 @@ struct SkinnyArgs {
 template <int MT, int NT, int EPI>
 __global__ void __launch_bounds__(kSkinnyThreads)
 gemm_skinny_kernel(const SkinnyArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int ROWS = MT * 16;  // activation rows (padded)
   constexpr int COLS = NT * 8;   // weight rows of this CTA
   // dynamic shared memory: red[8 warps][ROWS][COLS + 4] then tile[ROWS][COLS + 1]
@@ -199,40 +201,55 @@ gemm_skinny_kernel(const SkinnyArgs a) {
 }
 
 // ---------------------------------------------------------------------------
-// sampler partial merge: one warp per row over P partial records
+// sampler partial merge: one CTA per row over P partial records
 // ---------------------------------------------------------------------------
-__global__ void sampler_finalize_kernel(const float4* __restrict__ part_f, const int* __restrict__ part_i, int nparts,
-                                        int m, int32_t* __restrict__ x0_out, float* __restrict__ conf_out) {
-  const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (row >= m) return;
-  float mx = -INFINITY, se = 0.f, bv = -INFINITY, bl = 0.f;
-  int bi = 0x7fffffff;
-  for (int p = lane; p < nparts; p += 32) {
+struct SampleRec {
+  float mx, se, bv, bl;
+  int bi;
+};
+
+__device__ __forceinline__ void merge_rec(SampleRec& a, const SampleRec& b) {
+  const float nm = fmaxf(a.mx, b.mx);
+  const float sa = (a.mx == -INFINITY) ? 0.f : a.se * expf(a.mx - nm);
+  const float sb = (b.mx == -INFINITY) ? 0.f : b.se * expf(b.mx - nm);
+  a.se = sa + sb;
+  a.mx = nm;
+  if (b.bv > a.bv || (b.bv == a.bv && b.bi < a.bi)) { a.bv = b.bv; a.bl = b.bl; a.bi = b.bi; }
+}
+
+constexpr int kFinalizeThreads = 256;
+
+__global__ void __launch_bounds__(kFinalizeThreads)
+sampler_finalize_kernel(const float4* __restrict__ part_f, const int* __restrict__ part_i, int nparts, int m,
+                        int32_t* __restrict__ x0_out, float* __restrict__ conf_out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  SampleRec r = {-INFINITY, 0.f, -INFINITY, 0.f, 0x7fffffff};
+  for (int p = threadIdx.x; p < nparts; p += kFinalizeThreads) {
     const float4 f = part_f[static_cast<int64_t>(p) * m + row];
-    const int i = part_i[static_cast<int64_t>(p) * m + row];
-    const float nm = fmaxf(mx, f.x);
-    se = se * expf(mx - nm) + f.y * expf(f.x - nm);
-    mx = nm;
-    if (f.z > bv || (f.z == bv && i < bi)) { bv = f.z; bl = f.w; bi = i; }
+    const SampleRec o = {f.x, f.y, f.z, f.w, part_i[static_cast<int64_t>(p) * m + row]};
+    merge_rec(r, o);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
-    const float omx = __shfl_xor_sync(0xffffffffu, mx, o);
-    const float ose = __shfl_xor_sync(0xffffffffu, se, o);
-    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-    const float ol = __shfl_xor_sync(0xffffffffu, bl, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    const float nm = fmaxf(mx, omx);
-    const float sa = (mx == -INFINITY) ? 0.f : se * expf(mx - nm);
-    const float sb = (omx == -INFINITY) ? 0.f : ose * expf(omx - nm);
-    se = sa + sb;
-    mx = nm;
-    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bl = ol; bi = oi; }
+    SampleRec t;
+    t.mx = __shfl_xor_sync(0xffffffffu, r.mx, o);
+    t.se = __shfl_xor_sync(0xffffffffu, r.se, o);
+    t.bv = __shfl_xor_sync(0xffffffffu, r.bv, o);
+    t.bl = __shfl_xor_sync(0xffffffffu, r.bl, o);
+    t.bi = __shfl_xor_sync(0xffffffffu, r.bi, o);
+    merge_rec(r, t);
   }
-  if (lane == 0) {
-    x0_out[row] = bi;
-    conf_out[row] = expf(bl - mx) / se;
+  __shared__ SampleRec sh[kFinalizeThreads / 32];
+  if (lane == 0) sh[warp] = r;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    SampleRec t = sh[0];
+    for (int w = 1; w < kFinalizeThreads / 32; ++w) merge_rec(t, sh[w]);
+    x0_out[row] = t.bi;
+    conf_out[row] = expf(t.bl - t.mx) / t.se;
   }
 }
 
@@ -243,6 +260,8 @@ __global__ void __launch_bounds__(256)
 logits_scan_kernel(const bf16* __restrict__ logits, int64_t ld, int m, int vocab, const float* __restrict__ temperatures,
                    int block, int noise_mode, const float* __restrict__ noise, uint32_t seed, uint32_t step_base,
                    const uint32_t* __restrict__ step_dev, float4* __restrict__ part_f, int* __restrict__ part_i) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.y;
   const uint32_t step = step_base + (step_dev != nullptr ? *step_dev : 0u);
   const int c_begin = blockIdx.x * kScanCols;
@@ -286,6 +305,8 @@ logits_scan_kernel(const bf16* __restrict__ logits, int64_t ld, int m, int vocab
 }
 
 __global__ void gumbel_noise_kernel(float* __restrict__ out, int m, int vocab, uint32_t seed, uint32_t step) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t total = static_cast<int64_t>(m) * vocab;
   for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
        idx += static_cast<int64_t>(gridDim.x) * blockDim.x)
@@ -296,6 +317,8 @@ __global__ void gumbel_noise_kernel(float* __restrict__ out, int m, int vocab, u
 __global__ void unmask_decide_kernel(int64_t* __restrict__ block_ids, const int32_t* __restrict__ x0,
                                      const float* __restrict__ conf, int block, int64_t mask_id, float threshold,
                                      int quota, uint8_t* __restrict__ transfer_out, int32_t* __restrict__ count_out) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float sconf[128];
   const int req = blockIdx.x;
   const int i = threadIdx.x;
@@ -358,8 +381,7 @@ int launch_skinny_inst(const SkinnyArgs& a, int ksplit, cudaStream_t st) {
   const int cols = (EPI == kEpiSwiglu) ? a.inter : a.n;
   const int per_cta = (EPI == kEpiSwiglu) ? COLS / 2 : COLS;
   dim3 grid(cols / per_cta, ksplit);
-  gemm_skinny_kernel<MT, NT, EPI><<<grid, kSkinnyThreads, smem, st>>>(a);
-  return mdb_check_launch();
+  return mdb_launch(gemm_skinny_kernel<MT, NT, EPI>, grid, dim3(kSkinnyThreads), smem, st, a);
 }
 
 template <int EPI>
@@ -386,48 +408,6 @@ int check_skinny_common(const void* x, int64_t ldx, const void* w, int m, int n,
 
 extern "C" {
 
-int64_t mdb_gemm_splitk_workspace_bytes(int m, int n, int ksplit) {
-  if (m <= 0 || n <= 0 || ksplit <= 0) return 0;
-  return static_cast<int64_t>(ksplit) * m * n * 4;
-}
-
-int mdb_gemm_splitk_partials(const void* x, int64_t ldx, const void* w, float* partials, int m, int n, int k,
-                             int ksplit, mdb_stream_t stream) {
-  if (m == 0) return MDB_OK;
-  int rc = check_skinny_common(x, ldx, w, m, n, k);
-  if (rc != MDB_OK) return rc;
-  MDB_REQUIRE(partials != nullptr && ksplit >= 1 && ksplit <= 64, MDB_ERR_ARG);
-  MDB_REQUIRE(mdb_aligned16(partials), MDB_ERR_ALIGN);
-  // every slice must be non-empty so that each partial row is written
-  MDB_REQUIRE(static_cast<int64_t>(skinny_k_per_cta(k, ksplit)) * (ksplit - 1) < k, MDB_ERR_ARG);
-  SkinnyArgs a = {};
-  a.x = static_cast<const bf16*>(x);
-  a.w = static_cast<const bf16*>(w);
-  a.ldx = ldx;
-  a.m = m; a.n = n; a.k = k;
-  a.partials = partials;
-  return launch_skinny<kEpiPartial>(a, ksplit, static_cast<cudaStream_t>(stream));
-}
-
-int mdb_gemm_gateup_swiglu(const void* x, int64_t ldx, const void* w_gate_up, void* act, int64_t ld_act, int m,
-                           int inter, int k, mdb_stream_t stream) {
-  if (m == 0) return MDB_OK;
-  int rc = check_skinny_common(x, ldx, w_gate_up, m, 2 * inter, k);
-  if (rc != MDB_OK) return rc;
-  MDB_REQUIRE(act != nullptr && ld_act >= inter, MDB_ERR_ARG);
-  MDB_REQUIRE(inter % 16 == 0, MDB_ERR_UNSUPPORTED);
-  MDB_REQUIRE(ld_act % 2 == 0 && mdb_aligned16(act), MDB_ERR_ALIGN);
-  SkinnyArgs a = {};
-  a.x = static_cast<const bf16*>(x);
-  a.w = static_cast<const bf16*>(w_gate_up);
-  a.ldx = ldx;
-  a.m = m; a.n = 2 * inter; a.k = k;
-  a.y = static_cast<bf16*>(act);
-  a.ldy = ld_act;
-  a.inter = inter;
-  return launch_skinny<kEpiSwiglu>(a, 1, static_cast<cudaStream_t>(stream));
-}
-
 int mdb_gumbel_noise(float* out, int m, int vocab, uint32_t seed, uint32_t step, mdb_stream_t stream) {
   MDB_REQUIRE(m >= 0 && vocab > 0, MDB_ERR_ARG);
   if (m == 0) return MDB_OK;
@@ -435,8 +415,8 @@ int mdb_gumbel_noise(float* out, int m, int vocab, uint32_t seed, uint32_t step,
   const int64_t total = static_cast<int64_t>(m) * vocab;
   int blocks = static_cast<int>((total + 255) / 256);
   if (blocks > 148 * 8) blocks = 148 * 8;
-  gumbel_noise_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(out, m, vocab, seed, step);
-  return mdb_check_launch();
+  return mdb_launch(gumbel_noise_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream), out, m, vocab,
+                    seed, step);
 }
 
 int mdb_unmask_decide(int64_t* block_ids, const int32_t* x0, const float* conf, int bs, int block, int64_t mask_id,
@@ -446,9 +426,8 @@ int mdb_unmask_decide(int64_t* block_ids, const int32_t* x0, const float* conf, 
   MDB_REQUIRE(block_ids && x0 && conf && transfer_out && count_out, MDB_ERR_ARG);
   MDB_REQUIRE(block <= 128, MDB_ERR_UNSUPPORTED);
   const int threads = block <= 32 ? 32 : (block <= 64 ? 64 : 128);
-  unmask_decide_kernel<<<bs, threads, 0, static_cast<cudaStream_t>(stream)>>>(block_ids, x0, conf, block, mask_id,
-                                                                             threshold, quota, transfer_out, count_out);
-  return mdb_check_launch();
+  return mdb_launch(unmask_decide_kernel, dim3(bs), dim3(threads), 0, static_cast<cudaStream_t>(stream), block_ids, x0,
+                    conf, block, mask_id, threshold, quota, transfer_out, count_out);
 }
 
 }  // extern "C"

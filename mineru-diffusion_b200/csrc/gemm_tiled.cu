@@ -16,6 +16,8 @@ constexpr int kGemmSmemBytes = kGemmStages * 2 * kGemmTileBytes;        // 96 KB
 __global__ void __launch_bounds__(kGemmThreads)
 gemm_tiled_kernel(const bf16* __restrict__ x, int64_t ldx, const bf16* __restrict__ w, bf16* __restrict__ y,
                   int64_t ldy, int m, int n, int k) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const uint32_t smem = smem_u32(smem_raw);
   const int m0 = blockIdx.y * kGemmBM, n0 = blockIdx.x * kGemmBN;
@@ -111,8 +113,7 @@ int launch_gemm_tiled(const bf16* x, int64_t ldx, const bf16* w, bf16* y, int64_
     attr_set = true;
   }
   dim3 grid((n + kGemmBN - 1) / kGemmBN, (m + kGemmBM - 1) / kGemmBM);
-  gemm_tiled_kernel<<<grid, kGemmThreads, kGemmSmemBytes, st>>>(x, ldx, w, y, ldy, m, n, k);
-  return mdb_check_launch();
+  return mdb_launch(gemm_tiled_kernel, grid, dim3(kGemmThreads), kGemmSmemBytes, st, x, ldx, w, y, ldy, m, n, k);
 }
 
 }  // namespace mdb

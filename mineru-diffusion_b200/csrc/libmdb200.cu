@@ -4,5 +4,6 @@
 #include "elementwise.cu"
 #include "attention.cu"
 #include "gemm_skinny.cu"
+#include "gemm_ws.cu"
 #include "gemm_tiled.cu"
 #include "api_linear.cu"

@@ -22,6 +22,14 @@ __device__ unsigned int g_device_status = 0;  // one definition: the library is 
 
 __device__ __forceinline__ void report_status(unsigned int bit) { atomicOr(&g_device_status, bit); }
 
+// ---- programmatic dependent launch ---------------------------------------------
+// Every kernel of the library opens with pdl_launch_dependents() (the next
+// kernel in the stream may be scheduled early, e.g. to prefetch weights) and
+// calls pdl_wait() before it touches memory an earlier kernel may still write
+// or read.  Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- small numeric helpers ------------------------------------------------
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
@@ -133,6 +141,27 @@ __device__ __forceinline__ float gumbel_noise(uint32_t seed, uint32_t step, uint
   } while (0)
 
 static inline bool mdb_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// process-wide options (mdb_set_option)
+static int g_opt_stream_kernel = 0;   // 0: tcgen05/TMA streaming kernel where possible, 1: register-streaming kernel
+static int g_opt_pdl = 1;             // programmatic dependent launch between the library's kernels
+
+// Launch with the programmatic-stream-serialization attribute when enabled.
+template <typename... KArgs, typename... Args>
+static inline int mdb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                             Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_opt_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...) == cudaSuccess ? MDB_OK : MDB_ERR_CUDA;
+}
 
 static inline int mdb_check_launch() {
   cudaError_t e = cudaGetLastError();

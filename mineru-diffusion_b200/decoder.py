@@ -95,19 +95,6 @@ def rope_table(max_pos: int, head_dim: int, base: float, device) -> torch.Tensor
     return torch.cat((freqs.cos(), freqs.sin()), dim=-1).contiguous().to(device)
 
 
-def pick_ksplit(n: int, k: int, rows: int) -> int:
-    """Split-k factor of a weight-streaming GEMM: enough CTAs to cover the SMs
-    about twice, every slice a whole multiple of 256 columns."""
-    cols_per_cta = 32 if rows <= 32 else 16
-    ctas = max(1, n // cols_per_cta)
-    want = max(1, -(-256 // ctas))
-    most = max(1, k // 256)
-    s = min(want, most, 16)
-    while s > 1 and (-(-k // s) + 255) // 256 * 256 * (s - 1) >= k:
-        s -= 1
-    return s
-
-
 class DecoderEngine:
 
     def __init__(self, cfg: DecoderConfig, weights: DecoderWeights, kv_cache: torch.Tensor, max_tokens: int,
@@ -146,9 +133,9 @@ class DecoderEngine:
         self.lm_rows = buf(max_seqs * block_size, h)
         # weight-streaming path: fp32 split-k slices shared by all four GEMMs
         rows = min(t, SKINNY_MAX_ROWS)
-        self.ks_qkv = pick_ksplit(self.nqkv, h, rows)
-        self.ks_o = pick_ksplit(h, hq * d, rows)
-        self.ks_down = pick_ksplit(h, i, rows)
+        self.ks_qkv = ops.pick_ksplit(rows, self.nqkv, h)
+        self.ks_o = ops.pick_ksplit(rows, h, hq * d)
+        self.ks_down = ops.pick_ksplit(rows, h, i)
         part_elems = rows * max(self.ks_qkv * self.nqkv, self.ks_o * h, self.ks_down * h)
         self.partials = buf(part_elems, dtype=torch.float32)
         # tiled path: materialised bf16 GEMM outputs

@@ -24,6 +24,7 @@ from ..decoder import DecoderEngine, DecoderWeights
 from .config import Config
 from .context import Context
 from .sequence import Sequence
+from .step_inputs import build_decode_inputs, build_prefill_inputs
 
 
 def _round_up(v: int, a: int) -> int:
@@ -119,6 +120,7 @@ class ModelRunner:
         self.graph_bs: list[int] = []
         self.last: dict = {}
         self.keep_last = False        # tests: keep x0 / confidence / hidden of the last step
+        self.step_events = None       # benchmark: (start, end) CUDA events around the GPU work of a step
         if not self.enforce_eager:
             self.capture_cudagraph()
 
@@ -149,55 +151,38 @@ class ModelRunner:
                                     d.num_key_value_heads, d.head_dim, dtype=torch.bfloat16, device=self.device)
 
     # ------------------------------------------------------------------ host -> step tensors
-    def prepare_block_tables(self, seqs: list[Sequence]) -> list[list[int]]:
-        width = max(len(seq.block_table) for seq in seqs)
-        return [seq.block_table + [-1] * (width - len(seq.block_table)) for seq in seqs]
-
     def prepare_prefill(self, seqs: list[Sequence]):
-        b = self.block_size
-        ids: list[int] = []
-        pos: list[int] = []
-        slots: list[int] = []
-        cu = [0]
-        max_len = 0
-        for seq in seqs:
-            seqlen = len(seq) + b
-            ids.extend(seq[seq.num_cached_tokens:] + seq.current_denoising_block.tolist())
-            pos.extend(range(seq.num_cached_tokens, seqlen))
-            cu.append(cu[-1] + seqlen - seq.num_cached_tokens)
-            max_len = max(max_len, seqlen)
-            if not seq.block_table:     # warm-up sequences hold no pages
-                continue
-            slots.extend(seq.get_slots(seq.num_cached_tokens, len(seq)) + [-1] * b)
+        inp = build_prefill_inputs(seqs, self.block_size)
         dev = self.device
-        input_ids = torch.tensor(ids, dtype=torch.int64, pin_memory=True).to(dev, non_blocking=True)
-        positions = torch.tensor(pos, dtype=torch.int64, pin_memory=True).to(dev, non_blocking=True)
-        cu_q = torch.tensor(cu, dtype=torch.int32, pin_memory=True).to(dev, non_blocking=True)
-        slot_mapping = torch.tensor(slots, dtype=torch.int32, pin_memory=True).to(dev, non_blocking=True)
-        ctx = Context(True, cu_q, cu_q, max_len, max_len, slot_mapping, None, None, b)
-        return input_ids, positions, ctx, cu
+
+        def up(a):
+            return torch.from_numpy(a).pin_memory().to(dev, non_blocking=True)
+
+        cu_q = up(inp["cu_seqlens"])
+        ctx = Context(True, cu_q, cu_q, inp["max_seqlen"], inp["max_seqlen"], up(inp["slot_mapping"]), None, None,
+                      self.block_size)
+        return up(inp["input_ids"]), up(inp["positions"]), ctx, inp["cu_seqlens"].tolist()
 
     def prepare_decode(self, seqs: list[Sequence]):
-        """Fills the packed pinned buffer; returns the device views of a step."""
+        """Fills the packed pinned buffer and starts its copy; returns the longest context."""
         b, bs = self.block_size, len(seqs)
-        tables = self.prepare_block_tables(seqs)
-        width = len(tables[0])
+        inp = build_decode_inputs(seqs, b)
+        width = inp["block_tables"].shape[1]
         if width > self.max_pages:
             raise AssertionError("page table wider than max_model_len allows")
         hn = self.hn
         hn["slots"].fill(-1)
         hn["ctx"].fill(0)
-        hn["tab"][:bs, :width] = np.asarray(tables, dtype=np.int32)
+        hn["ids"][:bs] = inp["input_ids"]
+        hn["pos"][:bs] = inp["positions"]
+        hn["slots"][:bs] = inp["slot_mapping"]
+        hn["ctx"][:bs] = inp["context_lens"]
+        hn["tab"][:bs, :width] = inp["block_tables"]
         for i, seq in enumerate(seqs):
-            n = len(seq)
-            hn["ids"][i] = seq.current_denoising_block.numpy()
-            hn["pos"][i] = np.arange(n, n + b, dtype=np.int64)
-            hn["slots"][i] = seq.get_slots(n, n + b)
-            hn["ctx"][i] = n + b
             hn["temp"][i] = seq.temperature
         hn["step"][0] = self.step_index
         self.inputs.dev.copy_(self.inputs.host, non_blocking=True)
-        return max(len(seq) for seq in seqs) + b
+        return int(inp["context_lens"].max())
 
     def prepare_sample(self, seqs: list[Sequence]) -> torch.Tensor:
         t = torch.tensor([seq.temperature for seq in seqs], dtype=torch.float32, pin_memory=True)
@@ -233,6 +218,8 @@ class ModelRunner:
     def run_model_decode(self, seqs: list[Sequence]):
         bs = len(seqs)
         max_ctx = self.prepare_decode(seqs)
+        if self.step_events is not None:
+            self.step_events[0].record()      # inputs are resident from here on
         use_graph = (not self.enforce_eager) and self.noise != "explicit" and bs <= self.max_bs and self.graph_bs
         if use_graph:
             gbs = next(x for x in self.graph_bs if x >= bs)
@@ -268,7 +255,11 @@ class ModelRunner:
         bs, b = len(seqs), self.block_size
         if bs > self.max_bs:
             raise AssertionError("batch larger than max_num_seqs")
-        hidden = self.run_model_prefill(seqs) if is_prefill else self.run_model_decode(seqs)
+        if is_prefill:
+            hidden = self.run_model_prefill(seqs)
+        else:
+            self.run_model_decode(seqs)
+            hidden = self.engine.final[:bs * b]     # final-norm rows of the step (graph replays write here too)
         with torch.inference_mode():
             # sampler state: the host copy of each block is the source of truth, as in the reference
             for i, seq in enumerate(seqs):
@@ -283,6 +274,8 @@ class ModelRunner:
             m = bs * b
             ops.unmask_decide(self.block_ids[:bs], self.engine.x0[:m], self.engine.conf[:m], seqs[0].mask_token_id,
                               sp.dynamic_threshold, quota, transfer=self.transfer[:bs], counts=self.counts[:bs])
+            if self.step_events is not None and not is_prefill:
+                self.step_events[1].record()
             self.h_block_ids[:bs].copy_(self.block_ids[:bs], non_blocking=True)
             self.h_transfer[:bs].copy_(self.transfer[:bs], non_blocking=True)
             self.h_counts[:bs].copy_(self.counts[:bs], non_blocking=True)
@@ -299,6 +292,19 @@ class ModelRunner:
             total += int(self.h_counts[i])
         self.step_index += 1
         return total
+
+    def launches_per_decode_step(self, bs: int = 1) -> int:
+        """Kernels of libmdb200 launched by one decode-form step: row gather,
+        per layer 2 norms + 4 GEMMs + q/k norm-rope-store + attention (+ merge
+        of the key-range splits), final norm, LM-head scan + merge, unmask rule."""
+        if self.graph_bs:
+            nsplit = self.graphs[next(x for x in self.graph_bs if x >= bs)][1]
+        else:
+            nsplit = self.engine.attn_nsplit(bs, self.config.max_model_len)
+        per_layer = 8 + (1 if nsplit > 1 else 0)
+        if bs * self.block_size > 64:
+            per_layer += 1      # stand-alone SiLU*mul on the tiled path
+        return 1 + self.dcfg.num_hidden_layers * per_layer + 1 + 2 + 1
 
     # ------------------------------------------------------------------ CUDA graphs
     @torch.inference_mode()

@@ -37,6 +37,23 @@ def _rows(t: torch.Tensor, name: str) -> int:
     return t.stride(0)
 
 
+OPT_STREAM_KERNEL = 0   # 0: tcgen05/TMA streaming kernel for short steps (default), 1: register-streaming kernel
+OPT_PDL = 1             # programmatic dependent launch between kernels (default on)
+
+
+def set_option(option: int, value: int) -> None:
+    _lib.check(_lib.lib().mdb_set_option(option, value), "mdb_set_option")
+
+
+def get_option(option: int) -> int:
+    return int(_lib.lib().mdb_get_option(option))
+
+
+def pick_ksplit(m: int, n: int, k: int) -> int:
+    """Split-k factor suited to the kernel that (m, n, k) will run on."""
+    return int(_lib.lib().mdb_gemm_pick_ksplit(m, n, k))
+
+
 # --------------------------------------------------------------------------
 def store_kvcache(key: torch.Tensor, value: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                   slot_mapping: torch.Tensor) -> None:
@@ -64,12 +81,13 @@ def store_kvcache(key: torch.Tensor, value: torch.Tensor, k_cache: torch.Tensor,
 
 
 def default_nsplit(bs: int, block: int, hq: int, hkv: int, max_ctx: int) -> int:
-    """Key-range splits per request so that a step fills the 148 SMs about twice."""
+    """Key-range splits per request: enough CTAs to cover the 148 SMs about
+    twice, but never parts shorter than 256 keys (four tiles)."""
     row_blocks = -(-(hq // hkv) * block // 64)
     ctas = max(1, bs * hkv * row_blocks)
     want = -(-2 * 148 // ctas)
-    tiles = max(1, -(-max_ctx // 64))
-    return int(max(1, min(want, tiles, 64)))
+    parts = max(1, max_ctx // 256)
+    return int(max(1, min(want, parts, 32)))
 
 
 def block_attn_with_kvcache(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,

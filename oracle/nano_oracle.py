@@ -497,3 +497,26 @@ class OracleModelRunner:
                          input_ids=ids, positions=pos)
         self.step_index += 1
         return int(transfer.sum())
+
+
+# --------------------------------------------------------------------------
+# timing aid for the CPU baseline
+# --------------------------------------------------------------------------
+_NATIVE_LINEAR = False
+
+
+def use_native_linear(flag: bool) -> None:
+    """Parity tests keep the fp32 restatement of ``linear``.  The CPU baseline
+    of the benchmark switches to ``torch.nn.functional.linear`` on the storage
+    dtype, which is the call the reference itself makes on a CPU
+    (NV/layers/linear.py:73,154), so that the timed work is the reference's."""
+    global _NATIVE_LINEAR, linear
+    _NATIVE_LINEAR = flag
+    if flag:
+        import torch.nn.functional as F
+        linear = lambda x, w: F.linear(x, w)  # noqa: E731
+    else:
+        linear = _linear_fp32
+
+
+_linear_fp32 = linear

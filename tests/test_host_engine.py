@@ -1,0 +1,111 @@
+"""Host-side mirror of the reference's scheduler / sequence / page allocator and
+the step-input builders, replayed against tensors recorded from the reference
+(tests/golden/index_contract.npz).  Integer contracts: bit-exact."""
+import itertools
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import load_golden
+
+
+def _replay(mdb, g):
+    from types import SimpleNamespace
+    eng = mdb.engine
+    B, MASK = 32, 151669
+    cfg = SimpleNamespace(max_num_seqs=4, max_num_batched_tokens=4096, eos=-1, num_kvcache_blocks=12,
+                          kvcache_block_size=256)
+    sched = mdb.Scheduler(cfg)
+    mdb.Sequence.counter = itertools.count()
+    gen = torch.Generator().manual_seed(11)
+    for pl, mn in zip(g["prompt_lens"].tolist(), g["max_new"].tolist()):
+        ids = torch.randint(0, 150000, (pl,), generator=gen).tolist()
+        sp = mdb.SamplingParams(temperature=1.0, max_new_tokens=mn, ignore_eos=True, stop_token_ids=[])
+        sched.add(mdb.Sequence(ids, sp, denoising_block_size=B, mask_token_id=MASK))
+    from importlib import import_module
+    si = import_module("mineru-diffusion_b200.engine.step_inputs")
+    nsteps = int(g["num_steps"])
+    kinds = set()
+    for step in range(nsteps):
+        p = f"s{step:03d}_"
+        seqs, is_prefill = sched.schedule()
+        assert int(is_prefill) == int(g[p + "is_prefill"]), step
+        assert [s.seq_id for s in seqs] == g[p + "seq_ids"].tolist()
+        if is_prefill:
+            inp = si.build_prefill_inputs(seqs, B)
+            assert np.array_equal(inp["input_ids"], g[p + "input_ids"])
+            assert np.array_equal(inp["positions"], g[p + "positions"])
+            assert np.array_equal(inp["slot_mapping"], g[p + "slot_mapping"])
+            assert np.array_equal(inp["cu_seqlens"], g[p + "cu_seqlens_q"])
+            assert np.array_equal(inp["cu_seqlens"], g[p + "cu_seqlens_k"])
+        else:
+            inp = si.build_decode_inputs(seqs, B)
+            for ours, theirs in (("input_ids", "input_ids"), ("positions", "positions"),
+                                 ("slot_mapping", "slot_mapping"), ("context_lens", "context_lens"),
+                                 ("block_tables", "block_tables")):
+                assert np.array_equal(inp[ours], g[p + theirs]), (step, ours)
+                assert inp[ours].dtype == g[p + theirs].dtype
+            if (inp["slot_mapping"][:, 0] // 256 != inp["slot_mapping"][:, -1] // 256).any():
+                kinds.add("straddle")
+        # apply the recorded sampler outcome, then the scheduler's own post-processing
+        for s, row in zip(seqs, g[p + "blocks_after"]):
+            s.current_denoising_block = torch.from_numpy(row.copy())
+        sched.postprocess(seqs)
+        assert [s.status.value for s in seqs] == g[p + "status_after"].tolist()
+        assert [s.num_tokens for s in seqs] == g[p + "num_tokens_after"].tolist()
+    assert sched.is_finished()
+    assert len(sched.block_manager.free_block_ids) == 12
+    return kinds
+
+
+def test_scheduler_and_step_inputs_match_reference(mdb):
+    g = load_golden("index_contract.npz")
+    kinds = _replay(mdb, g)
+    assert "straddle" in kinds      # a block that crosses a page boundary was exercised
+
+
+def test_get_slots_cases(mdb):
+    g = load_golden("index_contract.npz")
+    seq = mdb.Sequence(list(range(700)), mdb.SamplingParams(), denoising_block_size=32, mask_token_id=1)
+    seq.block_table = g["slots_table"].tolist()
+    for i, (lo, hi) in enumerate(g["slots_cases"].tolist()):
+        assert seq.get_slots(lo, hi) == g[f"slots_{i}"].tolist()
+    seq.block_table = []
+    assert seq.get_slots(5, 9) == [-1] * 4
+
+
+def test_preemption_when_pages_run_out(mdb):
+    from types import SimpleNamespace
+    cfg = SimpleNamespace(max_num_seqs=4, max_num_batched_tokens=4096, eos=-1, num_kvcache_blocks=2,
+                          kvcache_block_size=256)
+    sched = mdb.Scheduler(cfg)
+    a = mdb.Sequence([1] * 250, mdb.SamplingParams(max_new_tokens=64), denoising_block_size=32, mask_token_id=9)
+    b = mdb.Sequence([1] * 250, mdb.SamplingParams(max_new_tokens=64), denoising_block_size=32, mask_token_id=9)
+    sched.add(a)
+    sched.add(b)
+    seqs, is_prefill = sched.schedule()
+    assert is_prefill and seqs == [a, b]
+    # both need a second page for the block that spills over; only the first can be served
+    seqs, is_prefill = sched.schedule()
+    assert not is_prefill and seqs == [a]
+    assert b.status is mdb.SequenceStatus.WAITING and not b.block_table
+    assert len(a.block_table) == 2
+
+
+def test_sampling_params_and_config_validation(mdb):
+    with pytest.raises(AssertionError):
+        mdb.SamplingParams(temperature=0.0)
+    with pytest.raises(AssertionError):
+        mdb.Config(kvcache_block_size=100)
+    with pytest.raises(AssertionError):
+        mdb.Config(max_num_batched_tokens=100, max_model_len=4096)
+    c = mdb.Config()
+    assert c.decoder_config.vocab_size == 151936 and c.block_size == 32 and c.mask_token_id == 151669
+
+
+def test_model_runner_needs_cuda(mdb):
+    if torch.cuda.is_available():
+        pytest.skip("CUDA present")
+    with pytest.raises(RuntimeError):
+        mdb.ModelRunner(mdb.Config())

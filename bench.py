@@ -16,9 +16,11 @@ Printed JSON line: ``value`` = tokens committed in the K timed steps divided by
 the device time of those steps (inputs resident, CUDA events around the GPU
 work of each step); ``e2e`` = the same tokens divided by the bracketed wall
 time of the K calls through the public API, host->device and device->host
-copies included.  ``roofline`` is measured live for the dominant kernel (the
-weight-streaming gate/up projection with fused SiLU*mul) by launching it over
-the 28 layers' distinct weights (1.4 GB > L2) between CUDA events.
+copies included.  ``roofline`` is measured live for the dominant kernel symbol
+(the weight-streaming GEMM writing split-k slices: qkv, o_proj and down_proj
+of every layer) by launching it over the 28 layers' distinct weights (far
+beyond L2) inside a CUDA graph between two events; ``roofline.per_op`` lists
+every GEMM of a step, the gate/up projection and the LM head included.
 ``cpu_baseline`` times the CPU oracle (the reference's torch ops on the host
 cores) on a bounded sample of the same workload.
 """
@@ -170,41 +172,77 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                 ctx_end=len(engine.scheduler.running[0]) if engine.scheduler.running else total_len)
 
 
-def measure_dominant_kernel(pkg, runner, iters: int = 5):
-    """Live roofline of the gate/up projection kernel: one launch per layer over
-    distinct weights (28 x 50 MB, far beyond L2), CUDA events around the loop."""
+def _graph_time_us(fn, launches: int, reps: int = 5) -> float:
+    """Average device time of one launch: the launches are captured in a CUDA
+    graph (no host launch cost in the timed region) and the graph is replayed
+    ``reps`` times between two events on the launching stream."""
+    fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fn()
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (reps * launches)
+
+
+def measure_dominant_kernel(pkg, runner):
+    """Live roofline of the step's GEMM kernels at m = 32: each is launched once
+    per layer over the 28 layers' distinct weights (0.2 - 1.4 GB per sweep, far
+    beyond the 126 MB L2)."""
     peaks = {}
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
             peaks = json.load(f)
     peak = float(peaks.get("hbm_gbs", 6650.0))
-    eng = runner.engine
-    dcfg = runner.dcfg
+    eng, dcfg, ops = runner.engine, runner.dcfg, pkg.ops
     m = BLOCK
-    x = eng.x[:m]
-    act = eng.act[:m]
+    h, inter, d = dcfg.hidden_size, dcfg.intermediate_size, dcfg.head_dim
+    hq, hkv, vocab = dcfg.num_attention_heads, dcfg.num_key_value_heads, dcfg.vocab_size
+    nqkv = (hq + 2 * hkv) * d
     layers = runner.weights.layers
-    ops = pkg.ops
-    for lw in layers:                      # warm-up pass
-        ops.gateup_swiglu(x, lw.gate_up, out=act)
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(iters):
-        for lw in layers:
-            ops.gateup_swiglu(x, lw.gate_up, out=act)
-    e1.record()
-    torch.cuda.synchronize()
-    launches = iters * len(layers)
-    ms = e0.elapsed_time(e1) / launches
-    h, inter = dcfg.hidden_size, dcfg.intermediate_size
-    alg_bytes = 2 * inter * h * 2 + m * h * 2 + m * inter * 2     # weights once + activations in/out
-    achieved = alg_bytes / (ms * 1e-3) / 1e9
-    return {"bound": "hbm", "kernel": "gemm_skinny_kernel<2,4,swiglu> (gate_up + SiLU*mul, m=32)",
+    x, act, attn = eng.x[:m], eng.act[:m], eng.attn[:m].view(m, hq * d)
+    tc = ops.get_option(ops.OPT_STREAM_KERNEL) == 0
+    kname = "gemm_ws_kernel" if tc else "gemm_skinny_kernel"
+
+    def parts(ks, n):
+        return eng.partials[:ks * m * n].view(ks, m, n)
+
+    temps = torch.ones(1, device=x.device)
+    cases = [
+        ("gate_up + SiLU*mul", f"{kname}<swiglu>", 2 * inter * h * 2 + m * h * 2 + m * inter * 2, len(layers),
+         lambda: [ops.gateup_swiglu(x, lw.gate_up, out=act) for lw in layers]),
+        ("qkv", f"{kname}<partial>", nqkv * h * 2 + m * h * 2 + eng.ks_qkv * m * nqkv * 4, len(layers),
+         lambda: [ops.gemm_splitk_partials(x, lw.qkv, eng.ks_qkv, parts(eng.ks_qkv, nqkv)) for lw in layers]),
+        ("o_proj", f"{kname}<partial>", h * hq * d * 2 + m * hq * d * 2 + eng.ks_o * m * h * 4, len(layers),
+         lambda: [ops.gemm_splitk_partials(attn, lw.o, eng.ks_o, parts(eng.ks_o, h)) for lw in layers]),
+        ("down_proj", f"{kname}<partial>", h * inter * 2 + m * inter * 2 + eng.ks_down * m * h * 4, len(layers),
+         lambda: [ops.gemm_splitk_partials(act, lw.down, eng.ks_down, parts(eng.ks_down, h)) for lw in layers]),
+        ("lm_head + sampler scan", f"{kname}<lm_head> + sampler_finalize_kernel", vocab * h * 2 + m * h * 2 + m * 16, 2,
+         lambda: [eng.sample(eng.final[:m], temps, seed=1) for _ in range(2)]),
+    ]
+    out = []
+    for label, kernel, nbytes, launches, fn in cases:
+        us = _graph_time_us(fn, launches)
+        out.append({"op": label, "kernel": kernel, "us_per_launch": round(us, 2), "bytes_per_launch": nbytes,
+                    "achieved_gbs": round(nbytes / us / 1e3, 1), "frac": round(nbytes / us / 1e3 / peak, 4)})
+    # The kernel symbol with the largest share of a step is the split-k slice instantiation: it runs three
+    # times per layer (qkv, o_proj, down_proj).  Its roofline entry averages those launches.
+    part = [o for o in out if o["kernel"].endswith("<partial>")]
+    nbytes = sum(o["bytes_per_launch"] for o in part) / len(part)
+    us = sum(o["us_per_launch"] for o in part) / len(part)
+    achieved = nbytes / us / 1e3
+    return {"bound": "hbm", "kernel": f"{kname}<partial> (qkv, o_proj, down_proj launches of a step averaged, m=32)",
             "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
-            "traffic": None, "peak_source": "measured" if peaks else "fallback",
-            "bytes_per_launch": alg_bytes, "us_per_launch": round(ms * 1e3, 2)}
+            "traffic": None, "peak_source": "measured" if peaks else "fallback", "bytes_per_launch": round(nbytes),
+            "us_per_launch": round(us, 2), "per_op": out}
 
 
 # ----------------------------------------------------------------------------- CPU arm

@@ -52,6 +52,10 @@ int mdb_version(void);
  * with programmatic dependent launch (default), 0 = plain stream order. */
 enum { MDB_OPT_STREAM_KERNEL = 0, MDB_OPT_PDL = 1 };
 int mdb_set_option(int option, int value);
+/* Measurement aid: registers a device buffer (uint64 count, then (kernel,
+ * event, globaltimer ns) triples) that block 0 of the traced kernels appends
+ * to; NULL switches tracing off. */
+int mdb_set_trace(void* buffer, int64_t bytes);
 int mdb_get_option(int option);
 
 /* Copies the status word of the current device to *out (host memory) after

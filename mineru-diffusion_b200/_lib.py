@@ -21,6 +21,7 @@ SIGNATURES = {
     "mdb_strerror": (C.c_char_p, [_i]),
     "mdb_version": (_i, []),
     "mdb_set_option": (_i, [_i, _i]),
+    "mdb_set_trace": (_i, [_p, _i64]),
     "mdb_get_option": (_i, [_i]),
     "mdb_last_device_status": (_i, [C.POINTER(C.c_uint), _i]),
     "mdb_kv_commit": (_i, [_p, _i64, _p, _i64, _p, _p, _p, _i, _i, _i64, _p]),

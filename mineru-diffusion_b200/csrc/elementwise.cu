@@ -42,8 +42,10 @@ __global__ void __launch_bounds__(kNormThreads)
 add_rmsnorm_kernel(const bf16* __restrict__ x, const float* __restrict__ partials, int nparts,
                    const bf16* __restrict__ residual_in, const bf16* __restrict__ weight, float eps,
                    bf16* __restrict__ y_out, bf16* __restrict__ residual_out, int m, int h) {
+  if (threadIdx.x == 0) trace_event(10, 0);
   pdl_launch_dependents();
   pdl_wait();
+  if (threadIdx.x == 0) trace_event(10, 1);
   const int row = blockIdx.x;
   const int chunks = h >> 3;
   const int64_t row_off = static_cast<int64_t>(row) * h;
@@ -123,6 +125,7 @@ add_rmsnorm_kernel(const bf16* __restrict__ x, const float* __restrict__ partial
       *reinterpret_cast<uint4*>(y_out + row_off + c * 8) = o;
     }
   }
+  if (threadIdx.x == 0) trace_event(10, 2);
 }
 
 // ---------------------------------------------------------------------------
@@ -298,6 +301,14 @@ const char* mdb_strerror(int code) {
 }
 
 int mdb_version(void) { return 101; }
+
+int mdb_set_trace(void* buffer, int64_t bytes) {
+  TraceBuf t;
+  t.data = static_cast<unsigned long long*>(buffer);
+  t.capacity = buffer != nullptr && bytes >= 32 ? static_cast<unsigned int>((bytes - 8) / 24) : 0;
+  if (t.capacity == 0) t.data = nullptr;
+  return cudaMemcpyToSymbol(g_trace, &t, sizeof(t)) == cudaSuccess ? MDB_OK : MDB_ERR_CUDA;
+}
 
 int mdb_set_option(int option, int value) {
   switch (option) {

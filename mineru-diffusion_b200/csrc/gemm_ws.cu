@@ -171,6 +171,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tasks = a.tiles_n * a.ksplit;
+  if (threadIdx.x == 0) trace_event(EPI, 0);
   const uint32_t tmem_cols = 2 * a.ntok <= 32 ? 32 : (2 * a.ntok <= 64 ? 64 : 128);
 
   if (threadIdx.x == 0) {
@@ -195,6 +196,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = misc[0];
   pdl_launch_dependents();
+  if (threadIdx.x == 0) trace_event(EPI, 1);
 
   auto task_tile = [&](int task) { return task / a.ksplit; };
   auto task_slice = [&](int task) { return task % a.ksplit; };
@@ -220,7 +222,9 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (int c = 0; c < nchunks; ++c) {
           if (!deps_ready && deferred == a.stages) {
             // ring full of weight tiles: now the activations are needed
+            trace_event(EPI, 2);
             pdl_wait();
+            trace_event(EPI, 3);
             deps_ready = true;
             for (int d = 0; d < deferred; ++d) {
               const int s = (deferred_stage0 + d) % a.stages;
@@ -249,7 +253,9 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
       }
       if (!deps_ready) {
+        trace_event(EPI, 2);
         pdl_wait();
+        trace_event(EPI, 3);
         for (int d = 0; d < deferred; ++d) {
           const int s = (deferred_stage0 + d) % a.stages;
           tma_load_2d(x_tiles + s * x_tile_bytes, &map_x, deferred_k[d], 0, bar_full + 8 * s);
@@ -273,6 +279,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const uint32_t d_tmem = tmem_base + acc * a.ntok;
         for (int c = 0; c < nchunks; ++c) {
           if (!mbar_wait(bar_full + 8 * stage, phase)) { ok = false; break; }
+          if (c == 0) trace_event(EPI, 4);
           tc_fence_after();
           const uint64_t adesc = umma_desc_sw128(w_tiles + stage * kWsWTileBytes);
           const uint64_t bdesc = umma_desc_sw128(x_tiles + stage * x_tile_bytes);
@@ -284,6 +291,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         if (!ok) break;
         umma_commit(bar_acc_full + 8 * acc);           // accumulator complete
+        trace_event(EPI, 5);
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
       if (!ok) { misc[1] = 1; report_status(MDB_STATUS_WAIT_TIMEOUT); }
@@ -302,6 +310,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (lane == 0) { misc[1] = 1; report_status(MDB_STATUS_WAIT_TIMEOUT); }
         break;
       }
+      if (threadIdx.x == 0) trace_event(EPI, 6);
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * a.ntok + (static_cast<uint32_t>(32 * warp) << 16);
       float v[64];
@@ -337,25 +346,31 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (int t = 0; t < 64; ++t)
           if (t < a.m) a.y[t * a.ldy + row] = __float2bfloat16_rn(v[t]);
       } else if (EPI == kWsSwiglu) {
-        // rows 0..63 of the tile are gate rows, 64..127 the matching up rows
-        if (warp >= 2) {
+        // rows 0..63 of the tile are gate rows, 64..127 the matching up rows: every thread parks its
+        // row in shared memory, then all 128 threads share the SiLU*mul work (64 columns x 32 step rows
+        // per pass, 16 outputs per thread)
 #pragma unroll
-          for (int t = 0; t < 64; ++t)
-            if (t < a.m) epi[(row_local - 64) * 33 + (t & 31) + (t >> 5) * (64 * 33)] = v[t];
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (warp < 2) {
-          const int col = tile * 64 + row_local;
+        for (int half = 0; half < 2; ++half) {
+          if (half * 32 >= a.m) break;
 #pragma unroll
-          for (int t = 0; t < 64; ++t)
-            if (t < a.m) {
-              const float gt = bf16_round(v[t]);
-              const float up = bf16_round(epi[row_local * 33 + (t & 31) + (t >> 5) * (64 * 33)]);
-              const float s = gt * (1.0f / (1.0f + expf(-gt)));
-              a.y[t * a.ldy + col] = __float2bfloat16_rn(bf16_round(s) * up);
+          for (int t = 0; t < 32; ++t) epi[row_local * 33 + t] = v[32 * half + t];
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          const int c = threadIdx.x & 63;
+          const int tg = threadIdx.x >> 6;          // 0 or 1: step rows [16*tg, 16*tg + 16)
+          const int col = tile * 64 + c;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int tt = 16 * tg + i;
+            const int r = 32 * half + tt;
+            if (r < a.m) {
+              const float gt = bf16_round(epi[c * 33 + tt]);
+              const float up = bf16_round(epi[(64 + c) * 33 + tt]);
+              const float s = gt * __frcp_rn(1.0f + __expf(-gt));
+              a.y[r * a.ldy + col] = __float2bfloat16_rn(bf16_round(s) * up);
             }
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
       } else {
         // LM head: stage the tile, then each warp reduces 8-row groups of the step over the 128 vocabulary rows
 #pragma unroll
@@ -404,6 +419,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
   }
 
+  if (threadIdx.x == 0) trace_event(EPI, 7);
   tc_fence_before();
   __syncthreads();
   if (warp == 5) {

@@ -30,6 +30,27 @@ __device__ __forceinline__ void report_status(unsigned int bit) { atomicOr(&g_de
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// ---- optional device-side timeline (measurement aid) ---------------------------
+// When a trace buffer is registered (mdb_set_trace), block 0 of the traced
+// kernels appends (kernel id, event id, %globaltimer) triples to it.
+struct TraceBuf {
+  unsigned long long* data;   // [0] = count, then triples
+  unsigned int capacity;      // triples
+};
+__device__ TraceBuf g_trace = {nullptr, 0};
+
+__device__ __forceinline__ void trace_event(unsigned int kernel_id, unsigned int event_id) {
+  if (g_trace.data == nullptr || blockIdx.x != 0 || blockIdx.y != 0 || blockIdx.z != 0) return;
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  const unsigned long long slot = atomicAdd(g_trace.data, 1ull);
+  if (slot < g_trace.capacity) {
+    g_trace.data[1 + 3 * slot] = kernel_id;
+    g_trace.data[2 + 3 * slot] = event_id;
+    g_trace.data[3 + 3 * slot] = t;
+  }
+}
+
 // ---- small numeric helpers ------------------------------------------------
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 

@@ -30,7 +30,8 @@ enum {
   MDB_ERR_ALIGN = -2,       /* pointer or stride not 16-byte aligned */
   MDB_ERR_UNSUPPORTED = -3, /* shape outside what the kernels are built for */
   MDB_ERR_CUDA = -4,        /* the launch itself was refused by the runtime */
-  MDB_ERR_WORKSPACE = -5    /* workspace smaller than *_workspace_bytes() */
+  MDB_ERR_WORKSPACE = -5,   /* workspace smaller than *_workspace_bytes() */
+  MDB_ERR_STATIC_LIMIT = -6 /* request needs more than the fixed scratch of an allocation-free entry point */
 };
 
 /* bits of the device status word */
@@ -87,6 +88,24 @@ int mdb_attn_block_paged(const void* q, const void* k_cache, const void* v_cache
                          const int32_t* block_table, int table_stride, const int32_t* ctx_lens, int bs, int block,
                          int hq, int hkv, int num_pages, float softmax_scale, int nsplit, void* workspace,
                          int64_t workspace_bytes, mdb_stream_t stream);
+
+/* No counterpart in the reference.  Same operation and arguments as
+ * mdb_attn_block_paged, but without a workspace argument: the split partials
+ * go to a fixed 8 MiB array that lives inside the library (one per device,
+ * held from load to exit), and the call allocates nothing.  It is meant for
+ * hosts that cannot provide scratch memory, e.g. an engine whose KV-cache
+ * pool has taken all remaining device memory, or a serving thread that must
+ * not enter the allocator.  A request whose partials would not fit
+ * (mdb_attn_paged_workspace_bytes(bs, block, hq, nsplit) above
+ * mdb_attn_block_paged_noalloc_limit()) is refused with MDB_ERR_STATIC_LIMIT;
+ * lower nsplit or bs.  The first call on each device resolves the array's
+ * device address and should be made outside stream capture.  Calls share the
+ * array: calls that overlap on the GPU race, so issue them on one stream. */
+int64_t mdb_attn_block_paged_noalloc_limit(void);
+int mdb_attn_block_paged_noalloc(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                 const int32_t* block_table, int table_stride, const int32_t* ctx_lens, int bs,
+                                 int block, int hq, int hkv, int num_pages, float softmax_scale, int nsplit,
+                                 mdb_stream_t stream);
 
 /* ---- staircase (block-causal, right-aligned) prefill attention ----------- */
 

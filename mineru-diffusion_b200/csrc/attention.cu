@@ -533,4 +533,48 @@ int mdb_attn_staircase_varlen(const void* q, int64_t q_stride, const void* k, in
                     static_cast<cudaStream_t>(stream), a);
 }
 
+// ---------------------------------------------------------------------------
+// Allocation-free variant of the paged block attention.
+//
+// Some hosts of this library cannot give it a workspace: an engine that has
+// already handed every spare byte of the device to its KV-cache pool has no
+// headroom left for a cudaMalloc, and a serving thread that must never stall
+// cannot afford one either (cudaMalloc takes driver locks and may synchronise
+// the device).  For them the split partials live in a fixed array inside the
+// library image instead of a caller buffer.  The array is part of every
+// device's copy of the module from load until the process exits.
+//
+// The array's name is only a host-side handle here: its device address is
+// looked up once per device with cudaGetSymbolAddress (with that device
+// current) on the first call made on that device, so make that first call
+// outside any stream capture.  Nothing in the array has to start at zero: the
+// attention kernel overwrites every (request, split, head, row) slot that
+// the merge kernel then reads.  All calls on a device share the one array, so
+// two calls that overlap on the GPU (different streams) race on it; keep
+// them on one stream or order them with events.
+constexpr int64_t kAttnStaticScratchBytes = 8ll << 20;   // 8 MiB, e.g. 16 splits x 16 heads x 32 rows for one request
+static __device__ __align__(256) unsigned char g_attn_static_scratch[kAttnStaticScratchBytes];
+static void* s_attn_static_scratch_ptr[64] = {};          // device address per device ordinal
+
+int64_t mdb_attn_block_paged_noalloc_limit(void) { return kAttnStaticScratchBytes; }
+
+int mdb_attn_block_paged_noalloc(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                 const int32_t* block_table, int table_stride, const int32_t* ctx_lens, int bs,
+                                 int block, int hq, int hkv, int num_pages, float softmax_scale, int nsplit,
+                                 mdb_stream_t stream) {
+  MDB_REQUIRE(bs >= 0 && block > 0 && hq > 0 && nsplit >= 1, MDB_ERR_ARG);
+  const int64_t need = mdb_attn_paged_workspace_bytes(bs, block, hq, nsplit);
+  MDB_REQUIRE(need <= kAttnStaticScratchBytes, MDB_ERR_STATIC_LIMIT);
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MDB_ERR_CUDA;
+  if (s_attn_static_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_attn_static_scratch) != cudaSuccess || p == nullptr) return MDB_ERR_CUDA;
+    s_attn_static_scratch_ptr[dev] = p;
+  }
+  return mdb_attn_block_paged(q, k_cache, v_cache, out, block_table, table_stride, ctx_lens, bs, block, hq, hkv,
+                              num_pages, softmax_scale, nsplit, s_attn_static_scratch_ptr[dev], kAttnStaticScratchBytes,
+                              stream);
+}
+
 }  // extern "C"

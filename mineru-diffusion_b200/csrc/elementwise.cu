@@ -296,6 +296,8 @@ const char* mdb_strerror(int code) {
     case MDB_ERR_UNSUPPORTED: return "shape not supported by the sm_100a kernels";
     case MDB_ERR_CUDA: return "CUDA runtime refused the launch";
     case MDB_ERR_WORKSPACE: return "workspace too small";
+    case MDB_ERR_STATIC_LIMIT:
+      return "request exceeds the fixed scratch array of the allocation-free entry point (lower nsplit or the batch)";
     default: return "unknown error code";
   }
 }

@@ -124,6 +124,33 @@ def block_attn_with_kvcache(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
     return out
 
 
+def block_attn_with_kvcache_noalloc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                                    cache_seqlens: torch.Tensor, block_table: torch.Tensor, out: torch.Tensor,
+                                    softmax_scale: float | None = None, nsplit: int = 1) -> torch.Tensor:
+    """``block_attn_with_kvcache`` for hosts that cannot hand over scratch memory
+    (all device memory already given to the KV-cache pool, or a thread that must
+    stay out of the allocator): the split partials use a fixed 8 MiB array
+    inside the library, so neither this wrapper nor the call allocates -- the
+    caller passes ``out``.  Raises ``MdbError`` when (bs, nsplit) need more than
+    that array.  Calls share the array; keep them on one stream."""
+    bs, block, hq, d = q.shape
+    pages, page, hkv, _ = k_cache.shape
+    for t, nm in ((q, "q"), (k_cache, "k_cache"), (v_cache, "v_cache"), (out, "out")):
+        _need(t, _BF16, nm)
+        if not t.is_contiguous():
+            raise ValueError(f"{nm} must be contiguous")
+    _need(cache_seqlens, torch.int32, "cache_seqlens")
+    _need(block_table, torch.int32, "block_table")
+    if softmax_scale is None:
+        softmax_scale = d ** -0.5
+    _lib.check(_lib.lib().mdb_attn_block_paged_noalloc(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                                       out.data_ptr(), block_table.data_ptr(), block_table.stride(0),
+                                                       cache_seqlens.data_ptr(), bs, block, hq, hkv, pages,
+                                                       float(softmax_scale), nsplit, _stream()),
+               "mdb_attn_block_paged_noalloc")
+    return out
+
+
 def sparse_attn_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_q: torch.Tensor,
                        cu_seqlens_k: torch.Tensor, staircase_size: int = 4, max_seqlen: int | None = None,
                        out: torch.Tensor | None = None) -> torch.Tensor:

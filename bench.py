@@ -241,7 +241,10 @@ def measure_dominant_kernel(pkg, runner):
     achieved = nbytes / us / 1e3
     return {"bound": "hbm", "kernel": f"{kname}<partial> (qkv, o_proj, down_proj launches of a step averaged, m=32)",
             "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
-            "traffic": None, "peak_source": "measured" if peaks else "fallback", "bytes_per_launch": round(nbytes),
+            # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
+            # profiles/gemm_ws_kernel_partial_config2_m32.md (same three launches, averaged)
+            "traffic": 17051819 if tc else None,
+            "peak_source": "measured" if peaks else "fallback", "bytes_per_launch": round(nbytes),
             "us_per_launch": round(us, 2), "per_op": out}
 
 

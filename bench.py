@@ -354,15 +354,9 @@ def main():
         torch.distributed.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
     res = run_ours(args, rank, world, local_rank)
     tokens, dev_ms, e2e_ms = res["tokens"], res["dev_ms"], res["e2e_ms"]
-    if world > 1:
-        t = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=f"cuda:{local_rank}")
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-        dev_ms, e2e_ms = float(t[0]), float(t[1])
-        c = torch.tensor([tokens, res["launches"]], dtype=torch.int64, device=f"cuda:{local_rank}")
-        torch.distributed.all_reduce(c)
-        tokens, launches = int(c[0]), int(c[1])
-    else:
-        launches = res["launches"]
+    dp = importlib.import_module("mineru-diffusion_b200.engine.dp")
+    tokens, (dev_ms, e2e_ms), (launches,) = dp.reduce_throughput(tokens, [dev_ms, e2e_ms], [res["launches"]],
+                                                                 f"cuda:{local_rank}")
     if rank == 0:
         cpu = None
         if args.gpus == 1 and not args.no_cpu_baseline:

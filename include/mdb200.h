@@ -213,6 +213,53 @@ int mdb_gumbel_noise(float* out, int m, int vocab, uint32_t seed, uint32_t step,
 int mdb_unmask_decide(int64_t* block_ids, const int32_t* x0, const float* conf, int bs, int block, int64_t mask_id,
                       float threshold, int quota, uint8_t* transfer_out, int32_t* count_out, mdb_stream_t stream);
 
+/* ---- tensor-parallel pair (TP = 2) -------------------------------------------------- */
+
+/* Replaces dist.all_reduce in RowParallelLinear.forward (NV/layers/linear.py:153-157),
+ * the logits gather of ParallelLMHead (NV/layers/embed_head.py:68-71) and the
+ * handle plumbing NCCL does for them.  Each rank holds half of the heads, MLP
+ * columns and vocabulary tiles.  The o_proj / down_proj GEMM of a rank stores
+ * its fp32 k-slices into its own slice buffer AND, over NVLink, into the
+ * peer's (plain stores from the epilogue), then writes a sequence number into
+ * its CTA's flag slot in the peer's memory.  The consumer (RMSNorm with
+ * residual add) waits, bounded, for the peer's slots and sums rank 0's slices
+ * then rank 1's, so both ranks obtain bit-identical rows.  Sequence number =
+ * (*epoch) * 256 + tag; the host advances *epoch every step, tag (1..255) is
+ * distinct per producing launch within a step. */
+
+/* Device memory the peer may map: allocate, export a 64-byte handle, import the
+ * peer's handle (in the other process), release/free at shutdown.  Called at
+ * engine start only. */
+int mdb_tp_alloc(int64_t bytes, void** out);
+int mdb_tp_free(void* ptr);
+int mdb_tp_export(void* ptr, void* handle_out64);
+int mdb_tp_import(const void* handle64, void** peer_ptr_out);
+int mdb_tp_release(void* peer_ptr);
+
+/* mdb_gemm_splitk_partials whose slices also go to peer_partials (same layout,
+ * peer memory) and that signals peer_flags[cta]; m <= 64, n % 128 == 0,
+ * k % 64 == 0.  mdb_tp_grid_size gives the number of CTAs = flag slots used. */
+int mdb_gemm_splitk_partials_tp(const void* x, int64_t ldx, const void* w, float* partials, float* peer_partials,
+                                int m, int n, int k, int ksplit, uint32_t* peer_flags, uint32_t tag,
+                                const uint32_t* epoch, mdb_stream_t stream);
+int mdb_tp_grid_size(int m, int n, int k, int ksplit);
+
+/* mdb_add_rmsnorm that first waits for wait_count flag slots written by the peer. */
+int mdb_add_rmsnorm_tp(const void* x, const float* partials, int nparts, const void* residual_in, const void* weight,
+                       float eps, void* y_out, void* residual_out, int m, int h, const uint32_t* wait_flags,
+                       int wait_count, uint32_t tag, const uint32_t* epoch, mdb_stream_t stream);
+
+/* mdb_lmhead_sample over the vocabulary tiles [tile_begin, tile_begin + tile_count)
+ * (128 rows each) of the full weight; the per-tile records (20 bytes per step
+ * row) are mirrored into the peer's workspace instead of gathering logits, and
+ * the merge waits for the peer's records. */
+int mdb_lmhead_sample_tp(const void* hidden, int64_t ld_hidden, const void* w, int m, int vocab, int h,
+                         const float* temperatures, int block, int noise_mode, const float* noise, uint32_t seed,
+                         uint32_t step, const uint32_t* step_dev, void* workspace, void* peer_workspace,
+                         int64_t workspace_bytes, int tile_begin, int tile_count, uint32_t* peer_flags,
+                         const uint32_t* wait_flags, int wait_count, uint32_t tag, const uint32_t* epoch,
+                         int32_t* x0_out, float* conf_out, mdb_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -45,6 +45,16 @@ SIGNATURES = {
     "mdb_logits_sample": (_i, [_p, _i64, _i, _i, _p, _i, _i, _p, _u32, _u32, _p, _p, _i64, _p, _p, _p]),
     "mdb_gumbel_noise": (_i, [_p, _i, _i, _u32, _u32, _p]),
     "mdb_unmask_decide": (_i, [_p, _p, _p, _i, _i, _i64, _f, _i, _p, _p, _p]),
+    "mdb_tp_alloc": (_i, [_i64, C.POINTER(C.c_void_p)]),
+    "mdb_tp_free": (_i, [_p]),
+    "mdb_tp_export": (_i, [_p, _p]),
+    "mdb_tp_import": (_i, [_p, C.POINTER(C.c_void_p)]),
+    "mdb_tp_release": (_i, [_p]),
+    "mdb_gemm_splitk_partials_tp": (_i, [_p, _i64, _p, _p, _p, _i, _i, _i, _i, _p, _u32, _p, _p]),
+    "mdb_tp_grid_size": (_i, [_i, _i, _i, _i]),
+    "mdb_add_rmsnorm_tp": (_i, [_p, _p, _i, _p, _p, _f, _p, _p, _i, _i, _p, _i, _u32, _p, _p]),
+    "mdb_lmhead_sample_tp": (_i, [_p, _i64, _p, _i, _i, _i, _p, _i, _i, _p, _u32, _u32, _p, _p, _p, _i64, _i, _i, _p,
+                                  _p, _i, _u32, _p, _p, _p, _p]),
 }
 
 _lib = None

@@ -23,9 +23,9 @@ LmHeadLayout lmhead_layout(int m, int vocab) {
 }
 
 int finalize_sampler(const float4* part_f, const int* part_i, int nparts, int m, int32_t* x0_out, float* conf_out,
-                     cudaStream_t st) {
+                     cudaStream_t st, const TpSignal tp = TpSignal{nullptr, nullptr, 0, 0, nullptr}) {
   return mdb_launch(sampler_finalize_kernel, dim3(m), dim3(kFinalizeThreads), 0, st, part_f, part_i, nparts, m, x0_out,
-                    conf_out);
+                    conf_out, tp);
 }
 
 int scan_logits(const bf16* logits, int64_t ld, int m, int vocab, const float* temperatures, int block, int noise_mode,
@@ -246,6 +246,76 @@ int mdb_logits_sample(const void* logits, int64_t ld, int m, int vocab, const fl
   MDB_REQUIRE(workspace_bytes >= align256(nparts * m * 16) + align256(nparts * m * 4), MDB_ERR_WORKSPACE);
   return scan_logits(static_cast<const bf16*>(logits), ld, m, vocab, temperatures, block, noise_mode, noise, seed, step,
                      step_dev, static_cast<unsigned char*>(workspace), x0_out, conf_out, static_cast<cudaStream_t>(stream));
+}
+
+// ---- tensor-parallel pair (TP = 2) ----------------------------------------------------
+
+int mdb_gemm_splitk_partials_tp(const void* x, int64_t ldx, const void* w, float* partials, float* peer_partials,
+                                int m, int n, int k, int ksplit, uint32_t* peer_flags, uint32_t tag,
+                                const uint32_t* epoch, mdb_stream_t stream) {
+  if (m == 0) return MDB_OK;
+  int rc = check_skinny_common(x, ldx, w, m, n, k);
+  if (rc != MDB_OK) return rc;
+  MDB_REQUIRE(partials && peer_partials && peer_flags && epoch && ksplit >= 1 && ksplit <= 64, MDB_ERR_ARG);
+  MDB_REQUIRE(tag >= 1 && tag <= 255, MDB_ERR_ARG);
+  MDB_REQUIRE(mdb_aligned16(partials) && mdb_aligned16(peer_partials), MDB_ERR_ALIGN);
+  MDB_REQUIRE(ws_supported(kWsPartial, m, n, k, ldx), MDB_ERR_UNSUPPORTED);
+  const int chunks = k / kWsBK;
+  MDB_REQUIRE(((chunks + ksplit - 1) / ksplit) * (ksplit - 1) < chunks, MDB_ERR_ARG);
+  WsArgs a = {};
+  a.m = m; a.n = n; a.k = k; a.ksplit = ksplit;
+  a.partials = partials;
+  a.peer_partials = peer_partials;
+  a.tp = TpSignal{peer_flags, nullptr, 0, tag, epoch};
+  return launch_ws<kWsPartial>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), a,
+                               static_cast<cudaStream_t>(stream));
+}
+
+int mdb_tp_grid_size(int m, int n, int k, int ksplit) {
+  // CTAs (= flag slots) a streaming GEMM of this shape is launched with
+  if (n % kWsTileRows != 0) return 0;
+  const int tasks = n / kWsTileRows * (ksplit > 0 ? ksplit : 1);
+  return tasks < 148 ? tasks : 148;
+}
+
+int mdb_lmhead_sample_tp(const void* hidden, int64_t ld_hidden, const void* w, int m, int vocab, int h,
+                         const float* temperatures, int block, int noise_mode, const float* noise, uint32_t seed,
+                         uint32_t step, const uint32_t* step_dev, void* workspace, void* peer_workspace,
+                         int64_t workspace_bytes, int tile_begin, int tile_count, uint32_t* peer_flags,
+                         const uint32_t* wait_flags, int wait_count, uint32_t tag, const uint32_t* epoch,
+                         int32_t* x0_out, float* conf_out, mdb_stream_t stream) {
+  MDB_REQUIRE(m >= 1 && m <= 64 && vocab > 0 && h > 0 && block > 0, MDB_ERR_ARG);
+  MDB_REQUIRE(hidden && w && temperatures && x0_out && conf_out && workspace && peer_workspace, MDB_ERR_ARG);
+  MDB_REQUIRE(peer_flags && wait_flags && epoch && wait_count > 0 && tag >= 1 && tag <= 255, MDB_ERR_ARG);
+  MDB_REQUIRE(m % block == 0 && ld_hidden >= h, MDB_ERR_ARG);
+  MDB_REQUIRE(noise_mode >= 0 && noise_mode <= 2 && (noise_mode != 1 || noise != nullptr), MDB_ERR_ARG);
+  MDB_REQUIRE(ws_supported(kWsLmHead, m, vocab, h, ld_hidden), MDB_ERR_UNSUPPORTED);
+  const int tiles_total = vocab / kWsTileRows;
+  MDB_REQUIRE(tile_begin >= 0 && tile_count >= 1 && tile_begin + tile_count <= tiles_total, MDB_ERR_ARG);
+  const LmHeadLayout lay = lmhead_layout(m, vocab);
+  MDB_REQUIRE(workspace_bytes >= lay.total, MDB_ERR_WORKSPACE);
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+  unsigned char* pws = static_cast<unsigned char*>(peer_workspace);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  WsArgs a = {};
+  a.m = m; a.n = vocab; a.k = h; a.ksplit = 1;
+  a.temperatures = temperatures;
+  a.block = block;
+  a.noise_mode = noise_mode;
+  a.noise = noise;
+  a.seed = seed; a.step = step;
+  a.step_dev = step_dev;
+  a.part_f = reinterpret_cast<float4*>(ws);
+  a.part_i = reinterpret_cast<int*>(ws + lay.off_i);
+  a.peer_part_f = reinterpret_cast<float4*>(pws);
+  a.peer_part_i = reinterpret_cast<int*>(pws + lay.off_i);
+  a.tile_begin = tile_begin;
+  a.tiles_override = tile_count;
+  a.tp = TpSignal{peer_flags, nullptr, 0, tag, epoch};
+  int rc = launch_ws<kWsLmHead>(static_cast<const bf16*>(hidden), ld_hidden, static_cast<const bf16*>(w), a, st);
+  if (rc != MDB_OK) return rc;
+  const TpSignal wait = {nullptr, wait_flags, wait_count, tag, epoch};
+  return finalize_sampler(a.part_f, a.part_i, tiles_total, m, x0_out, conf_out, st, wait);
 }
 
 }  // extern "C"

@@ -41,10 +41,11 @@ constexpr int kNormMaxChunks = 4;  // h <= 256 * 4 * 8 = 8192
 __global__ void __launch_bounds__(kNormThreads)
 add_rmsnorm_kernel(const bf16* __restrict__ x, const float* __restrict__ partials, int nparts,
                    const bf16* __restrict__ residual_in, const bf16* __restrict__ weight, float eps,
-                   bf16* __restrict__ y_out, bf16* __restrict__ residual_out, int m, int h) {
+                   bf16* __restrict__ y_out, bf16* __restrict__ residual_out, int m, int h, const TpSignal tp) {
   if (threadIdx.x == 0) trace_event(10, 0);
   pdl_launch_dependents();
   pdl_wait();
+  tp_wait(tp);     // tensor-parallel pair: the peer's slices must have landed
   if (threadIdx.x == 0) trace_event(10, 1);
   const int row = blockIdx.x;
   const int chunks = h >> 3;
@@ -356,8 +357,9 @@ int mdb_kv_commit(const void* key, int64_t key_stride, const void* value, int64_
                     static_cast<bf16*>(k_cache), static_cast<bf16*>(v_cache), slot_mapping, row_elems, num_slots);
 }
 
-int mdb_add_rmsnorm(const void* x, const float* partials, int nparts, const void* residual_in, const void* weight,
-                    float eps, void* y_out, void* residual_out, int m, int h, mdb_stream_t stream) {
+static int add_rmsnorm_impl(const void* x, const float* partials, int nparts, const void* residual_in,
+                            const void* weight, float eps, void* y_out, void* residual_out, int m, int h,
+                            const TpSignal& tp, mdb_stream_t stream) {
   MDB_REQUIRE(m >= 0 && h > 0, MDB_ERR_ARG);
   if (m == 0) return MDB_OK;
   MDB_REQUIRE((x != nullptr) != (partials != nullptr), MDB_ERR_ARG);
@@ -370,7 +372,21 @@ int mdb_add_rmsnorm(const void* x, const float* partials, int nparts, const void
   return mdb_launch(add_rmsnorm_kernel, dim3(m), dim3(kNormThreads), 0, static_cast<cudaStream_t>(stream),
                     static_cast<const bf16*>(x), partials, nparts, static_cast<const bf16*>(residual_in),
                     static_cast<const bf16*>(weight), eps, static_cast<bf16*>(y_out),
-                    static_cast<bf16*>(residual_out), m, h);
+                    static_cast<bf16*>(residual_out), m, h, tp);
+}
+
+int mdb_add_rmsnorm(const void* x, const float* partials, int nparts, const void* residual_in, const void* weight,
+                    float eps, void* y_out, void* residual_out, int m, int h, mdb_stream_t stream) {
+  const TpSignal none = {nullptr, nullptr, 0, 0, nullptr};
+  return add_rmsnorm_impl(x, partials, nparts, residual_in, weight, eps, y_out, residual_out, m, h, none, stream);
+}
+
+int mdb_add_rmsnorm_tp(const void* x, const float* partials, int nparts, const void* residual_in, const void* weight,
+                       float eps, void* y_out, void* residual_out, int m, int h, const uint32_t* wait_flags,
+                       int wait_count, uint32_t tag, const uint32_t* epoch, mdb_stream_t stream) {
+  MDB_REQUIRE(wait_flags && epoch && wait_count > 0 && tag >= 1 && tag <= 255, MDB_ERR_ARG);
+  const TpSignal tp = {nullptr, wait_flags, wait_count, tag, epoch};
+  return add_rmsnorm_impl(x, partials, nparts, residual_in, weight, eps, y_out, residual_out, m, h, tp, stream);
 }
 
 int mdb_qknorm_rope_commit(const void* qkv, int64_t ld_qkv, const float* partials, int nparts,

@@ -221,9 +221,10 @@ constexpr int kFinalizeThreads = 256;
 
 __global__ void __launch_bounds__(kFinalizeThreads)
 sampler_finalize_kernel(const float4* __restrict__ part_f, const int* __restrict__ part_i, int nparts, int m,
-                        int32_t* __restrict__ x0_out, float* __restrict__ conf_out) {
+                        int32_t* __restrict__ x0_out, float* __restrict__ conf_out, const TpSignal tp) {
   pdl_launch_dependents();
   pdl_wait();
+  tp_wait(tp);     // tensor-parallel pair: the peer's records of its vocabulary shard must have landed
   const int row = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   SampleRec r = {-INFINITY, 0.f, -INFINITY, 0.f, 0x7fffffff};

@@ -60,8 +60,15 @@ struct WsArgs {
   const float* noise;
   uint32_t seed, step;
   const uint32_t* step_dev;
-  float4* part_f;      // [tiles_n][m]
+  float4* part_f;      // [tiles_total][m]
   int* part_i;
+  // tensor-parallel pair (all null / zero on one GPU)
+  int tile_begin;            // first weight-row tile this rank owns (LM head: vocabulary shard)
+  int tiles_override;        // > 0: number of tiles this rank processes instead of all of them
+  float* peer_partials;      // same layout as partials, in the peer's memory
+  float4* peer_part_f;       // LM head records mirrored into the peer's memory
+  int* peer_part_i;
+  TpSignal tp;
 };
 
 // ---- PTX wrappers ------------------------------------------------------------
@@ -198,7 +205,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   pdl_launch_dependents();
   if (threadIdx.x == 0) trace_event(EPI, 1);
 
-  auto task_tile = [&](int task) { return task / a.ksplit; };
+  auto task_tile = [&](int task) { return a.tile_begin + task / a.ksplit; };
   auto task_slice = [&](int task) { return task % a.ksplit; };
   auto slice_chunks = [&](int slice) {
     const int beg = slice * a.chunks_per_slice;
@@ -340,6 +347,12 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
         for (int t = 0; t < 64; ++t)
           if (t < a.m) dst[static_cast<int64_t>(t) * a.n] = v[t];
+        if (a.peer_partials != nullptr) {   // the other GPU of the pair sums these slices too: store them there directly
+          float* pdst = a.peer_partials + static_cast<int64_t>(slice) * a.m * a.n + row;
+#pragma unroll
+          for (int t = 0; t < 64; ++t)
+            if (t < a.m) pdst[static_cast<int64_t>(t) * a.n] = v[t];
+        }
       } else if (EPI == kWsBf16) {
         const int row = tile * kWsTileRows + row_local;
 #pragma unroll
@@ -411,6 +424,10 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             if (lane == 0) {
               a.part_f[static_cast<int64_t>(tile) * a.m + r] = make_float4(mx, se, bv, bl);
               a.part_i[static_cast<int64_t>(tile) * a.m + r] = bi;
+              if (a.peer_part_f != nullptr) {
+                a.peer_part_f[static_cast<int64_t>(tile) * a.m + r] = make_float4(mx, se, bv, bl);
+                a.peer_part_i[static_cast<int64_t>(tile) * a.m + r] = bi;
+              }
             }
           }
           asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -420,6 +437,11 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   }
 
   if (threadIdx.x == 0) trace_event(EPI, 7);
+  if (a.tp.peer_flags != nullptr && warp < 4) {
+    // all four epilogue warps have issued their peer stores: publish them to the peer
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (threadIdx.x == 0) tp_signal(a.tp);
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == 5) {
@@ -520,6 +542,7 @@ static int launch_ws(const bf16* x, int64_t ldx, const bf16* w, WsArgs& a, cudaS
   a.chunks_total = a.k / kWsBK;
   a.chunks_per_slice = (a.chunks_total + a.ksplit - 1) / a.ksplit;
   a.tiles_n = (EPI == kWsSwiglu) ? a.inter / 64 : a.n / kWsTileRows;
+  if (a.tiles_override > 0) a.tiles_n = a.tiles_override;
   const int budget = 227 * 1024;
   int stages = 12;
   while (stages > 2 && ws_smem_bytes(stages, a.ntok) > budget) --stages;

@@ -7,3 +7,4 @@
 #include "gemm_ws.cu"
 #include "gemm_tiled.cu"
 #include "api_linear.cu"
+#include "tp_p2p.cu"

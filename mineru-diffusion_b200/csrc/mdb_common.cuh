@@ -4,6 +4,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <string.h>
 
 #include "../../include/mdb200.h"
 
@@ -49,6 +50,52 @@ __device__ __forceinline__ void trace_event(unsigned int kernel_id, unsigned int
     g_trace.data[2 + 3 * slot] = event_id;
     g_trace.data[3 + 3 * slot] = t;
   }
+}
+
+// ---- tensor-parallel pair: signals over peer memory ------------------------------
+// A producer kernel that has stored its partial results into the peer GPU's
+// buffer publishes them by writing a sequence number into its CTA's slot of a
+// flag array that also lives in the peer's memory (release at system scope).
+// The consumer kernel on the peer waits, for a bounded time, until all slots
+// carry that number.  The number is (step word in device memory) * 256 + tag,
+// so it grows with every launch and a captured graph can be replayed.
+struct TpSignal {
+  unsigned int* peer_flags;        // producer side: slots in the peer's memory (one per CTA); null = no peer
+  const unsigned int* wait_flags;  // consumer side: slots in local memory the peer writes; null = nothing to wait for
+  int wait_count;
+  unsigned int tag;                // 1..255, distinct per producing launch of a step
+  const unsigned int* epoch;       // device word the host advances every step
+};
+
+__device__ __forceinline__ unsigned int tp_seq(const TpSignal& s) { return *s.epoch * 256u + s.tag; }
+
+// Called by one thread of a CTA after the CTA's peer stores are complete (CTA-wide barrier before it).
+__device__ __forceinline__ void tp_signal(const TpSignal& s) {
+  if (s.peer_flags == nullptr) return;
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(s.peer_flags + blockIdx.x), "r"(tp_seq(s)) : "memory");
+}
+
+// Called by every thread of a CTA; returns after all slots show the sequence number or 2 s have passed
+// (then MDB_STATUS_WAIT_TIMEOUT is raised and the kernel carries on with whatever the buffer holds).
+__device__ __forceinline__ void tp_wait(const TpSignal& s) {
+  if (s.wait_flags == nullptr) return;
+  const unsigned int want = tp_seq(s);
+  for (int i = threadIdx.x; i < s.wait_count; i += blockDim.x) {
+    unsigned long long deadline = 0;
+    for (unsigned int it = 0;; ++it) {
+      unsigned int v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(s.wait_flags + i) : "memory");
+      if (static_cast<int>(v - want) >= 0) break;
+      if ((it & 255u) == 255u) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        if (deadline == 0) deadline = now + 2000000000ull;
+        else if (now > deadline) { report_status(MDB_STATUS_WAIT_TIMEOUT); break; }
+      }
+    }
+  }
+  __syncthreads();
 }
 
 // ---- small numeric helpers ------------------------------------------------

@@ -98,7 +98,13 @@ def rope_table(max_pos: int, head_dim: int, base: float, device) -> torch.Tensor
 class DecoderEngine:
 
     def __init__(self, cfg: DecoderConfig, weights: DecoderWeights, kv_cache: torch.Tensor, max_tokens: int,
-                 max_seqs: int, block_size: int):
+                 max_seqs: int, block_size: int, tp_rank: int = 0, tp_size: int = 1):
+        """``cfg`` and ``weights`` are this rank's shard when ``tp_size`` is 2
+        (see tp.shard_config / tp.shard_weights); ``attach_tp`` then supplies
+        the peer buffers before the first step."""
+        self.tp = None              # TensorParallelPair once attached
+        self.tp_epoch = None        # device word the runner advances every step
+        self.tp_rank, self.tp_size = tp_rank, tp_size
         self.cfg = cfg
         self.w = weights
         self.kv_cache = kv_cache    # [2, L, pages, 256, Hkv, D]
@@ -170,19 +176,19 @@ class DecoderEngine:
         hq, hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         eps = cfg.rms_norm_eps
         skinny = m <= SKINNY_MAX_ROWS
+        if self.tp_size > 1 and self.tp is None:
+            raise RuntimeError("tensor-parallel engine used before attach_tp()")
         x, res = self.x[:m], self.res[:m]
         q, attn, act = self.q[:m], self.attn[:m], self.act[:m]
         pos = positions.reshape(-1)
         slots = ctx.slot_mapping.reshape(-1) if ctx.slot_mapping is not None and ctx.slot_mapping.numel() else None
-        prev = None  # output of the previous layer's down projection: ("bf16", t) or ("parts", t)
+        prev = None  # output of the previous row-parallel projection, see _row_gemm
         for li, lw in enumerate(self.w.layers):
             k_cache, v_cache = self.kv_cache[0, li], self.kv_cache[1, li]
             if prev is None:
                 ops.add_rms_norm(self.embeds[:m], None, lw.input_ln, eps, out=x, residual_out=res)
-            elif prev[0] == "parts":
-                ops.add_rms_norm(None, res, lw.input_ln, eps, partials=prev[1], out=x, residual_out=res)
             else:
-                ops.add_rms_norm(prev[1], res, lw.input_ln, eps, out=x, residual_out=res)
+                self._add_norm(prev, res, lw.input_ln, eps, x)
 
             kb = self.kbuf[:m] if ctx.is_prefill else None
             vb = self.vbuf[:m] if ctx.is_prefill else None
@@ -205,36 +211,76 @@ class DecoderEngine:
                 ops.block_attn_with_kvcache(q.view(bs, self.block_size, hq, d), k_cache, v_cache, ctx.context_lens,
                                             ctx.block_tables, self.scale, nsplit=nsplit, workspace=self.attn_ws,
                                             out=attn.view(bs, self.block_size, hq, d))
-            attn2 = attn.view(m, hq * d)
+            prev = self._row_gemm(0, attn.view(m, hq * d), lw.o, m, li)
+            self._add_norm(prev, res, lw.post_ln, eps, x)
             if skinny:
-                parts = self.partials[:self.ks_o * m * h].view(self.ks_o, m, h)
-                ops.gemm_splitk_partials(attn2, lw.o, self.ks_o, parts)
-                ops.add_rms_norm(None, res, lw.post_ln, eps, partials=parts, out=x, residual_out=res)
                 ops.gateup_swiglu(x, lw.gate_up, out=act)
-                parts = self.partials[:self.ks_down * m * h].view(self.ks_down, m, h)
-                ops.gemm_splitk_partials(act, lw.down, self.ks_down, parts)
-                prev = ("parts", parts)
             else:
-                ho = self.h_out[:m]
-                ops.linear(attn2, lw.o, out=ho)
-                ops.add_rms_norm(ho, res, lw.post_ln, eps, out=x, residual_out=res)
                 gu = self.gu_out[:m]
                 ops.linear(x, lw.gate_up, out=gu)
                 ops.silu_and_mul(gu, out=act)
-                ops.linear(act, lw.down, out=ho)
-                prev = ("bf16", ho)
+            prev = self._row_gemm(1, act, lw.down, m, li)
         out = self.final[:m]
-        if prev[0] == "parts":
-            ops.add_rms_norm(None, res, self.w.final_ln, eps, partials=prev[1], out=out, residual_out=res)
-        else:
-            ops.add_rms_norm(prev[1], res, self.w.final_ln, eps, out=out, residual_out=res)
+        self._add_norm(prev, res, self.w.final_ln, eps, out)
         return out
+
+    # ------------------------------------------------------------------ row-parallel projections
+    def attach_tp(self, pair, epoch_word: torch.Tensor):
+        """Second half of TP = 2 set-up: the peer buffers and the step word."""
+        self.tp, self.tp_epoch = pair, epoch_word
+
+    def _row_gemm(self, which: int, x_in: torch.Tensor, w: torch.Tensor, m: int, li: int):
+        """o_proj (which = 0) or down_proj (1), the reference's RowParallelLinear
+        (nanovllm/layers/linear.py:131-157).  Returns how the following
+        norm finds the result: ("bf16", y) | ("parts", slices) | ("tp", slices,
+        flag slots to wait on, their number, launch tag)."""
+        h = self.cfg.hidden_size
+        ks = self.ks_o if which == 0 else self.ks_down
+        if m <= SKINNY_MAX_ROWS:
+            if self.tp is None:
+                parts = self.partials[:ks * m * h].view(ks, m, h)
+                ops.gemm_splitk_partials(x_in, w, ks, parts)
+                return ("parts", parts)
+            view, mine, theirs = self.tp.o_slices(m) if which == 0 else self.tp.down_slices(m)
+            wait_ptr, signal_ptr = self.tp.flags(which)
+            tag = 2 * li + 1 + which
+            ops.gemm_splitk_partials_tp(x_in, w, ks, mine, theirs, signal_ptr, tag, self.tp_epoch)
+            return ("tp", view, wait_ptr, ops.tp_grid_size(m, h, x_in.shape[1], ks), tag)
+        ho = self.h_out[:m]
+        ops.linear(x_in, w, out=ho)
+        if self.tp_size > 1:
+            # many-row steps (prefill) keep the reference's collective: bf16 partial outputs summed by NCCL
+            torch.distributed.all_reduce(ho)
+        return ("bf16", ho)
+
+    def _add_norm(self, prev, res: torch.Tensor, ln: torch.Tensor, eps: float, out: torch.Tensor):
+        if prev[0] == "parts":
+            ops.add_rms_norm(None, res, ln, eps, partials=prev[1], out=out, residual_out=res)
+        elif prev[0] == "tp":
+            _, view, wait_ptr, count, tag = prev
+            ops.add_rms_norm_tp(view, res, ln, eps, out, res, wait_ptr, count, tag, self.tp_epoch)
+        else:
+            ops.add_rms_norm(prev[1], res, ln, eps, out=out, residual_out=res)
 
     def sample(self, rows: torch.Tensor, temperatures: torch.Tensor, noise=None, seed=None, step: int = 0,
                step_dev=None):
         """LM head + sampler statistics over ``rows`` [m, H]; returns views of
         the internal x0 / confidence buffers."""
         m = rows.shape[0]
-        return ops.lm_head_sample(rows, self.w.lm_head, temperatures, self.block_size, noise=noise, seed=seed,
-                                  step=step, step_dev=step_dev, workspace=self.lm_ws, x0=self.x0[:m],
-                                  conf=self.conf[:m])
+        if self.tp is None:
+            return ops.lm_head_sample(rows, self.w.lm_head, temperatures, self.block_size, noise=noise, seed=seed,
+                                      step=step, step_dev=step_dev, workspace=self.lm_ws, x0=self.x0[:m],
+                                      conf=self.conf[:m])
+        if m > SKINNY_MAX_ROWS:
+            raise NotImplementedError("the tensor-parallel LM head takes at most 64 rows per step")
+        # vocabulary tiles (128 rows) split between the two ranks; records are exchanged, never logits
+        tiles = self.cfg.vocab_size // 128
+        first = (tiles + 1) // 2
+        begin, count = (0, first) if self.tp_rank == 0 else (first, tiles - first)
+        ws, peer_ws = self.tp.lm_workspace()
+        wait_ptr, signal_ptr = self.tp.flags(2)
+        peer_count = tiles - count
+        return ops.lm_head_sample_tp(rows, self.w.lm_head, temperatures, self.block_size, ws, peer_ws, begin, count,
+                                     signal_ptr, wait_ptr, min(peer_count, 148), 2 * len(self.w.layers) + 1,
+                                     self.tp_epoch, self.x0[:m], self.conf[:m], noise=noise, seed=seed, step=step,
+                                     step_dev=step_dev)

@@ -76,8 +76,8 @@ class ModelRunner:
                  weight_seed: int = 20260320, noise: str = "gumbel", noise_seed: int = 0, device: str | None = None):
         if not torch.cuda.is_available():
             raise RuntimeError("ModelRunner needs a CUDA device: the decode path has no CPU implementation")
-        if config.tensor_parallel_size != 1:
-            raise NotImplementedError("this runner drives one GPU; tensor_parallel_size must be 1")
+        if config.tensor_parallel_size not in (1, 2):
+            raise NotImplementedError("tensor_parallel_size must be 1 or 2 (more GPUs serve as request-parallel replicas)")
         if noise not in ("gumbel", "none", "explicit"):
             raise ValueError("noise must be 'gumbel', 'none' or 'explicit'")
         self.config = config
@@ -91,8 +91,21 @@ class ModelRunner:
         self.enforce_eager = config.enforce_eager
         self.device = torch.device(device or f"cuda:{rank}")
         torch.cuda.set_device(self.device)
-        self.dcfg = config.decoder_config
-        self.weights = weights if weights is not None else DecoderWeights.random_init(self.dcfg, weight_seed, self.device)
+        self.full_dcfg = config.decoder_config
+        self.dcfg = self.full_dcfg
+        full = weights if weights is not None else DecoderWeights.random_init(self.full_dcfg, weight_seed, self.device)
+        if self.world_size == 2:
+            # One process per GPU, every rank calling run() with the same requests (the sampler's decisions
+            # are bit-identical on both ranks, so the two schedulers stay in step without a control channel).
+            from .. import tp as tp_mod
+            if not torch.distributed.is_initialized():
+                torch.distributed.init_process_group("nccl", init_method="tcp://127.0.0.1:2333", world_size=2,
+                                                     rank=rank, device_id=self.device)
+            self.dcfg = tp_mod.shard_config(self.full_dcfg, 2)
+            self.weights = tp_mod.shard_weights(full, self.full_dcfg, rank, 2)
+            del full
+        else:
+            self.weights = full
         self.noise = noise
         self.noise_seed = noise_seed
         self.noise_fn = None          # explicit mode: fn(step_index, m, vocab) -> fp32 [m, vocab] CUDA tensor
@@ -102,12 +115,22 @@ class ModelRunner:
         self.max_bs = min(config.max_num_seqs, 512)
         max_tokens = max(config.max_num_batched_tokens + config.max_num_seqs * b, self.max_bs * b)
         max_tokens = min(max_tokens, config.max_model_len * config.max_num_seqs + config.max_num_seqs * b)
-        self.engine = DecoderEngine(self.dcfg, self.weights, self.kv_cache, max_tokens, self.max_bs, b)
+        self.engine = DecoderEngine(self.dcfg, self.weights, self.kv_cache, max_tokens, self.max_bs, b,
+                                    tp_rank=rank if self.world_size == 2 else 0, tp_size=self.world_size)
         self.max_pages = (config.max_model_len + b + self.kvcache_block_size - 1) // self.kvcache_block_size
         self.inputs = _StepInputs(self.max_bs, b, self.max_pages, self.device)
         self.hv = self.inputs.views(self.inputs.host)
         self.hn = {k: v.numpy() for k, v in self.hv.items()}   # numpy views of the pinned buffer
         self.dv = self.inputs.views(self.inputs.dev)
+        self.tp_pair = None
+        if self.world_size == 2:
+            from .. import tp as tp_mod
+            self.tp_pair = tp_mod.TensorParallelPair(rank, self.device, self.dcfg.hidden_size, self.engine.ks_o,
+                                                     self.engine.ks_down,
+                                                     ops.lmhead_workspace_bytes(64, self.dcfg.vocab_size))
+            # word 1 of the step slot is the flag epoch: step index + 1, so that real steps never reuse the
+            # sequence numbers of the warm-up launches made while graphs are captured (epoch 0)
+            self.engine.attach_tp(self.tp_pair, self.dv["step"][1:2])
         # sampler state on the device and its pinned mirror: ids int64 | transfer u8 | counts i32
         n = self.max_bs * b
         self.block_ids = torch.zeros(self.max_bs, b, dtype=torch.int64, device=self.device)
@@ -131,6 +154,9 @@ class ModelRunner:
     def exit(self):
         self.graphs.clear()
         torch.cuda.synchronize(self.device)
+        if self.tp_pair is not None:
+            self.tp_pair.close()
+            self.tp_pair = None
 
     # ------------------------------------------------------------------ memory
     def allocate_kv_cache(self):
@@ -181,6 +207,7 @@ class ModelRunner:
         for i, seq in enumerate(seqs):
             hn["temp"][i] = seq.temperature
         hn["step"][0] = self.step_index
+        hn["step"][1] = self.step_index + 1
         self.inputs.dev.copy_(self.inputs.host, non_blocking=True)
         return int(inp["context_lens"].max())
 
@@ -236,6 +263,10 @@ class ModelRunner:
         eng = self.engine
         if m > eng.max_tokens:
             raise AssertionError("prefill batch exceeds the activation buffers")
+        if self.tp_pair is not None:       # the flag sequence numbers of this step
+            self.hn["step"][0] = self.step_index
+            self.hn["step"][1] = self.step_index + 1
+            self.dv["step"].copy_(self.hv["step"], non_blocking=True)
         ops.gather_rows(self.weights.embed, input_ids, out=eng.embeds[:m])
         for i, seq in enumerate(seqs):
             if seq.inputs_embeds is not None and seq.num_cached_tokens == 0:

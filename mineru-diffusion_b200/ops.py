@@ -388,3 +388,49 @@ def unmask_decide(block_ids: torch.Tensor, x0: torch.Tensor, conf: torch.Tensor,
                                             int(mask_id), float(threshold), int(quota), transfer.data_ptr(),
                                             counts.data_ptr(), _stream()), "mdb_unmask_decide")
     return transfer, counts
+
+
+# -------------------------------------------------------------------------- tensor-parallel pair
+def gemm_splitk_partials_tp(x: torch.Tensor, weight: torch.Tensor, ksplit: int, local_ptr: int, peer_ptr: int,
+                            peer_flags_ptr: int, tag: int, epoch: torch.Tensor) -> None:
+    """Split-k slices of x W^T written to this rank's slice range locally and, over
+    NVLink, in the peer's buffer; then the peer's flag slots are raised."""
+    m, k = x.shape
+    n = weight.shape[0]
+    _lib.check(_lib.lib().mdb_gemm_splitk_partials_tp(x.data_ptr(), _rows(x, "x"), weight.data_ptr(), local_ptr,
+                                                      peer_ptr, m, n, k, ksplit, peer_flags_ptr, tag,
+                                                      epoch.data_ptr(), _stream()), "mdb_gemm_splitk_partials_tp")
+
+
+def tp_grid_size(m: int, n: int, k: int, ksplit: int) -> int:
+    return int(_lib.lib().mdb_tp_grid_size(m, n, k, ksplit))
+
+
+def add_rms_norm_tp(partials: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float,
+                    out: torch.Tensor, residual_out: torch.Tensor, wait_flags_ptr: int, wait_count: int, tag: int,
+                    epoch: torch.Tensor) -> None:
+    """``add_rms_norm`` over [2*S, m, h] slices of both ranks after the peer's flag slots show this launch's number."""
+    m, h = partials.shape[-2], partials.shape[-1]
+    _lib.check(_lib.lib().mdb_add_rmsnorm_tp(None, partials.data_ptr(), partials.shape[0], residual.data_ptr(),
+                                             weight.data_ptr(), float(eps), out.data_ptr(), residual_out.data_ptr(),
+                                             m, h, wait_flags_ptr, wait_count, tag, epoch.data_ptr(), _stream()),
+               "mdb_add_rmsnorm_tp")
+
+
+def lm_head_sample_tp(hidden: torch.Tensor, weight: torch.Tensor, temperatures: torch.Tensor, block: int,
+                      workspace: torch.Tensor, peer_workspace_ptr: int, tile_begin: int, tile_count: int,
+                      peer_flags_ptr: int, wait_flags_ptr: int, wait_count: int, tag: int, epoch: torch.Tensor,
+                      x0: torch.Tensor, conf: torch.Tensor, noise: torch.Tensor | None = None,
+                      seed: int | None = None, step: int = 0, step_dev: torch.Tensor | None = None):
+    """LM head + sampler statistics with the vocabulary split by 128-row tiles between the two ranks."""
+    m, h = hidden.shape
+    vocab = weight.shape[0]
+    mode = 1 if noise is not None else (2 if seed is not None else 0)
+    _lib.check(_lib.lib().mdb_lmhead_sample_tp(hidden.data_ptr(), _rows(hidden, "hidden"), weight.data_ptr(), m, vocab,
+                                               h, temperatures.data_ptr(), block, mode, _ptr(noise),
+                                               int(seed or 0) & 0xFFFFFFFF, int(step) & 0xFFFFFFFF, _ptr(step_dev),
+                                               workspace.data_ptr(), peer_workspace_ptr,
+                                               workspace.numel() * workspace.element_size(), tile_begin, tile_count,
+                                               peer_flags_ptr, wait_flags_ptr, wait_count, tag, epoch.data_ptr(),
+                                               x0.data_ptr(), conf.data_ptr(), _stream()), "mdb_lmhead_sample_tp")
+    return x0, conf

@@ -120,11 +120,16 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     torch.cuda.set_device(device)
     dcfg = pkg.DecoderConfig()
     total_len = VISUAL_ROWS + TEXT_IDS + NEW_TOKENS + BLOCK
-    cfg = pkg.Config(max_num_batched_tokens=4096, max_num_seqs=1, max_model_len=4096, enforce_eager=False,
-                     num_kvcache_blocks=(total_len + 255) // 256 + 1, decoder_config=dcfg)
-    runner = pkg.ModelRunner(cfg, rank=0, weight_seed=WEIGHT_SEED, noise="gumbel", noise_seed=2 + rank, device=device)
+    max_len = max(4096, (total_len + 255) // 256 * 256)
+    cfg = pkg.Config(max_num_batched_tokens=max_len, max_num_seqs=1, max_model_len=max_len, enforce_eager=False,
+                     num_kvcache_blocks=(total_len + 255) // 256 + 1, decoder_config=dcfg,
+                     tensor_parallel_size=args.tp)
+    # tensor-parallel pair: both ranks serve the same request with the same noise; replicas: one request each
+    seed = 2 if args.tp == 2 else 2 + rank
+    runner = pkg.ModelRunner(cfg, rank=rank if args.tp == 2 else 0, weight_seed=WEIGHT_SEED, noise="gumbel",
+                             noise_seed=seed, device=device)
     engine = pkg.LLMEngine(cfg, runner)
-    engine.add_sequence(make_request(pkg, dcfg, seed=2 + rank, device=device))
+    engine.add_sequence(make_request(pkg, dcfg, seed=seed, device=device))
     stream = torch.cuda.current_stream()
 
     # prefill (first denoising pass of the first block) + warm-up decode steps, untimed
@@ -166,7 +171,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     h2d = runner.inputs.nbytes + BLOCK * 8
     d2h = BLOCK * 8 + BLOCK + 4
 
-    roof = measure_dominant_kernel(pkg, runner) if rank == 0 else None
+    roof = measure_dominant_kernel(pkg, runner) if rank == 0 and args.tp == 1 else None
     return dict(tokens=tokens, steps=steps_done, dev_ms=dev_ms, e2e_ms=max(e2e_ms, wall * 1e3), clocks=clocks,
                 h2d=h2d, d2h=d2h, launches=launches_per_step * steps_done, roofline=roof,
                 ctx_end=len(engine.scheduler.running[0]) if engine.scheduler.running else total_len)
@@ -322,14 +327,21 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="config2", choices=["config2", "config4"],
+                    help="config4: one request, 4096 visual rows, 4096 new tokens (the TP=2 vs TP=1 comparison)")
+    ap.add_argument("--tp", type=int, default=1, choices=[1, 2], help="2: the two ranks form one tensor-parallel pair")
     args = ap.parse_args()
+    global VISUAL_ROWS, NEW_TOKENS
+    if args.workload == "config4":
+        VISUAL_ROWS, NEW_TOKENS = 4096, 4096
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     config = {"workload": "config2: full decoder (28 layers, hidden 2048, 16q/8kv heads, vocab 151936), 1 request per "
                           "GPU, 1024 synthetic visual rows + 32 text ids, 1024 new tokens, block 32, threshold 0.9, "
                           "temperature 1.0",
-              "block_size": BLOCK, "requests_per_gpu": 1, "parallelism": f"dp{args.gpus}",
+              "block_size": BLOCK, "requests_per_gpu": 1,
+              "parallelism": f"tp{args.tp}" if args.tp == 2 else f"dp{args.gpus}",
               "l2_policy": "per-step weight traffic (3.4 GB) exceeds L2 (126 MB); no explicit flush"}
 
     if args.impl == "reference":
@@ -350,9 +362,14 @@ def main():
         print(json.dumps(line))
         return
 
+    if args.workload == "config4":
+        config["workload"] = ("config4: full decoder, 1 request, 4096 synthetic visual rows + 32 text ids, 4096 new "
+                              "tokens, block 32, threshold 0.9, temperature 1.0")
     if world > 1:
         torch.distributed.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
     res = run_ours(args, rank, world, local_rank)
+    if args.tp == 2:
+        res["tokens"] = res["tokens"] if rank == 0 else 0      # one request served by the pair: count it once
     tokens, dev_ms, e2e_ms = res["tokens"], res["dev_ms"], res["e2e_ms"]
     dp = importlib.import_module("mineru-diffusion_b200.engine.dp")
     tokens, (dev_ms, e2e_ms), (launches,) = dp.reduce_throughput(tokens, [dev_ms, e2e_ms], [res["launches"]],

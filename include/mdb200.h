@@ -213,6 +213,64 @@ int mdb_gumbel_noise(float* out, int m, int vocab, uint32_t seed, uint32_t step,
 int mdb_unmask_decide(int64_t* block_ids, const int32_t* x0, const float* conf, int bs, int block, int64_t mask_id,
                       float threshold, int quota, uint8_t* transfer_out, int32_t* count_out, mdb_stream_t stream);
 
+/* ---- whole denoising step as one persistent kernel ----------------------------------- */
+
+/* Replaces, for steps of at most 64 rows, everything ModelRunner.run_model does
+ * between the input copies and the sampler (NV/engine/model_runner.py:194-211,
+ * NV/models/sdar.py:141-181, NV/layers/embed_head.py:61-72, NV/layers/sampler.py:
+ * 11-22): embedding rows, every layer, final norm, LM head and sampler
+ * statistics, as ONE cooperative kernel whose TMA producer streams the weights
+ * of all projections back to back.  All pointers are device pointers; the
+ * arrays of per-layer pointers are host arrays of length `layers`.
+ * mdb_fused_step_create encodes the tensor maps and writes the descriptor into
+ * caller-owned device memory of mdb_fused_step_desc_bytes() bytes (blocking
+ * copy; call at set-up).  mdb_fused_step_launch zeroes the barrier word
+ * (grid_bar, the one given at creation) and runs one step; the per-step inputs
+ * are read from the buffers named in the descriptor.  noise_mode 0 or 2. */
+typedef struct {
+  int layers, m, bs, block, hidden, inter, hq, hkv, vocab;
+  int ks_qkv, ks_o, ks_down, nsplit;
+  float eps, softmax_scale;
+  const void* const* w_qkv;
+  const void* const* w_o;
+  const void* const* w_gate_up;
+  const void* const* w_down;
+  const void* const* ln1;
+  const void* const* ln2;
+  const void* const* q_norm;
+  const void* const* k_norm;
+  void* const* k_cache;
+  void* const* v_cache;
+  const void* final_ln;
+  const void* embed_table;
+  int64_t embed_rows;
+  const void* lm_head;
+  void *x, *res, *q, *attn, *act, *final_rows;
+  float* parts;       /* max(ks_qkv*nqkv, ks_o*hidden, ks_down*hidden) * m floats */
+  void* attn_ws;      /* mdb_attn_paged_workspace_bytes(bs, block, hq, nsplit) */
+  const float* rope;
+  int max_pos;
+  const int64_t* ids;
+  const int64_t* positions;
+  const int32_t* slots;
+  const int32_t* ctx_lens;
+  const int32_t* block_table;
+  int table_stride, num_pages;
+  int64_t num_slots;
+  const float* temperatures;
+  int noise_mode;
+  uint32_t seed;
+  const uint32_t* step_dev;
+  void* lm_ws;        /* mdb_lmhead_workspace_bytes(m, vocab) */
+  int32_t* x0;
+  float* conf;
+  uint32_t* grid_bar; /* one word: arrival counter of the kernel's grid barrier */
+} mdb_fused_step_params;
+
+int64_t mdb_fused_step_desc_bytes(void);
+int mdb_fused_step_create(const mdb_fused_step_params* params, void* desc_device);
+int mdb_fused_step_launch(const void* desc_device, uint32_t* grid_bar, int m, mdb_stream_t stream);
+
 /* ---- tensor-parallel pair (TP = 2) -------------------------------------------------- */
 
 /* Replaces dist.all_reduce in RowParallelLinear.forward (NV/layers/linear.py:153-157),

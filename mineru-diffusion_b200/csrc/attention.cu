@@ -156,19 +156,20 @@ __device__ __forceinline__ void attn_tile_step(const uint32_t (&qf)[8][4], uint3
 // ---------------------------------------------------------------------------
 // decode form over the paged cache
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(kAttnWarps * 32)
-attn_block_paged_kernel(const AttnPagedArgs a) {
-  pdl_launch_dependents();
-  pdl_wait();
-  extern __shared__ __align__(128) unsigned char smem_raw[];
-  const uint32_t smem = smem_u32(smem_raw);
-  const int split = blockIdx.x;
+// 128 threads synchronise either as a whole CTA or, inside the fused step kernel where two more warps
+// do other work, on named barrier 1.
+template <bool NAMED>
+__device__ __forceinline__ void attn_sync() {
+  if (NAMED) asm volatile("bar.sync 1, 128;" ::: "memory");
+  else __syncthreads();
+}
+
+// One work item of the decode form: (request, KV head, 64-row block of the packed query rows, key-range split).
+template <bool NAMED>
+__device__ __forceinline__ void attn_paged_item(const AttnPagedArgs& a, uint32_t smem, int split, int kvh, int rb,
+                                                int req) {
   const int group = a.hq / a.hkv;
   const int rows_total = group * a.block;
-  const int row_blocks = (rows_total + kAttnRows - 1) / kAttnRows;
-  const int kvh = blockIdx.y / row_blocks;
-  const int rb = blockIdx.y % row_blocks;
-  const int req = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
 
@@ -231,11 +232,11 @@ attn_block_paged_kernel(const AttnPagedArgs a) {
     } else {
       cp_async_wait<0>();
     }
-    __syncthreads();
+    attn_sync<NAMED>();
     const uint32_t kt = smem + (it & 1) * 2 * kAttnTileBytes;
     const int key0 = kbeg + it * kAttnKeys;
     attn_tile_step(qf, kt, kt + kAttnTileBytes, key0, kend - 1, kend - 1, a.scale_log2, o, m, l);
-    __syncthreads();
+    attn_sync<NAMED>();
   }
 
   // quad-reduce the row sums
@@ -270,18 +271,24 @@ attn_block_paged_kernel(const AttnPagedArgs a) {
   }
 }
 
+__global__ void __launch_bounds__(kAttnWarps * 32)
+attn_block_paged_kernel(const AttnPagedArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const int group = a.hq / a.hkv;
+  const int row_blocks = (group * a.block + kAttnRows - 1) / kAttnRows;
+  attn_paged_item<false>(a, smem_u32(smem_raw), blockIdx.x, blockIdx.y / row_blocks, blockIdx.y % row_blocks,
+                         blockIdx.z);
+}
+
 // Merge the nsplit partials of one (request, head, token) row; one warp per row.
 // Lanes first take one split each (running max and weighted sum across the
 // warp), then every lane accumulates its 4 output columns over the splits
 // with the weights broadcast by shuffle; the O loads are independent.
-__global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    bf16* __restrict__ out, int bs, int block, int hq, int nsplit) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  const int rows = bs * hq * block;
-  if (warp_global >= rows) return;
+__device__ __forceinline__ void attn_combine_row(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                                 bf16* __restrict__ out, int block, int hq, int nsplit,
+                                                 int warp_global, int lane) {
   const int tok = warp_global % block;
   const int head = (warp_global / block) % hq;
   const int req = warp_global / (block * hq);
@@ -324,6 +331,15 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
   o.x = pack_bf16x2(acc[0] * inv, acc[1] * inv);
   o.y = pack_bf16x2(acc[2] * inv, acc[3] * inv);
   *reinterpret_cast<uint2*>(dst) = o;
+}
+
+__global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                    bf16* __restrict__ out, int bs, int block, int hq, int nsplit) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (warp_global >= bs * hq * block) return;
+  attn_combine_row(part_o, part_ml, out, block, hq, nsplit, warp_global, threadIdx.x & 31);
 }
 
 // ---------------------------------------------------------------------------

@@ -136,18 +136,15 @@ add_rmsnorm_kernel(const bf16* __restrict__ x, const float* __restrict__ partial
 // ---------------------------------------------------------------------------
 constexpr int kRopeWarps = 4;
 
-__global__ void __launch_bounds__(kRopeWarps * 32)
-qknorm_rope_commit_kernel(const bf16* __restrict__ qkv, int64_t ld_qkv, const float* __restrict__ partials, int nparts,
-                          const int64_t* __restrict__ positions, const float* __restrict__ rope_table, int max_pos,
-                          const bf16* __restrict__ q_norm_w, const bf16* __restrict__ k_norm_w, float eps,
-                          const int32_t* __restrict__ slot_mapping, bf16* __restrict__ q_out,
-                          bf16* __restrict__ k_out, bf16* __restrict__ v_out, bf16* __restrict__ k_cache,
-                          bf16* __restrict__ v_cache, int64_t num_slots, int m, int hq, int hkv) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const int token = blockIdx.x;
-  const int head = blockIdx.y * kRopeWarps + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
+// One (token, head) of the fused qkv output: per-head RMSNorm for q and k heads, rotary embedding, store of q into
+// q_out and of k / v into the contiguous outputs and/or the paged cache.  Executed by one warp.
+__device__ __forceinline__ void qknorm_rope_commit_warp(
+    int token, int head, int lane, const bf16* __restrict__ qkv, int64_t ld_qkv, const float* __restrict__ partials,
+    int nparts, const int64_t* __restrict__ positions, const float* __restrict__ rope_table, int max_pos,
+    const bf16* __restrict__ q_norm_w, const bf16* __restrict__ k_norm_w, float eps,
+    const int32_t* __restrict__ slot_mapping, bf16* __restrict__ q_out, bf16* __restrict__ k_out,
+    bf16* __restrict__ v_out, bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, int64_t num_slots, int m, int hq,
+    int hkv) {
   const int nheads = hq + 2 * hkv;
   if (head >= nheads) return;
   const int ncols = nheads * kHeadDim;
@@ -227,6 +224,20 @@ qknorm_rope_commit_kernel(const bf16* __restrict__ qkv, int64_t ld_qkv, const fl
     *reinterpret_cast<uint32_t*>(dst) = lo;
     *reinterpret_cast<uint32_t*>(dst + 64) = hi;
   }
+}
+
+__global__ void __launch_bounds__(kRopeWarps * 32)
+qknorm_rope_commit_kernel(const bf16* __restrict__ qkv, int64_t ld_qkv, const float* __restrict__ partials, int nparts,
+                          const int64_t* __restrict__ positions, const float* __restrict__ rope_table, int max_pos,
+                          const bf16* __restrict__ q_norm_w, const bf16* __restrict__ k_norm_w, float eps,
+                          const int32_t* __restrict__ slot_mapping, bf16* __restrict__ q_out,
+                          bf16* __restrict__ k_out, bf16* __restrict__ v_out, bf16* __restrict__ k_cache,
+                          bf16* __restrict__ v_cache, int64_t num_slots, int m, int hq, int hkv) {
+  pdl_launch_dependents();
+  pdl_wait();
+  qknorm_rope_commit_warp(blockIdx.x, blockIdx.y * kRopeWarps + (threadIdx.x >> 5), threadIdx.x & 31, qkv, ld_qkv,
+                          partials, nparts, positions, rope_table, max_pos, q_norm_w, k_norm_w, eps, slot_mapping,
+                          q_out, k_out, v_out, k_cache, v_cache, num_slots, m, hq, hkv);
 }
 
 // ---------------------------------------------------------------------------

@@ -6,5 +6,6 @@
 #include "gemm_skinny.cu"
 #include "gemm_ws.cu"
 #include "gemm_tiled.cu"
+#include "fused_step.cu"
 #include "api_linear.cu"
 #include "tp_p2p.cu"

@@ -16,6 +16,8 @@ embeddings of the first prompt positions, which is what
 """
 from __future__ import annotations
 
+import os
+
 import numpy as np
 import torch
 
@@ -73,7 +75,8 @@ class _StepInputs:
 class ModelRunner:
 
     def __init__(self, config: Config, rank: int = 0, event=None, weights: DecoderWeights | None = None,
-                 weight_seed: int = 20260320, noise: str = "gumbel", noise_seed: int = 0, device: str | None = None):
+                 weight_seed: int = 20260320, noise: str = "gumbel", noise_seed: int = 0, device: str | None = None,
+                 fused_step: bool | None = None):
         if not torch.cuda.is_available():
             raise RuntimeError("ModelRunner needs a CUDA device: the decode path has no CPU implementation")
         if config.tensor_parallel_size not in (1, 2):
@@ -108,6 +111,11 @@ class ModelRunner:
             self.weights = full
         self.noise = noise
         self.noise_seed = noise_seed
+        # one persistent kernel per decode step (steps of at most 64 rows, one GPU); MDB_FUSED_STEP=0/1 overrides
+        if fused_step is None:
+            fused_step = os.environ.get("MDB_FUSED_STEP", "0") == "1"
+        self.fused_step = bool(fused_step)
+        self.fused_desc: dict[tuple[int, int], torch.Tensor] = {}
         self.noise_fn = None          # explicit mode: fn(step_index, m, vocab) -> fp32 [m, vocab] CUDA tensor
         self.step_index = 0
         self.allocate_kv_cache()
@@ -231,6 +239,15 @@ class ModelRunner:
         b = self.block_size
         m = bs * b
         dv, eng = self.dv, self.engine
+        if self.fused_step and self.noise != "explicit" and eng.fused_supported(m):
+            key = (bs, nsplit)
+            if key not in self.fused_desc:
+                if torch.cuda.is_current_stream_capturing():
+                    raise RuntimeError("the one-kernel step must be built before stream capture")
+                self.fused_desc[key] = eng.build_fused_step(
+                    bs, nsplit, dv["ids"], dv["pos"], dv["slots"], dv["ctx"], dv["tab"], dv["temp"],
+                    self.noise_seed if self.noise == "gumbel" else None, dv["step"])
+            return eng.run_fused_step(self.fused_desc[key], m)
         ops.gather_rows(self.weights.embed, dv["ids"][:bs].reshape(-1), out=eng.embeds[:m])
         ctx = Context(False, slot_mapping=dv["slots"][:bs], context_lens=dv["ctx"][:bs],
                       block_tables=dv["tab"][:bs], block_size=b)
@@ -332,6 +349,8 @@ class ModelRunner:
             nsplit = self.graphs[next(x for x in self.graph_bs if x >= bs)][1]
         else:
             nsplit = self.engine.attn_nsplit(bs, self.config.max_model_len)
+        if self.fused_step and self.noise != "explicit" and self.engine.fused_supported(bs * self.block_size):
+            return 2            # the one-kernel step and the unmask rule
         per_layer = 8 + (1 if nsplit > 1 else 0)
         if bs * self.block_size > 64:
             per_layer += 1      # stand-alone SiLU*mul on the tiled path

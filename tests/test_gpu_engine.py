@@ -26,11 +26,11 @@ def _oracle_cfg(c):
                              max_position_embeddings=c.max_position_embeddings)
 
 
-def _make_runner(mdb, dcfg, weights, pages, eager, noise="explicit", max_seqs=4, max_len=1024):
+def _make_runner(mdb, dcfg, weights, pages, eager, noise="explicit", max_seqs=4, max_len=1024, fused=False):
     cfg = mdb.Config(max_num_batched_tokens=2048, max_num_seqs=max_seqs, max_model_len=max_len, enforce_eager=eager,
                      num_kvcache_blocks=pages, decoder_config=dcfg, mask_token_id=500)
     w = mdb.DecoderWeights.from_reference_layout(weights, DEV)
-    return cfg, mdb.ModelRunner(cfg, weights=w, noise=noise)
+    return cfg, mdb.ModelRunner(cfg, weights=w, noise=noise, fused_step=fused)
 
 
 def test_runner_matches_reference_fixture(mdb):
@@ -192,6 +192,44 @@ def test_teacher_forced_agreement(mdb, eager, temperature):
         # dividing by a small temperature magnifies logit differences 20x, so few decisions stay outside
         # the tolerance band; what matters here is that the threshold branch ran and agreed where it must
         assert multi > 0
+    assert mdb._lib.device_status(clear=True) == 0
+
+
+@pytest.mark.parametrize("eager", [True, False])
+def test_one_kernel_step_matches_separate_kernels(mdb, eager):
+    """The persistent one-kernel decode step against the chain of separate
+    kernels: same requests, same counter-based noise, teacher-forced.  The two
+    run the same arithmetic (only the RMSNorm row sum is ordered differently),
+    so sampled tokens must agree and hidden rows stay within a few bf16 steps."""
+    dcfg = _tiny_cfg(mdb, vocab=1024, layers=3)
+    weights = orc.make_weights(_oracle_cfg(dcfg), seed=5)
+    cfg_a, ra = _make_runner(mdb, dcfg, weights, pages=8, eager=eager, noise="gumbel", fused=True)
+    cfg_b, rb = _make_runner(mdb, dcfg, weights, pages=8, eager=eager, noise="gumbel", fused=False)
+    ra.keep_last = rb.keep_last = True
+    gen = torch.Generator().manual_seed(3)
+    sched = mdb.Scheduler(cfg_a)
+    for plen in (150, 40, 260):
+        sp = mdb.SamplingParams(temperature=1.0, max_new_tokens=64, ignore_eos=True)
+        sched.add(mdb.Sequence(torch.randint(0, 490, (plen,), generator=gen).tolist(), sp, denoising_block_size=32,
+                               mask_token_id=500))
+    steps = agree = total = 0
+    worst = 0.0
+    while not sched.is_finished() and steps < 300:
+        seqs, is_prefill = sched.schedule()
+        twins = [_clone_seq(mdb, s) for s in seqs]
+        ra.run(seqs, is_prefill)
+        rb.run(twins, is_prefill)
+        same = ra.last["x0"] == rb.last["x0"]
+        agree += int(same.sum())
+        total += same.numel()
+        worst = max(worst, float((ra.last["hidden"].float() - rb.last["hidden"].float()).abs().max()))
+        assert torch.allclose(ra.last["conf"][same], rb.last["conf"][same], rtol=5e-2)
+        sched.postprocess(seqs)
+        steps += 1
+    assert sched.is_finished()
+    print(f"one-kernel step vs separate kernels (eager={eager}): sampled tokens {agree}/{total}, "
+          f"hidden max-abs {worst:.4f}, steps {steps}")
+    assert agree / total >= 0.99 and worst <= 0.05
     assert mdb._lib.device_status(clear=True) == 0
 
 

@@ -137,8 +137,10 @@ int mdb_gemm_splitk_partials(const void* x, int64_t ldx, const void* w, float* p
                              int ksplit, mdb_stream_t stream);
 
 /* gate_up projection fused with SiLU*mul (NV/models/sdar.py:109-111,
- * NV/layers/activation.py:12-15) for m <= 64: w is [2*inter, k] with gate rows
- * first; act[m, inter] = bf16(silu_fp32(bf16(gate))) * bf16(up). */
+ * NV/layers/activation.py:12-15): w is [2*inter, k] with gate rows first;
+ * act[m, inter] = bf16(silu_fp32(bf16(gate))) * bf16(up).  m <= 64 streams the
+ * weight once (inter % 16 == 0); larger m runs the tcgen05 tile kernel
+ * (inter % 128 == 0, k % 64 == 0). */
 int mdb_gemm_gateup_swiglu(const void* x, int64_t ldx, const void* w_gate_up, void* act, int64_t ld_act, int m,
                            int inter, int k, mdb_stream_t stream);
 

@@ -114,6 +114,18 @@ int mdb_gemm_splitk_partials(const void* x, int64_t ldx, const void* w, float* p
 int mdb_gemm_gateup_swiglu(const void* x, int64_t ldx, const void* w_gate_up, void* act, int64_t ld_act, int m,
                            int inter, int k, mdb_stream_t stream) {
   if (m == 0) return MDB_OK;
+  if (m > 64) {
+    // many rows: tile GEMM on tcgen05 whose weight tile pairs 128 gate rows with their 128 up rows
+    MDB_REQUIRE(x && w_gate_up && act && inter > 0 && k > 0 && ldx >= k && ld_act >= inter, MDB_ERR_ARG);
+    MDB_REQUIRE(mdb_aligned16(x) && mdb_aligned16(w_gate_up) && mdb_aligned16(act), MDB_ERR_ALIGN);
+    MDB_REQUIRE(g_opt_stream_kernel == 0 && tc_supported(kTcSwiglu, m, inter, k, ldx, ld_act), MDB_ERR_UNSUPPORTED);
+    TcArgs a = {};
+    a.m = m; a.n = inter; a.k = k; a.inter = inter;
+    a.y = static_cast<bf16*>(act);
+    a.ldy = ld_act;
+    return launch_tc<kTcSwiglu>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w_gate_up), 2 * inter, a,
+                                static_cast<cudaStream_t>(stream));
+  }
   int rc = check_skinny_common(x, ldx, w_gate_up, m, 2 * inter, k);
   if (rc != MDB_OK) return rc;
   MDB_REQUIRE(act != nullptr && ld_act >= inter, MDB_ERR_ARG);
@@ -163,6 +175,13 @@ int mdb_gemm_bf16(const void* x, int64_t ldx, const void* w, void* y, int64_t ld
     a.y = static_cast<bf16*>(y);
     a.ldy = ldy;
     return launch_skinny<kEpiBf16>(a, 1, st);
+  }
+  if (g_opt_stream_kernel == 0 && m > 64 && tc_supported(kTcBf16, m, n, k, ldx, ldy)) {
+    TcArgs a = {};
+    a.m = m; a.n = n; a.k = k;
+    a.y = static_cast<bf16*>(y);
+    a.ldy = ldy;
+    return launch_tc<kTcBf16>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), n, a, st);
   }
   MDB_REQUIRE(k % kGemmBK == 0 && n % 2 == 0, MDB_ERR_UNSUPPORTED);
   return launch_gemm_tiled(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), static_cast<bf16*>(y), ldy,

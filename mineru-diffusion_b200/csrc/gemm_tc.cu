@@ -1,0 +1,251 @@
+// y = x W^T for many rows (prefill, batched decode) on the 5th-generation tensor
+// cores: persistent CTAs (one per SM), tiles of 128 step rows x 256 weight
+// rows, tcgen05.mma M128 N256 K16 with the activation tile as A and the
+// weight tile as B (both K-major, 128-byte swizzle, staged by TMA through a
+// 4-stage ring of 48 KB), fp32 accumulators in tensor memory, double-buffered
+// (2 x 256 columns = all 512) so the epilogue of a tile overlaps the main loop
+// of the next.  Warp 4 = TMA producer, warp 5 = MMA issue, warps 0-3 =
+// epilogue (tcgen05.ld, one step row per thread).
+//
+// Epilogues: bf16 store; SiLU(gate)*up for weight tiles made of 128 gate rows
+// and their 128 up rows (the thread that owns a step row holds both halves).
+// Tiles are ordered so that consecutive CTAs share a weight tile: it is read
+// from HBM once and served from L2 to the others.
+#include "mdb_common.cuh"
+
+namespace mdb {
+
+enum TcEpilogue { kTcBf16 = 0, kTcSwiglu = 1 };
+
+constexpr int kTcBM = 128, kTcBN = 256, kTcBK = 64;
+constexpr int kTcStages = 4;
+constexpr int kTcABytes = kTcBM * kTcBK * 2;   // 16 KB
+constexpr int kTcBBytes = kTcBN * kTcBK * 2;   // 32 KB
+constexpr int kTcThreads = 192;
+constexpr int kTcSmemBytes = 1024 + kTcStages * (kTcABytes + kTcBBytes) + 256;
+
+struct TcArgs {
+  int m, n, k;        // n = output columns (swiglu: the intermediate size)
+  int tiles_m, tiles_n;
+  int inter;          // swiglu: first up row of the weight
+  bf16* y;
+  int64_t ldy;
+};
+
+template <int EPI>
+__global__ void __launch_bounds__(kTcThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
+  extern __shared__ unsigned char tc_smem_raw[];
+  const uint32_t raw = smem_u32(tc_smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* gen_base = tc_smem_raw + (base - raw);
+  const uint32_t a_tiles = base;
+  const uint32_t b_tiles = base + kTcStages * kTcABytes;
+  const uint32_t bars_off = kTcStages * (kTcABytes + kTcBBytes);
+  const uint32_t bars = base + bars_off;
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * kTcStages;
+  const uint32_t bar_acc_full = bars + 16 * kTcStages, bar_acc_empty = bar_acc_full + 16;
+  volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(gen_base + bars_off + 16 * kTcStages + 32);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles = a.tiles_m * a.tiles_n;
+  const int kchunks = a.k / kTcBK;
+
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kTcStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_acc_full + 8 * b, 1);
+      mbar_init(bar_acc_empty + 8 * b, 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 5) {
+    const uint32_t slot = smem_u32(const_cast<uint32_t*>(&misc[0]));
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = misc[0];
+
+  if (warp == 4) {
+    if (lane == 0) {
+      pdl_wait();   // activations come from the preceding kernel
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+        const int tn = t / a.tiles_m, tm = t % a.tiles_m;   // consecutive CTAs: same weight tile
+        for (int c = 0; c < kchunks; ++c) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1)) { ok = false; break; }
+          const uint32_t full = bar_full + 8 * stage;
+          mbar_arrive_expect_tx(full, kTcABytes + kTcBBytes);
+          tma_load_2d(a_tiles + stage * kTcABytes, &map_x, c * kTcBK, tm * kTcBM, full);
+          const uint32_t bdst = b_tiles + stage * kTcBBytes;
+          if (EPI == kTcSwiglu) {
+            tma_load_2d(bdst, &map_w, c * kTcBK, tn * 128, full);                             // 128 gate rows
+            tma_load_2d(bdst + kTcBBytes / 2, &map_w, c * kTcBK, a.inter + tn * 128, full);   // their up rows
+          } else {
+            tma_load_2d(bdst, &map_w, c * kTcBK, tn * kTcBN, full);
+          }
+          if (++stage == kTcStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) report_status(MDB_STATUS_WAIT_TIMEOUT);
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      // bf16 x bf16 -> fp32, K-major operands, M = 128, N = 256
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kTcBN >> 3) << 17) |
+                             (static_cast<uint32_t>(kTcBM >> 4) << 24);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kTcBN;
+        for (int c = 0; c < kchunks; ++c) {
+          if (!mbar_wait(bar_full + 8 * stage, phase)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t adesc = umma_desc_sw128(a_tiles + stage * kTcABytes);
+          const uint64_t bdesc = umma_desc_sw128(b_tiles + stage * kTcBBytes);
+#pragma unroll
+          for (int k16 = 0; k16 < kTcBK / 16; ++k16)
+            umma_bf16(d_tmem, adesc + 2 * k16, bdesc + 2 * k16, idesc, (c > 0 || k16 > 0) ? 1u : 0u);
+          umma_commit(bar_empty + 8 * stage);
+          if (++stage == kTcStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(bar_acc_full + 8 * acc);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+      if (!ok) report_status(MDB_STATUS_WAIT_TIMEOUT);
+    }
+  } else {
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    pdl_wait();   // the output buffer may still be read by the preceding kernel
+    for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
+      const int tn = t / a.tiles_m, tm = t % a.tiles_m;
+      bool ok = mbar_wait(bar_acc_full + 8 * acc, acc_phase);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) report_status(MDB_STATUS_WAIT_TIMEOUT);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * kTcBN + (static_cast<uint32_t>(32 * warp) << 16);
+      const int row = tm * kTcBM + 32 * warp + lane;
+      if (EPI == kTcBf16) {
+        bf16* dst = a.y + static_cast<int64_t>(row) * a.ldy + tn * kTcBN;
+#pragma unroll 1
+        for (int c = 0; c < kTcBN / 32; ++c) {
+          float v0[16], v1[16];
+          tmem_ld16(taddr + 32 * c, v0);
+          tmem_ld16(taddr + 32 * c + 16, v1);
+          tmem_ld_wait();
+          const int col = tn * kTcBN + 32 * c;
+          if (row < a.m) {
+            if (col + 32 <= a.n) {
+              uint4 o[4];
+              o[0] = make_uint4(pack_bf16x2(v0[0], v0[1]), pack_bf16x2(v0[2], v0[3]), pack_bf16x2(v0[4], v0[5]), pack_bf16x2(v0[6], v0[7]));
+              o[1] = make_uint4(pack_bf16x2(v0[8], v0[9]), pack_bf16x2(v0[10], v0[11]), pack_bf16x2(v0[12], v0[13]), pack_bf16x2(v0[14], v0[15]));
+              o[2] = make_uint4(pack_bf16x2(v1[0], v1[1]), pack_bf16x2(v1[2], v1[3]), pack_bf16x2(v1[4], v1[5]), pack_bf16x2(v1[6], v1[7]));
+              o[3] = make_uint4(pack_bf16x2(v1[8], v1[9]), pack_bf16x2(v1[10], v1[11]), pack_bf16x2(v1[12], v1[13]), pack_bf16x2(v1[14], v1[15]));
+              uint4* d4 = reinterpret_cast<uint4*>(dst + 32 * c);
+              d4[0] = o[0]; d4[1] = o[1]; d4[2] = o[2]; d4[3] = o[3];
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                if (col + i < a.n) dst[32 * c + i] = __float2bfloat16_rn(v0[i]);
+                if (col + 16 + i < a.n) dst[32 * c + 16 + i] = __float2bfloat16_rn(v1[i]);
+              }
+            }
+          }
+        }
+      } else {
+        // columns [0,128) gate, [128,256) up of the same 128 intermediate columns
+        bf16* dst = a.y + static_cast<int64_t>(row) * a.ldy + tn * 128;
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+          float g[16], u[16];
+          tmem_ld16(taddr + 16 * c, g);
+          tmem_ld16(taddr + 128 + 16 * c, u);
+          tmem_ld_wait();
+          if (row < a.m) {
+            uint32_t o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              float r[2];
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const float gt = bf16_round(g[2 * i + e]);
+                const float up = bf16_round(u[2 * i + e]);
+                const float sl = gt * __frcp_rn(1.0f + __expf(-gt));
+                r[e] = bf16_round(sl) * up;
+              }
+              o[i] = pack_bf16x2(r[0], r[1]);
+            }
+            uint4* d4 = reinterpret_cast<uint4*>(dst + 16 * c);
+            d4[0] = make_uint4(o[0], o[1], o[2], o[3]);
+            d4[1] = make_uint4(o[4], o[5], o[6], o[7]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+// Shapes this kernel takes: k a multiple of 64, 16-byte aligned rows; swiglu additionally inter % 128 == 0.
+static bool tc_supported(int epi, int m, int n, int k, int64_t ldx, int64_t ldy) {
+  if (m < 1 || k % kTcBK != 0 || ldx % 8 != 0 || ldy % 8 != 0) return false;
+  if (epi == kTcSwiglu) return n % 128 == 0;
+  return n % 8 == 0;
+}
+
+template <int EPI>
+static int launch_tc(const bf16* x, int64_t ldx, const bf16* w, int w_rows, TcArgs& a, cudaStream_t st) {
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  a.tiles_m = (a.m + kTcBM - 1) / kTcBM;
+  a.tiles_n = (EPI == kTcSwiglu) ? a.n / 128 : (a.n + kTcBN - 1) / kTcBN;
+  CUtensorMap map_x, map_w;
+  if (!get_tensor_map(x, a.m, a.k, ldx, kTcBM, &map_x)) return MDB_ERR_CUDA;
+  if (!get_tensor_map(w, w_rows, a.k, a.k, (EPI == kTcSwiglu) ? 128 : kTcBN, &map_w)) return MDB_ERR_CUDA;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_tc_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes) !=
+        cudaSuccess)
+      return MDB_ERR_CUDA;
+    attr_set = true;
+  }
+  const int tiles = a.tiles_m * a.tiles_n;
+  return mdb_launch(gemm_tc_kernel<EPI>, dim3(tiles < sm_count ? tiles : sm_count), dim3(kTcThreads), kTcSmemBytes, st,
+                    map_x, map_w, a);
+}
+
+}  // namespace mdb

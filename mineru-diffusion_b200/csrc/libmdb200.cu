@@ -5,6 +5,7 @@
 #include "attention.cu"
 #include "gemm_skinny.cu"
 #include "gemm_ws.cu"
+#include "gemm_tc.cu"
 #include "gemm_tiled.cu"
 #include "fused_step.cu"
 #include "api_linear.cu"

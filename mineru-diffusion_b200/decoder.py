@@ -215,7 +215,7 @@ class DecoderEngine:
                                             out=attn.view(bs, self.block_size, hq, d))
             prev = self._row_gemm(0, attn.view(m, hq * d), lw.o, m, li)
             self._add_norm(prev, res, lw.post_ln, eps, x)
-            if skinny:
+            if skinny or (inter % 128 == 0 and h % 64 == 0 and ops.get_option(ops.OPT_STREAM_KERNEL) == 0):
                 ops.gateup_swiglu(x, lw.gate_up, out=act)
             else:
                 gu = self.gu_out[:m]

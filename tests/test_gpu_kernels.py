@@ -216,8 +216,23 @@ def test_gemm_gateup_swiglu(mdb, stream_kernel, m):
     assert float((got == want).float().mean()) >= 0.95
 
 
-@pytest.mark.parametrize("m,n,k", [(65, 384, 256), (200, 4096, 2048), (1088, 2048, 6144), (129, 130, 64)])
-def test_gemm_tiled(mdb, m, n, k):
+@pytest.mark.parametrize("m", [65, 300])
+def test_gemm_gateup_swiglu_many_rows(mdb, m):
+    gen = torch.Generator().manual_seed(m)
+    k, inter = 512, 768
+    x = torch.randn(m, k, generator=gen).to(BF)
+    w = (0.05 * torch.randn(2 * inter, k, generator=gen)).to(BF)
+    want = orc.silu_mul(orc.linear(x, w))
+    got = mdb.ops.gateup_swiglu(x.to(DEV), w.to(DEV)).cpu()
+    tol = want.float().abs() * 2.0 ** -6 + 1e-3 * float(want.float().std())
+    assert bool(((got.float() - want.float()).abs() <= tol).all())
+    assert float((got == want).float().mean()) >= 0.95
+    assert mdb._lib.device_status(clear=True) == 0
+
+
+@pytest.mark.parametrize("m,n,k", [(65, 384, 256), (200, 4096, 2048), (1088, 2048, 6144), (129, 136, 64),
+                                   (2048, 4096, 2048)])
+def test_gemm_tiled(mdb, stream_kernel, m, n, k):
     gen = torch.Generator().manual_seed(m + n)
     x = torch.randn(m, k, generator=gen).to(BF)
     w = (0.02 * torch.randn(n, k, generator=gen)).to(BF)

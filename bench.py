@@ -47,6 +47,7 @@ VISUAL_ROWS = 1024
 TEXT_IDS = 32
 NEW_TOKENS = 1024
 THRESHOLD = 0.9
+REQUESTS = 1
 WEIGHT_SEED = 20260320
 
 
@@ -104,11 +105,12 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------- workload
-def make_request(pkg, dcfg, seed: int, device):
+def make_request(pkg, dcfg, seed: int, device, visual_rows: int | None = None):
     g = torch.Generator().manual_seed(seed)
-    visual = torch.randn(VISUAL_ROWS, dcfg.hidden_size, generator=g).to(torch.bfloat16)
+    rows = VISUAL_ROWS if visual_rows is None else visual_rows
+    visual = torch.randn(rows, dcfg.hidden_size, generator=g).to(torch.bfloat16)
     text = torch.randint(0, 151000, (TEXT_IDS,), generator=g).tolist()
-    ids = [0] * VISUAL_ROWS + text          # the visual positions' ids are never embedded
+    ids = [0] * rows + text                 # the visual positions' ids are never embedded
     sp = pkg.SamplingParams(temperature=1.0, max_new_tokens=NEW_TOKENS, ignore_eos=True, dynamic_threshold=THRESHOLD)
     return pkg.Sequence(ids, sp, denoising_block_size=BLOCK, mask_token_id=151669,
                         inputs_embeds=visual.pin_memory() if device != "cpu" else visual)
@@ -121,19 +123,33 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     dcfg = pkg.DecoderConfig()
     total_len = VISUAL_ROWS + TEXT_IDS + NEW_TOKENS + BLOCK
     max_len = max(4096, (total_len + 255) // 256 * 256)
-    cfg = pkg.Config(max_num_batched_tokens=max_len, max_num_seqs=1, max_model_len=max_len, enforce_eager=False,
-                     num_kvcache_blocks=(total_len + 255) // 256 + 1, decoder_config=dcfg,
+    nreq = REQUESTS
+    if nreq > 1:
+        # config 3: per-request visual rows uniform in [512, 4096]; pages for every request's full length
+        vg = torch.Generator().manual_seed(3 + rank)
+        visual_rows = torch.randint(512, 4097, (nreq,), generator=vg).tolist()
+        pages = sum((v + TEXT_IDS + NEW_TOKENS + BLOCK + 255) // 256 for v in visual_rows) + 2
+        max_len = (4096 + TEXT_IDS + NEW_TOKENS + BLOCK + 255) // 256 * 256
+    else:
+        visual_rows = [VISUAL_ROWS]
+        pages = (total_len + 255) // 256 + 1
+    cfg = pkg.Config(max_num_batched_tokens=max(max_len, 16384 if nreq > 1 else 0), max_num_seqs=nreq,
+                     max_model_len=max_len, enforce_eager=False, num_kvcache_blocks=pages, decoder_config=dcfg,
                      tensor_parallel_size=args.tp)
     # tensor-parallel pair: both ranks serve the same request with the same noise; replicas: one request each
     seed = 2 if args.tp == 2 else 2 + rank
     runner = pkg.ModelRunner(cfg, rank=rank if args.tp == 2 else 0, weight_seed=WEIGHT_SEED, noise="gumbel",
                              noise_seed=seed, device=device)
     engine = pkg.LLMEngine(cfg, runner)
-    engine.add_sequence(make_request(pkg, dcfg, seed=seed, device=device))
+    for i, v in enumerate(visual_rows):
+        engine.add_sequence(make_request(pkg, dcfg, seed=seed + 1000 * i, device=device, visual_rows=v))
     stream = torch.cuda.current_stream()
 
-    # prefill (first denoising pass of the first block) + warm-up decode steps, untimed
+    # prefill (first denoising pass of the first block; several batches when there are many requests)
+    # + warm-up decode steps, untimed
     engine.step()
+    while engine.scheduler.waiting:
+        engine.step()
     for _ in range(args.warmup):
         engine.step()
     torch.cuda.synchronize()
@@ -147,7 +163,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     sampler.start()
     tokens = 0
     steps_done = 0
-    launches_per_step = runner.launches_per_decode_step()
+    launches_per_step = runner.launches_per_decode_step(nreq)
     wall0 = time.perf_counter()
     e_all0 = torch.cuda.Event(enable_timing=True)
     e_all1 = torch.cuda.Event(enable_timing=True)
@@ -168,10 +184,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     runner.step_events = None
     dev_ms = sum(a.elapsed_time(b) for a, b in ev[:steps_done])
     e2e_ms = e_all0.elapsed_time(e_all1)
-    h2d = runner.inputs.nbytes + BLOCK * 8
-    d2h = BLOCK * 8 + BLOCK + 4
+    h2d = runner.inputs.nbytes + nreq * BLOCK * 8
+    d2h = nreq * (BLOCK * 8 + BLOCK + 4)
 
-    roof = measure_dominant_kernel(pkg, runner) if rank == 0 and args.tp == 1 else None
+    roof = measure_dominant_kernel(pkg, runner) if rank == 0 and args.tp == 1 and nreq == 1 else None
     return dict(tokens=tokens, steps=steps_done, dev_ms=dev_ms, e2e_ms=max(e2e_ms, wall * 1e3), clocks=clocks,
                 h2d=h2d, d2h=d2h, launches=launches_per_step * steps_done, roofline=roof,
                 ctx_end=len(engine.scheduler.running[0]) if engine.scheduler.running else total_len)
@@ -327,13 +343,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="config2", choices=["config2", "config4"],
-                    help="config4: one request, 4096 visual rows, 4096 new tokens (the TP=2 vs TP=1 comparison)")
+    ap.add_argument("--workload", default="config2", choices=["config2", "config3", "config4"],
+                    help="config3: 64 concurrent requests, visual rows uniform in [512, 4096], 2048 new tokens each; "
+                         "config4: one request, 4096 visual rows, 4096 new tokens (the TP=2 vs TP=1 comparison)")
     ap.add_argument("--tp", type=int, default=1, choices=[1, 2], help="2: the two ranks form one tensor-parallel pair")
     args = ap.parse_args()
-    global VISUAL_ROWS, NEW_TOKENS
+    global VISUAL_ROWS, NEW_TOKENS, REQUESTS
     if args.workload == "config4":
         VISUAL_ROWS, NEW_TOKENS = 4096, 4096
+    if args.workload == "config3":
+        NEW_TOKENS, REQUESTS = 2048, 64
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -362,6 +381,10 @@ def main():
         print(json.dumps(line))
         return
 
+    if args.workload == "config3":
+        config["workload"] = ("config3: full decoder, 64 concurrent requests on one GPU, visual rows uniform in "
+                              "[512, 4096] + 32 text ids, 2048 new tokens each, block 32, threshold 0.9, temperature 1.0")
+        config["requests_per_gpu"] = 64
     if args.workload == "config4":
         config["workload"] = ("config4: full decoder, 1 request, 4096 synthetic visual rows + 32 text ids, 4096 new "
                               "tokens, block 32, threshold 0.9, temperature 1.0")

@@ -50,8 +50,11 @@ int mdb_version(void);
  * fault isolation).  MDB_OPT_STREAM_KERNEL: 0 = short steps (m <= 64) use the
  * tcgen05/TMA weight-streaming kernel where the shape allows (default), 1 =
  * always the register-streaming kernel.  MDB_OPT_PDL: 1 = kernels are chained
- * with programmatic dependent launch (default), 0 = plain stream order. */
-enum { MDB_OPT_STREAM_KERNEL = 0, MDB_OPT_PDL = 1 };
+ * with programmatic dependent launch (default), 0 = plain stream order.
+ * MDB_OPT_ATTN_KERNEL: which kernel mdb_attn_block_paged runs: 0 = chosen by
+ * the amount of work (default), 1 = the mma.sync kernel, 2 = the tcgen05/TMA
+ * kernel whenever the shape allows (block * hq / hkv <= 64). */
+enum { MDB_OPT_STREAM_KERNEL = 0, MDB_OPT_PDL = 1, MDB_OPT_ATTN_KERNEL = 2 };
 int mdb_set_option(int option, int value);
 /* Measurement aid: registers a device buffer (uint64 count, then (kernel,
  * event, globaltimer ns) triples) that block 0 of the traced kernels appends

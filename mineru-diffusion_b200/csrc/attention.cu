@@ -21,6 +21,7 @@ constexpr int kAttnRows = kAttnWarps * 16;  // query rows per CTA
 constexpr int kAttnKeys = 64;               // keys per tile
 constexpr int kAttnTileBytes = kAttnKeys * kHeadDim * 2;
 constexpr int kAttnSmemBytes = 2 /*stages*/ * 2 /*K,V*/ * kAttnTileBytes;  // 64 KB
+constexpr int64_t kAttnTcMinTiles = 2048;    // 128-key tiles (upper bound) from which the tcgen05 kernel is chosen
 
 struct AttnPagedArgs {
   const bf16* q;
@@ -34,6 +35,10 @@ struct AttnPagedArgs {
   int table_stride, block, hq, hkv, num_pages, nsplit;
   float scale_log2;  // softmax_scale * log2(e)
 };
+
+// tcgen05/TMA form of the paged kernel (defined with the other tcgen05 kernels)
+static bool attn_tc_supported(int block, int hq, int hkv, float softmax_scale);
+static int attn_tc_launch(const AttnPagedArgs& a, int bs, cudaStream_t st);
 
 struct AttnStairArgs {
   const bf16* q;
@@ -494,7 +499,15 @@ int mdb_attn_block_paged(const void* q, const void* k_cache, const void* v_cache
   const int row_blocks = (rows_total + kAttnRows - 1) / kAttnRows;
   dim3 grid(nsplit, hkv * row_blocks, bs);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int rc = mdb_launch(attn_block_paged_kernel, grid, dim3(kAttnWarps * 32), kAttnSmemBytes, st, a);
+  // The tensor-core pipeline pays off once there are enough 128-key tiles to keep every SM streaming;
+  // the context lengths live on the device, so the page-table width stands in for them.
+  const int64_t tiles_bound = static_cast<int64_t>(bs) * hkv * table_stride * (kPage / 128);
+  const bool want_tc = g_opt_attn_kernel == 2 || (g_opt_attn_kernel == 0 && tiles_bound >= kAttnTcMinTiles);
+  int rc;
+  if (want_tc && attn_tc_supported(block, hq, hkv, softmax_scale))
+    rc = attn_tc_launch(a, bs, st);
+  else
+    rc = mdb_launch(attn_block_paged_kernel, grid, dim3(kAttnWarps * 32), kAttnSmemBytes, st, a);
   if (rc != MDB_OK) return rc;
   if (nsplit > 1) {
     const int rows = bs * hq * block;

@@ -1,0 +1,563 @@
+// Block attention over the paged KV cache on the 5th-generation tensor cores,
+// for steps with many requests or long prefixes (the decode form of
+// flash_attn_with_kvcache as nanovllm/layers/sdar_attention.py:50-55 calls it).
+//
+// One work unit = (request, KV head, key-range split).  Its query rows are the
+// block's tokens times the query heads that share the KV head (at most 64),
+// row = token * group + head_in_group.  Persistent CTAs, one per SM, walk the
+// units; inside a CTA
+//   warp 4   TMA producer: the Q tile (3-D box: 64 channels x group x block)
+//            and 128-key K and V tiles straight out of the cache pages
+//            ([tokens, hkv*128] seen as a matrix, boxes of 128 rows x 64
+//            channels, 128-byte swizzle) into a 2-stage K ring and a 3-stage V ring;
+//   warp 5   MMA issue: S = Q K^T (tcgen05.mma M128 N128, both operands
+//            K-major) into one of two S buffers in tensor memory, one tile
+//            ahead of O += P V (P from shared memory K-major, V as the
+//            MN-major B operand: the cache rows are the K dimension);
+//   warps 0-1 softmax: one query row per thread, S read with tcgen05.ld,
+//            running maximum kept lazily (O is rescaled only when a row's
+//            maximum grows by more than 2^8, so the common tile needs no
+//            read-modify-write of O), P rounded to bf16 into shared memory,
+//            and at the end of the unit O/l to the output or the (max, sum,
+//            O) partial to the split workspace.
+// The MMA reads 128 operand rows although at most 64 are query rows; the rows
+// above them are whatever follows in shared memory, and only feed accumulator
+// lanes nobody reads.  Tensor memory: S0 | S1 | O, 128 columns each.
+//
+// HBM traffic is K and V once: 512 bytes per key per KV head.
+#include "mdb_common.cuh"
+
+namespace mdb {
+
+constexpr int kAtKeys = 128;                          // keys per tile
+constexpr int kAtHalfBytes = kAtKeys * 128;           // [128 keys][64 channels] bf16
+constexpr int kAtTileBytes = 2 * kAtHalfBytes;        // 32 KB
+constexpr int kAtKStages = 2, kAtVStages = 3;
+constexpr int kAtRows = 64;                           // query rows held per unit
+constexpr int kAtQBytes = 2 * kAtRows * 128;          // 16 KB: two channel halves of [64 rows][128 B]
+constexpr int kAtPBytes = 2 * kAtRows * 128;          // 16 KB: two key halves of [64 rows][128 B]
+constexpr int kAtThreads = 192;
+constexpr int kAtSoftmaxWarps = 2;
+constexpr int kAtOffQ = 0;
+constexpr int kAtOffP = kAtOffQ + 2 * kAtQBytes;
+constexpr int kAtOffK = kAtOffP + 2 * kAtPBytes;
+constexpr int kAtOffV = kAtOffK + kAtKStages * kAtTileBytes;
+constexpr int kAtOffBars = kAtOffV + kAtVStages * kAtTileBytes;
+constexpr int kAtSmemBytes = 1024 + kAtOffBars + 256;
+constexpr float kAtRescaleStep = 8.0f;                // log2 units a row maximum may lag behind
+
+// barrier slots (8 bytes each) after the tiles
+enum {
+  kAtBarQFull = 0, kAtBarQEmpty = 2, kAtBarKFull = 4, kAtBarKEmpty = 6, kAtBarVFull = 8, kAtBarVEmpty = 11,
+  kAtBarSFull = 14, kAtBarSEmpty = 16, kAtBarPFull = 18, kAtBarPEmpty = 20, kAtBarOFull = 22, kAtBarOEmpty = 23,
+  kAtBarCount = 24
+};
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+        "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+        "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])),
+        "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])),
+        "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+        "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])),
+        "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])),
+        "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// V tile as the B operand of O += P V: N = channels (contiguous, 64 per 128-byte
+// row, the two channel halves kAtHalfBytes apart), K = keys (rows of 128 bytes,
+// groups of 8 keys 1024 bytes apart).
+__device__ __forceinline__ uint64_t umma_desc_sw128_mn(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFF);
+  d |= static_cast<uint64_t>(kAtHalfBytes >> 4) << 16;          // leading byte offset: next 64 channels
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;                  // stride byte offset: next 8 keys
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+// The part of the unit list every role derives the same way.
+struct AtUnit {
+  int req, kvh, split, kbeg, kend, ntiles;
+};
+__device__ __forceinline__ AtUnit at_unit(const AttnPagedArgs& a, int u) {
+  AtUnit w;
+  w.split = u % a.nsplit;
+  w.kvh = (u / a.nsplit) % a.hkv;
+  w.req = u / (a.nsplit * a.hkv);
+  const int ctx = a.ctx_lens[w.req];
+  int chunk = ctx > 0 ? (ctx + a.nsplit - 1) / a.nsplit : 0;
+  chunk = (chunk + kAtKeys - 1) / kAtKeys * kAtKeys;
+  w.kbeg = w.split * chunk;
+  w.kend = min(ctx, w.kbeg + chunk);
+  w.ntiles = w.kend > w.kbeg ? (w.kend - w.kbeg + kAtKeys - 1) / kAtKeys : 0;
+  return w;
+}
+
+// A ring position: stage index and the parity of the phase that stage is in.
+struct AtRing {
+  int stage = 0;
+  uint32_t phase = 0;
+  __device__ __forceinline__ void advance(int stages) {
+    if (++stage == stages) { stage = 0; phase ^= 1; }
+  }
+};
+
+__global__ void __launch_bounds__(kAtThreads, 1)
+attn_paged_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                     const __grid_constant__ CUtensorMap map_v, const AttnPagedArgs a, const int units) {
+  extern __shared__ unsigned char at_smem_raw[];
+  const uint32_t raw = smem_u32(at_smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* gen_base = at_smem_raw + (base - raw);
+  const uint32_t bars = base + kAtOffBars;
+  auto bar = [&](int slot) { return bars + 8u * static_cast<uint32_t>(slot); };
+  volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(gen_base + kAtOffBars + 8 * kAtBarCount);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int group = a.hq / a.hkv;
+  const int rows_total = group * a.block;
+
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kAtBarCount; ++s) {
+      const bool by_softmax = (s >= kAtBarSEmpty && s < kAtBarSEmpty + 2) || (s >= kAtBarPFull && s < kAtBarPFull + 2) ||
+                              s == kAtBarOEmpty;
+      mbar_init(bar(s), by_softmax ? kAtSoftmaxWarps : 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 5) {
+    const uint32_t slot = smem_u32(const_cast<uint32_t*>(&misc[0]));
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = misc[0];
+  const uint32_t tmem_o = tmem_base + 256;
+  pdl_wait();   // q and the cache rows of this step come from the preceding kernel
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      AtRing kr, vr, qr;
+      uint32_t pend_k = 0, pend_v = 0, pend_q = 0;          // stages with a copy in flight, and the parity it completes
+      uint32_t par_k = 0, par_v = 0, par_q = 0;
+      bool ok = true;
+      auto load_tile = [&](const CUtensorMap* map, uint32_t tiles0, int full0, int empty0, int stages, AtRing& r,
+                           uint32_t& pend, uint32_t& par, int kvh, int token_row) {
+        if (!mbar_wait(bar(empty0 + r.stage), r.phase ^ 1)) return false;
+        const uint32_t full = bar(full0 + r.stage);
+        const uint32_t dst = tiles0 + r.stage * kAtTileBytes;
+        mbar_arrive_expect_tx(full, kAtTileBytes);
+        tma_load_2d(dst, map, kvh * kHeadDim, token_row, full);
+        tma_load_2d(dst + kAtHalfBytes, map, kvh * kHeadDim + 64, token_row, full);
+        pend |= 1u << r.stage;
+        par = (par & ~(1u << r.stage)) | (r.phase << r.stage);
+        r.advance(stages);
+        return true;
+      };
+      for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+        const AtUnit w = at_unit(a, u);
+        if (w.ntiles == 0) continue;
+        if (!mbar_wait(bar(kAtBarQEmpty + qr.stage), qr.phase ^ 1)) { ok = false; break; }
+        {
+          const uint32_t full = bar(kAtBarQFull + qr.stage);
+          const uint32_t dst = base + kAtOffQ + qr.stage * kAtQBytes;
+          mbar_arrive_expect_tx(full, static_cast<uint32_t>(rows_total) * 256u);
+          tma_load_3d(dst, &map_q, 0, w.kvh * group, w.req * a.block, full);
+          tma_load_3d(dst + kAtRows * 128, &map_q, 64, w.kvh * group, w.req * a.block, full);
+          pend_q |= 1u << qr.stage;
+          par_q = (par_q & ~(1u << qr.stage)) | (qr.phase << qr.stage);
+          qr.advance(2);
+        }
+        auto token_row = [&](int tile) {
+          const int key0 = w.kbeg + tile * kAtKeys;
+          int page = a.block_table[static_cast<int64_t>(w.req) * a.table_stride + key0 / kPage];
+          if (page < 0 || page >= a.num_pages) {
+            report_status(MDB_STATUS_BAD_PAGE);
+            page = 0;
+          }
+          return page * kPage + key0 % kPage;
+        };
+        // in the order the MMA warp needs them: K0 K1 V0 K2 V1 ...
+        for (int j = 0; j < w.ntiles && ok; ++j) {
+          if (j == 0) ok = load_tile(&map_k, base + kAtOffK, kAtBarKFull, kAtBarKEmpty, kAtKStages, kr, pend_k, par_k, w.kvh, token_row(0));
+          if (ok && j + 1 < w.ntiles)
+            ok = load_tile(&map_k, base + kAtOffK, kAtBarKFull, kAtBarKEmpty, kAtKStages, kr, pend_k, par_k, w.kvh, token_row(j + 1));
+          if (ok) ok = load_tile(&map_v, base + kAtOffV, kAtBarVFull, kAtBarVEmpty, kAtVStages, vr, pend_v, par_v, w.kvh, token_row(j));
+        }
+      }
+      if (!ok) {
+        report_status(MDB_STATUS_WAIT_TIMEOUT);
+        // let the copies already issued land before the CTA gives its shared memory back
+        for (int s = 0; s < kAtKStages; ++s) if (pend_k >> s & 1) mbar_wait(bar(kAtBarKFull + s), par_k >> s & 1);
+        for (int s = 0; s < kAtVStages; ++s) if (pend_v >> s & 1) mbar_wait(bar(kAtBarVFull + s), par_v >> s & 1);
+        for (int s = 0; s < 2; ++s) if (pend_q >> s & 1) mbar_wait(bar(kAtBarQFull + s), par_q >> s & 1);
+      }
+    }
+  } else if (warp == 5) {
+    // ----------------------------------------------------------------- MMA issue
+    if (lane == 0) {
+      // bf16 x bf16 -> fp32, M = 128, N = 128; bit 16 set: B operand MN-major
+      const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kAtKeys >> 3) << 17) |
+                               (static_cast<uint32_t>(128 >> 4) << 24);
+      const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
+                               (static_cast<uint32_t>(kHeadDim >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+      AtRing kr, vr, qr, sr, pr;        // sr: S buffer the next S = Q K^T goes to; pr: P buffer of the next P V
+      uint32_t o_phase = 0;             // parity of the o_empty phase to wait for
+      bool ok = true;
+      for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+        const AtUnit w = at_unit(a, u);
+        if (w.ntiles == 0) continue;
+        if (!mbar_wait(bar(kAtBarQFull + qr.stage), qr.phase)) { ok = false; break; }
+        const uint32_t q_tile = base + kAtOffQ + qr.stage * kAtQBytes;
+        auto issue_s = [&](int j) {
+          if (!mbar_wait(bar(kAtBarKFull + kr.stage), kr.phase)) return false;
+          if (!mbar_wait(bar(kAtBarSEmpty + sr.stage), sr.phase ^ 1)) return false;
+          tc_fence_after();
+          const uint32_t k_tile = base + kAtOffK + kr.stage * kAtTileBytes;
+          const uint32_t d_tmem = tmem_base + sr.stage * kAtKeys;
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint64_t adesc = umma_desc_sw128(q_tile + (kk >> 2) * (kAtRows * 128)) + 2 * (kk & 3);
+            const uint64_t bdesc = umma_desc_sw128(k_tile + (kk >> 2) * kAtHalfBytes) + 2 * (kk & 3);
+            umma_bf16(d_tmem, adesc, bdesc, idesc_s, kk > 0 ? 1u : 0u);
+          }
+          umma_commit(bar(kAtBarKEmpty + kr.stage));
+          umma_commit(bar(kAtBarSFull + sr.stage));
+          if (j == w.ntiles - 1) umma_commit(bar(kAtBarQEmpty + qr.stage));
+          kr.advance(kAtKStages);
+          sr.advance(2);
+          return true;
+        };
+        ok = issue_s(0);
+        for (int j = 0; j < w.ntiles && ok; ++j) {
+          if (j + 1 < w.ntiles) ok = issue_s(j + 1);
+          if (!ok) break;
+          if (!mbar_wait(bar(kAtBarVFull + vr.stage), vr.phase)) { ok = false; break; }
+          if (!mbar_wait(bar(kAtBarPFull + pr.stage), pr.phase)) { ok = false; break; }
+          if (j == 0) {
+            // the previous unit's accumulator must have been read out
+            if (!mbar_wait(bar(kAtBarOEmpty), o_phase ^ 1)) { ok = false; break; }
+            o_phase ^= 1;
+          }
+          tc_fence_after();
+          const uint32_t p_tile = base + kAtOffP + pr.stage * kAtPBytes;
+          const uint32_t v_tile = base + kAtOffV + vr.stage * kAtTileBytes;
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint64_t adesc = umma_desc_sw128(p_tile + (kk >> 2) * (kAtRows * 128)) + 2 * (kk & 3);
+            const uint64_t bdesc = umma_desc_sw128_mn(v_tile + kk * 2048);
+            umma_bf16(tmem_o, adesc, bdesc, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(bar(kAtBarVEmpty + vr.stage));
+          umma_commit(bar(kAtBarPEmpty + pr.stage));
+          if (j == w.ntiles - 1) umma_commit(bar(kAtBarOFull));
+          vr.advance(kAtVStages);
+          pr.advance(2);
+        }
+        qr.advance(2);
+      }
+      if (!ok) report_status(MDB_STATUS_WAIT_TIMEOUT);
+    }
+  } else if (warp < kAtSoftmaxWarps) {
+    // ------------------------------------------------------------------- softmax
+    const int row = 32 * warp + lane;
+    const bool row_valid = row < rows_total;
+    const int tok = row_valid ? row / group : 0;
+    const int head_in_group = row_valid ? row % group : 0;
+    const uint32_t lane_field = static_cast<uint32_t>(32 * warp) << 16;
+    AtRing sr, pr, vr;                 // positions of the tile being handled in the S, P and V rings
+    uint32_t prev_p_stage = 0, prev_p_phase = 0;   // P ring position of the previous tile (its P V frees O for a rescale)
+    uint32_t o_phase = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+      const AtUnit w = at_unit(a, u);
+      const int head = w.kvh * group + head_in_group;
+      const int64_t prow = ((static_cast<int64_t>(w.req) * a.nsplit + w.split) * a.hq + head) * a.block + tok;
+      bf16* out_row = a.out + ((static_cast<int64_t>(w.req) * a.block + tok) * a.hq + head) * kHeadDim;
+      if (w.ntiles == 0) {
+        if (row_valid) {
+          if (a.nsplit == 1) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) reinterpret_cast<uint4*>(out_row)[c] = make_uint4(0u, 0u, 0u, 0u);
+          } else {
+            float4* po = reinterpret_cast<float4*>(a.part_o + prow * kHeadDim);
+#pragma unroll
+            for (int c = 0; c < 32; ++c) po[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float2*>(a.part_ml + prow * 2) = make_float2(-INFINITY, 0.f);
+          }
+        }
+        continue;
+      }
+      float m_ref = -INFINITY, l = 0.f;
+      for (int j = 0; j < w.ntiles; ++j) {
+        ok = mbar_wait(bar(kAtBarSFull + sr.stage), sr.phase);
+        if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t s_addr = tmem_base + sr.stage * kAtKeys + lane_field;
+        const int key0 = w.kbeg + j * kAtKeys;
+        const int nvalid = min(kAtKeys, w.kend - key0);      // >= 1
+        // pass 1: row maximum of the raw scores
+        float mx = -INFINITY;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          float s[32];
+          tmem_ld32(s_addr + 32 * c, s);
+          tmem_ld_wait();
+          if (nvalid < 32 * (c + 1)) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) if (32 * c + i >= nvalid) s[i] = -INFINITY;
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, s[i]);
+        }
+        if (!row_valid) mx = 0.f;                             // rows past the block hold whatever the tile held
+        const float m_tile = mx * a.scale_log2;
+        const bool grow = m_tile > m_ref + kAtRescaleStep || m_ref == -INFINITY;
+        if (__any_sync(0xffffffffu, grow)) {
+          const float m_new = fmaxf(m_ref, m_tile);
+          const float f = m_ref == -INFINITY ? 0.f : ex2_approx(m_ref - m_new);
+          l *= f;
+          if (j > 0) {
+            // O is quiet once the previous tile's P V has completed
+            ok = mbar_wait(bar(kAtBarPEmpty + prev_p_stage), prev_p_phase);
+            if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+              float o[32];
+              tmem_ld32(tmem_o + lane_field + 32 * c, o);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] *= f;
+              tmem_st32(tmem_o + lane_field + 32 * c, o);
+            }
+            tmem_st_wait();
+          }
+          m_ref = m_new;
+        }
+        // the P buffer of this tile is free once the P V two tiles back has completed
+        ok = mbar_wait(bar(kAtBarPEmpty + pr.stage), pr.phase ^ 1);
+        if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+        // pass 2: P = 2^(s * scale - m_ref), bf16, into the K-major swizzled P tile
+        const uint32_t p_row = base + kAtOffP + pr.stage * kAtPBytes + row * 128;
+        float lsum = 0.f;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          float s[32];
+          tmem_ld32(s_addr + 32 * c, s);
+          tmem_ld_wait();
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float p0 = ex2_approx(fmaf(s[i], a.scale_log2, -m_ref));
+            float p1 = ex2_approx(fmaf(s[i + 1], a.scale_log2, -m_ref));
+            if (32 * c + i >= nvalid) p0 = 0.f;
+            if (32 * c + i + 1 >= nvalid) p1 = 0.f;
+            lsum += p0 + p1;
+            pk[i >> 1] = pack_bf16x2(p0, p1);
+          }
+          // 32 keys = four 16-byte chunks of the key half (c >> 1), chunk index 4 * (c & 1) + q
+          const uint32_t half_base = p_row + (c >> 1) * (kAtRows * 128);
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const uint32_t chunk = static_cast<uint32_t>(4 * (c & 1) + q4) ^ static_cast<uint32_t>(row & 7);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(half_base + (chunk << 4)), "r"(pk[4 * q4]),
+                         "r"(pk[4 * q4 + 1]), "r"(pk[4 * q4 + 2]), "r"(pk[4 * q4 + 3])
+                         : "memory");
+          }
+        }
+        l += lsum;
+        // S buffer read twice, now free for the tile after next
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(kAtBarSEmpty + sr.stage));
+        if (nvalid < kAtKeys) {
+          // stale cache rows past the context end must not reach O through 0 * (Inf or NaN): clear them in V
+          ok = mbar_wait(bar(kAtBarVFull + vr.stage), vr.phase);
+          if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+          const uint32_t v_tile = base + kAtOffV + vr.stage * kAtTileBytes;
+          for (int r = nvalid + row; r < kAtKeys; r += 32 * kAtSoftmaxWarps) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+              for (int c = 0; c < 8; ++c)
+                asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(v_tile + h * kAtHalfBytes + r * 128 + c * 16),
+                             "r"(0u)
+                             : "memory");
+          }
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(kAtBarPFull + pr.stage));
+        prev_p_stage = pr.stage;
+        prev_p_phase = pr.phase;
+        sr.advance(2);
+        pr.advance(2);
+        vr.advance(kAtVStages);
+      }
+      if (!ok) break;
+      // ------------------------------------------------------------- unit epilogue
+      ok = mbar_wait(bar(kAtBarOFull), o_phase);
+      if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+      o_phase ^= 1;
+      tc_fence_after();
+      if (a.nsplit == 1) {
+        const float inv = l > 0.f ? 1.0f / l : 0.f;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          float o[32];
+          tmem_ld32(tmem_o + lane_field + 32 * c, o);
+          tmem_ld_wait();
+          if (row_valid) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4)
+              reinterpret_cast<uint4*>(out_row + 32 * c)[q4] =
+                  make_uint4(pack_bf16x2(o[8 * q4] * inv, o[8 * q4 + 1] * inv), pack_bf16x2(o[8 * q4 + 2] * inv, o[8 * q4 + 3] * inv),
+                             pack_bf16x2(o[8 * q4 + 4] * inv, o[8 * q4 + 5] * inv), pack_bf16x2(o[8 * q4 + 6] * inv, o[8 * q4 + 7] * inv));
+          }
+        }
+      } else {
+        float4* po = reinterpret_cast<float4*>(a.part_o + prow * kHeadDim);
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          float o[32];
+          tmem_ld32(tmem_o + lane_field + 32 * c, o);
+          tmem_ld_wait();
+          if (row_valid) {
+#pragma unroll
+            for (int q4 = 0; q4 < 8; ++q4) po[8 * c + q4] = make_float4(o[4 * q4], o[4 * q4 + 1], o[4 * q4 + 2], o[4 * q4 + 3]);
+          }
+        }
+        if (row_valid) *reinterpret_cast<float2*>(a.part_ml + prow * 2) = make_float2(m_ref, l);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(kAtBarOEmpty));
+    }
+    if (!ok && lane == 0) report_status(MDB_STATUS_WAIT_TIMEOUT);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+// ---- host side ---------------------------------------------------------------
+struct QMapKey {
+  const void* ptr;
+  int64_t tokens;
+  int hq, group, block;
+  bool operator==(const QMapKey& o) const {
+    return ptr == o.ptr && tokens == o.tokens && hq == o.hq && group == o.group && block == o.block;
+  }
+};
+struct QMapKeyHash {
+  size_t operator()(const QMapKey& k) const {
+    return reinterpret_cast<size_t>(k.ptr) ^ static_cast<size_t>(k.tokens) * 0x9e3779b97f4a7c15ull ^
+           static_cast<size_t>(k.hq * 131 + k.group * 17 + k.block);
+  }
+};
+
+// Tensor map of q [tokens, hq, 128] bf16 read in boxes of 64 channels x group heads x block tokens.
+static bool get_q_tensor_map(const void* ptr, int64_t tokens, int hq, int group, int block, CUtensorMap* out) {
+  static std::mutex mu;
+  static std::unordered_map<QMapKey, CUtensorMap, QMapKeyHash> cache;
+  const QMapKey key{ptr, tokens, hq, group, block};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return true;
+  }
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (enc == nullptr) return false;
+  CUtensorMap m;
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(kHeadDim), static_cast<cuuint64_t>(hq), static_cast<cuuint64_t>(tokens)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(kHeadDim) * 2, static_cast<cuuint64_t>(hq) * kHeadDim * 2};
+  const cuuint32_t box[3] = {64u, static_cast<cuuint32_t>(group), static_cast<cuuint32_t>(block)};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  if (enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (cache.size() > 1024) cache.clear();
+  cache.emplace(key, m);
+  *out = m;
+  return true;
+}
+
+static bool attn_tc_supported(int block, int hq, int hkv, float softmax_scale) {
+  if (hkv <= 0 || hq % hkv != 0) return false;
+  const int group = hq / hkv;
+  return group * block <= kAtRows && block <= 256 && group <= 256 && softmax_scale > 0.f;
+}
+
+static int attn_tc_launch(const AttnPagedArgs& a, int bs, cudaStream_t st) {
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  CUtensorMap map_q, map_k, map_v;
+  const int64_t cache_rows = static_cast<int64_t>(a.num_pages) * kPage;
+  if (!get_q_tensor_map(a.q, static_cast<int64_t>(bs) * a.block, a.hq, a.hq / a.hkv, a.block, &map_q)) return MDB_ERR_CUDA;
+  if (!get_tensor_map(a.k_cache, cache_rows, a.hkv * kHeadDim, a.hkv * kHeadDim, kAtKeys, &map_k)) return MDB_ERR_CUDA;
+  if (!get_tensor_map(a.v_cache, cache_rows, a.hkv * kHeadDim, a.hkv * kHeadDim, kAtKeys, &map_v)) return MDB_ERR_CUDA;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(attn_paged_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAtSmemBytes) != cudaSuccess)
+      return MDB_ERR_CUDA;
+    attr_set = true;
+  }
+  const int64_t units = static_cast<int64_t>(bs) * a.hkv * a.nsplit;
+  if (units > (1 << 30)) return MDB_ERR_UNSUPPORTED;
+  const int grid = units < sm_count ? static_cast<int>(units) : sm_count;
+  return mdb_launch(attn_paged_tc_kernel, dim3(grid), dim3(kAtThreads), kAtSmemBytes, st, map_q, map_k, map_v, a,
+                    static_cast<int>(units));
+}
+
+}  // namespace mdb

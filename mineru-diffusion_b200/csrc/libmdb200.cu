@@ -6,6 +6,7 @@
 #include "gemm_skinny.cu"
 #include "gemm_ws.cu"
 #include "gemm_tc.cu"
+#include "attention_tc.cu"
 #include "gemm_tiled.cu"
 #include "fused_step.cu"
 #include "api_linear.cu"

@@ -255,7 +255,16 @@ def test_gemm_rejects_bad_arguments(mdb):
 
 
 # --------------------------------------------------------------------- block attention over the paged cache
-def _paged_case(seed, bs, block, hq, hkv, prefix_lens, pages_extra=3):
+@pytest.fixture(params=["mma", "tc"])
+def attn_kernel(request, mdb):
+    """Runs a test once per block-attention kernel: the mma.sync one and the
+    tcgen05/TMA one (which takes over where block * hq / hkv <= 64)."""
+    mdb.ops.set_option(mdb.ops.OPT_ATTN_KERNEL, 1 if request.param == "mma" else 2)
+    yield request.param
+    mdb.ops.set_option(mdb.ops.OPT_ATTN_KERNEL, 0)
+
+
+def _paged_case(seed, bs, block, hq, hkv, prefix_lens, pages_extra=3, poison=False):
     gen = torch.Generator().manual_seed(seed)
     ctx = [p + block if p >= 0 else 0 for p in prefix_lens]
     need = [(c + 255) // 256 for c in ctx]
@@ -265,6 +274,9 @@ def _paged_case(seed, bs, block, hq, hkv, prefix_lens, pages_extra=3):
     table = torch.full((bs, width), -1, dtype=torch.int32)
     kc = torch.zeros(num_pages, 256, hkv, 128, dtype=BF)
     vc = torch.zeros_like(kc)
+    if poison:      # slots no context covers hold what uninitialised memory may hold
+        kc.fill_(float("nan"))
+        vc.fill_(float("inf"))
     at = 0
     for r in range(bs):
         for j in range(need[r]):
@@ -279,9 +291,9 @@ def _paged_case(seed, bs, block, hq, hkv, prefix_lens, pages_extra=3):
     return q, kc, vc, torch.tensor(ctx, dtype=torch.int32), table
 
 
-@pytest.mark.parametrize("hq,hkv", [(16, 2), (16, 8), (8, 4)])
+@pytest.mark.parametrize("hq,hkv", [(16, 2), (16, 8), (8, 4), (4, 4)])
 @pytest.mark.parametrize("nsplit", [1, 3, 16])
-def test_attn_paged_config1(mdb, hq, hkv, nsplit):
+def test_attn_paged_config1(mdb, attn_kernel, hq, hkv, nsplit):
     """BASELINE config 1 (decode form): batch 4, prefix lengths uniform in
     [256, 2048] (seed 1), block 32, head_dim 128, 256-token pages in a
     permuted page table."""
@@ -297,11 +309,12 @@ def test_attn_paged_config1(mdb, hq, hkv, nsplit):
     _status_clean(mdb)
 
 
-@pytest.mark.parametrize("block", [8, 16, 64])
-def test_attn_paged_edges(mdb, block):
-    # prefix 0 (context = the block only), a request with context 0 (padding row), page-straddling lengths
-    prefix = [0, -1, 250, 513]
-    q, kc, vc, ctx, table = _paged_case(7, 4, block, 16, 8, prefix)
+@pytest.mark.parametrize("block", [8, 16, 32, 64])
+def test_attn_paged_edges(mdb, attn_kernel, block):
+    # prefix 0 (context = the block only), a request with context 0 (padding row), page-straddling lengths,
+    # contexts that end inside a key tile with NaN / Inf in the cache slots behind them
+    prefix = [0, -1, 250, 513, 1000, 128 - block, 256 - block]
+    q, kc, vc, ctx, table = _paged_case(7, len(prefix), block, 16, 8, prefix, poison=True)
     want = orc.attn_paged(q, kc, vc, ctx, table, 128 ** -0.5)
     for nsplit in (1, 4):
         got = mdb.ops.block_attn_with_kvcache(q.to(DEV), kc.to(DEV), vc.to(DEV), ctx.to(DEV), table.to(DEV),
@@ -311,7 +324,7 @@ def test_attn_paged_edges(mdb, block):
     _status_clean(mdb)
 
 
-def test_attn_paged_properties_at_full_size(mdb):
+def test_attn_paged_properties_at_full_size(mdb, attn_kernel):
     """BASELINE config 3 shape (64 requests, contexts up to ~6K, 8 KV heads):
     too big for the CPU oracle, checked through invariants instead."""
     gen = torch.Generator(device=DEV).manual_seed(3)

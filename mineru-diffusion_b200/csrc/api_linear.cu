@@ -15,7 +15,7 @@ struct LmHeadLayout {
 LmHeadLayout lmhead_layout(int m, int vocab) {
   LmHeadLayout l;
   const bool streaming = m <= 64;
-  l.nparts = streaming ? (vocab + 31) / 32 : (vocab + kScanCols - 1) / kScanCols;
+  l.nparts = streaming ? (vocab + 31) / 32 : (vocab + kTcBN - 1) / kTcBN;   // many rows: one record per 256-column tile
   l.off_i = align256(l.nparts * m * 16);
   l.off_logits = l.off_i + align256(l.nparts * m * 4);
   l.total = l.off_logits + (streaming ? 0 : align256(static_cast<int64_t>(m) * vocab * 2));
@@ -242,10 +242,34 @@ int mdb_lmhead_sample(const void* hidden, int64_t ld_hidden, const void* w, int 
     if (rc != MDB_OK) return rc;
     return finalize_sampler(a.part_f, a.part_i, vocab / 32, m, x0_out, conf_out, st);
   }
+  if (g_opt_stream_kernel == 0 && noise_mode != 1 && tc_supported(kTcLmHead, m, vocab, h, ld_hidden, 0)) {
+    // many rows: tcgen05 tile GEMM whose epilogue reduces each 256-column tile to a sampler record
+    TcArgs a = {};
+    a.m = m; a.n = vocab; a.k = h;
+    a.temperatures = temperatures;
+    a.block = block;
+    a.noise_mode = noise_mode;
+    a.seed = seed; a.step = step;
+    a.step_dev = step_dev;
+    a.part_f = reinterpret_cast<float4*>(ws);
+    a.part_i = reinterpret_cast<int*>(ws + lay.off_i);
+    int rc = launch_tc<kTcLmHead>(static_cast<const bf16*>(hidden), ld_hidden, static_cast<const bf16*>(w), vocab, a, st);
+    if (rc != MDB_OK) return rc;
+    return finalize_sampler(a.part_f, a.part_i, a.tiles_n, m, x0_out, conf_out, st);
+  }
   MDB_REQUIRE(h % kGemmBK == 0 && vocab % 2 == 0, MDB_ERR_UNSUPPORTED);
   bf16* logits = reinterpret_cast<bf16*>(ws + lay.off_logits);
-  int rc = launch_gemm_tiled(static_cast<const bf16*>(hidden), ld_hidden, static_cast<const bf16*>(w), logits, vocab, m,
-                             vocab, h, st);
+  int rc;
+  if (g_opt_stream_kernel == 0 && tc_supported(kTcBf16, m, vocab, h, ld_hidden, vocab)) {
+    TcArgs a = {};
+    a.m = m; a.n = vocab; a.k = h;
+    a.y = logits;
+    a.ldy = vocab;
+    rc = launch_tc<kTcBf16>(static_cast<const bf16*>(hidden), ld_hidden, static_cast<const bf16*>(w), vocab, a, st);
+  } else {
+    rc = launch_gemm_tiled(static_cast<const bf16*>(hidden), ld_hidden, static_cast<const bf16*>(w), logits, vocab, m,
+                           vocab, h, st);
+  }
   if (rc != MDB_OK) return rc;
   return scan_logits(logits, vocab, m, vocab, temperatures, block, noise_mode, noise, seed, step, step_dev, ws, x0_out,
                      conf_out, st);

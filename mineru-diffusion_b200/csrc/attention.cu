@@ -21,7 +21,7 @@ constexpr int kAttnRows = kAttnWarps * 16;  // query rows per CTA
 constexpr int kAttnKeys = 64;               // keys per tile
 constexpr int kAttnTileBytes = kAttnKeys * kHeadDim * 2;
 constexpr int kAttnSmemBytes = 2 /*stages*/ * 2 /*K,V*/ * kAttnTileBytes;  // 64 KB
-constexpr int64_t kAttnTcMinTiles = 2048;    // 128-key tiles (upper bound) from which the tcgen05 kernel is chosen
+constexpr int64_t kAttnTcMinTiles = 0;       // 128-key tiles (upper bound) from which the tcgen05 kernel is chosen: measured no slower at any size
 
 struct AttnPagedArgs {
   const bf16* q;

@@ -43,7 +43,7 @@ constexpr int kAtOffP = kAtOffQ + 2 * kAtQBytes;
 constexpr int kAtOffK = kAtOffP + 2 * kAtPBytes;
 constexpr int kAtOffV = kAtOffK + kAtKStages * kAtTileBytes;
 constexpr int kAtOffBars = kAtOffV + kAtVStages * kAtTileBytes;
-constexpr int kAtSmemBytes = 1024 + kAtOffBars + 256;
+constexpr int kAtSmemBytes = 1024 + kAtOffBars + 256 + 1024;   // + barriers and tensor-memory slot + request ranks
 constexpr float kAtRescaleStep = 8.0f;                // log2 units a row maximum may lag behind
 
 // barrier slots (8 bytes each) after the tiles
@@ -60,7 +60,7 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 // 32 lanes x 32 consecutive fp32 columns
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
   uint32_t r[32];
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -110,15 +110,28 @@ __device__ __forceinline__ uint64_t umma_desc_sw128_mn(uint32_t smem_addr) {
   return d;
 }
 
-// The part of the unit list every role derives the same way.
+// The unit list every role walks the same way.  Requests are ranked by context
+// length (longest first; the ranks sit in shared memory) and the ranked units
+// are dealt to the CTAs in alternating direction, wave by wave, so that every
+// CTA gets about the same number of key tiles however ragged the batch is.
+constexpr int kAtMaxRanked = 512;   // batches above this are walked in request order
 struct AtUnit {
   int req, kvh, split, kbeg, kend, ntiles;
+  bool valid;
 };
-__device__ __forceinline__ AtUnit at_unit(const AttnPagedArgs& a, int u) {
+__device__ __forceinline__ AtUnit at_unit(const AttnPagedArgs& a, const uint16_t* order, int bs, int units, int wave) {
   AtUnit w;
-  w.split = u % a.nsplit;
-  w.kvh = (u / a.nsplit) % a.hkv;
-  w.req = u / (a.nsplit * a.hkv);
+  const int G = static_cast<int>(gridDim.x), c = static_cast<int>(blockIdx.x);
+  const int p = wave * G + ((wave & 1) ? G - 1 - c : c);
+  w.valid = p < units;
+  w.ntiles = 0;
+  w.req = w.kvh = w.split = w.kbeg = w.kend = 0;
+  if (!w.valid) return w;
+  const int per_req = a.hkv * a.nsplit;
+  const int ranked = p / per_req, rem = p % per_req;
+  w.req = bs <= kAtMaxRanked ? static_cast<int>(order[ranked]) : ranked;
+  w.kvh = rem / a.nsplit;
+  w.split = rem % a.nsplit;
   const int ctx = a.ctx_lens[w.req];
   int chunk = ctx > 0 ? (ctx + a.nsplit - 1) / a.nsplit : 0;
   chunk = (chunk + kAtKeys - 1) / kAtKeys * kAtKeys;
@@ -139,7 +152,7 @@ struct AtRing {
 
 __global__ void __launch_bounds__(kAtThreads, 1)
 attn_paged_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                     const __grid_constant__ CUtensorMap map_v, const AttnPagedArgs a, const int units) {
+                     const __grid_constant__ CUtensorMap map_v, const AttnPagedArgs a, const int bs, const int units) {
   extern __shared__ unsigned char at_smem_raw[];
   const uint32_t raw = smem_u32(at_smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -147,12 +160,26 @@ attn_paged_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   const uint32_t bars = base + kAtOffBars;
   auto bar = [&](int slot) { return bars + 8u * static_cast<uint32_t>(slot); };
   volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(gen_base + kAtOffBars + 8 * kAtBarCount);
+  uint16_t* order = reinterpret_cast<uint16_t*>(gen_base + kAtOffBars + 256);
+  const int waves = (units + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int group = a.hq / a.hkv;
   const int rows_total = group * a.block;
 
   pdl_launch_dependents();
+  if (bs <= kAtMaxRanked) {
+    // context lengths are step inputs, not written by the kernels this one is chained to
+    for (int r = threadIdx.x; r < bs; r += kAtThreads) {
+      const int mine = a.ctx_lens[r];
+      int rank = 0;
+      for (int o = 0; o < bs; ++o) {
+        const int other = a.ctx_lens[o];
+        rank += (other > mine || (other == mine && o < r)) ? 1 : 0;
+      }
+      order[rank] = static_cast<uint16_t>(r);
+    }
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < kAtBarCount; ++s) {
       const bool by_softmax = (s >= kAtBarSEmpty && s < kAtBarSEmpty + 2) || (s >= kAtBarPFull && s < kAtBarPFull + 2) ||
@@ -193,8 +220,8 @@ attn_paged_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         r.advance(stages);
         return true;
       };
-      for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
-        const AtUnit w = at_unit(a, u);
+      for (int wave = 0; wave < waves && ok; ++wave) {
+        const AtUnit w = at_unit(a, order, bs, units, wave);
         if (w.ntiles == 0) continue;
         if (!mbar_wait(bar(kAtBarQEmpty + qr.stage), qr.phase ^ 1)) { ok = false; break; }
         {
@@ -243,8 +270,8 @@ attn_paged_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       AtRing kr, vr, qr, sr, pr;        // sr: S buffer the next S = Q K^T goes to; pr: P buffer of the next P V
       uint32_t o_phase = 0;             // parity of the o_empty phase to wait for
       bool ok = true;
-      for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
-        const AtUnit w = at_unit(a, u);
+      for (int wave = 0; wave < waves && ok; ++wave) {
+        const AtUnit w = at_unit(a, order, bs, units, wave);
         if (w.ntiles == 0) continue;
         if (!mbar_wait(bar(kAtBarQFull + qr.stage), qr.phase)) { ok = false; break; }
         const uint32_t q_tile = base + kAtOffQ + qr.stage * kAtQBytes;
@@ -308,8 +335,9 @@ attn_paged_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     uint32_t prev_p_stage = 0, prev_p_phase = 0;   // P ring position of the previous tile (its P V frees O for a rescale)
     uint32_t o_phase = 0;
     bool ok = true;
-    for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
-      const AtUnit w = at_unit(a, u);
+    for (int wave = 0; wave < waves && ok; ++wave) {
+      const AtUnit w = at_unit(a, order, bs, units, wave);
+      if (!w.valid) continue;
       const int head = w.kvh * group + head_in_group;
       const int64_t prow = ((static_cast<int64_t>(w.req) * a.nsplit + w.split) * a.hq + head) * a.block + tok;
       bf16* out_row = a.out + ((static_cast<int64_t>(w.req) * a.block + tok) * a.hq + head) * kHeadDim;
@@ -335,20 +363,25 @@ attn_paged_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         const uint32_t s_addr = tmem_base + sr.stage * kAtKeys + lane_field;
         const int key0 = w.kbeg + j * kAtKeys;
         const int nvalid = min(kAtKeys, w.kend - key0);      // >= 1
-        // pass 1: row maximum of the raw scores
-        float mx = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          float s[32];
-          tmem_ld32(s_addr + 32 * c, s);
-          tmem_ld_wait();
-          if (nvalid < 32 * (c + 1)) {
+        // the whole score row into registers, then the S buffer goes back to the MMA warp
+        float s[kAtKeys];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) if (32 * c + i >= nvalid) s[i] = -INFINITY;
-          }
+        for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + 32 * c, s + 32 * c);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(kAtBarSEmpty + sr.stage));
+        if (nvalid < kAtKeys) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, s[i]);
+          for (int i = 0; i < kAtKeys; ++i) if (i >= nvalid) s[i] = -INFINITY;   // also replaces NaN from stale rows
         }
+        float mx0 = fmaxf(s[0], s[1]), mx1 = fmaxf(s[2], s[3]);
+#pragma unroll
+        for (int i = 4; i < kAtKeys; i += 4) {
+          mx0 = fmaxf(mx0, fmaxf(s[i], s[i + 1]));
+          mx1 = fmaxf(mx1, fmaxf(s[i + 2], s[i + 3]));
+        }
+        float mx = fmaxf(mx0, mx1);
         if (!row_valid) mx = 0.f;                             // rows past the block hold whatever the tile held
         const float m_tile = mx * a.scale_log2;
         const bool grow = m_tile > m_ref + kAtRescaleStep || m_ref == -INFINITY;
@@ -374,42 +407,30 @@ attn_paged_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           }
           m_ref = m_new;
         }
+        // P = 2^(s * scale - m_ref) rounded to bf16; a masked key gives 2^-inf = 0
+        uint32_t pk[kAtKeys / 2];
+        float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < kAtKeys; i += 2) {
+          const float p0 = ex2_approx(fmaf(s[i], a.scale_log2, -m_ref));
+          const float p1 = ex2_approx(fmaf(s[i + 1], a.scale_log2, -m_ref));
+          l0 += p0;
+          l1 += p1;
+          pk[i >> 1] = pack_bf16x2(p0, p1);
+        }
+        l += l0 + l1;
         // the P buffer of this tile is free once the P V two tiles back has completed
         ok = mbar_wait(bar(kAtBarPEmpty + pr.stage), pr.phase ^ 1);
         if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-        // pass 2: P = 2^(s * scale - m_ref), bf16, into the K-major swizzled P tile
+        // K-major swizzled P tile: 16-byte chunk q of key half h holds keys 64 h + 8 q .. + 7
         const uint32_t p_row = base + kAtOffP + pr.stage * kAtPBytes + row * 128;
-        float lsum = 0.f;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          float s[32];
-          tmem_ld32(s_addr + 32 * c, s);
-          tmem_ld_wait();
-          uint32_t pk[16];
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float p0 = ex2_approx(fmaf(s[i], a.scale_log2, -m_ref));
-            float p1 = ex2_approx(fmaf(s[i + 1], a.scale_log2, -m_ref));
-            if (32 * c + i >= nvalid) p0 = 0.f;
-            if (32 * c + i + 1 >= nvalid) p1 = 0.f;
-            lsum += p0 + p1;
-            pk[i >> 1] = pack_bf16x2(p0, p1);
-          }
-          // 32 keys = four 16-byte chunks of the key half (c >> 1), chunk index 4 * (c & 1) + q
-          const uint32_t half_base = p_row + (c >> 1) * (kAtRows * 128);
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            const uint32_t chunk = static_cast<uint32_t>(4 * (c & 1) + q4) ^ static_cast<uint32_t>(row & 7);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(half_base + (chunk << 4)), "r"(pk[4 * q4]),
-                         "r"(pk[4 * q4 + 1]), "r"(pk[4 * q4 + 2]), "r"(pk[4 * q4 + 3])
-                         : "memory");
-          }
+        for (int q = 0; q < 16; ++q) {
+          const uint32_t chunk = static_cast<uint32_t>(q & 7) ^ static_cast<uint32_t>(row & 7);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + (q >> 3) * (kAtRows * 128) + (chunk << 4)),
+                       "r"(pk[4 * q]), "r"(pk[4 * q + 1]), "r"(pk[4 * q + 2]), "r"(pk[4 * q + 3])
+                       : "memory");
         }
-        l += lsum;
-        // S buffer read twice, now free for the tile after next
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(kAtBarSEmpty + sr.stage));
         if (nvalid < kAtKeys) {
           // stale cache rows past the context end must not reach O through 0 * (Inf or NaN): clear them in V
           ok = mbar_wait(bar(kAtBarVFull + vr.stage), vr.phase);
@@ -556,7 +577,7 @@ static int attn_tc_launch(const AttnPagedArgs& a, int bs, cudaStream_t st) {
   const int64_t units = static_cast<int64_t>(bs) * a.hkv * a.nsplit;
   if (units > (1 << 30)) return MDB_ERR_UNSUPPORTED;
   const int grid = units < sm_count ? static_cast<int>(units) : sm_count;
-  return mdb_launch(attn_paged_tc_kernel, dim3(grid), dim3(kAtThreads), kAtSmemBytes, st, map_q, map_k, map_v, a,
+  return mdb_launch(attn_paged_tc_kernel, dim3(grid), dim3(kAtThreads), kAtSmemBytes, st, map_q, map_k, map_v, a, bs,
                     static_cast<int>(units));
 }
 

@@ -8,14 +8,18 @@
 // epilogue (tcgen05.ld, one step row per thread).
 //
 // Epilogues: bf16 store; SiLU(gate)*up for weight tiles made of 128 gate rows
-// and their 128 up rows (the thread that owns a step row holds both halves).
+// and their 128 up rows (the thread that owns a step row holds both halves);
+// LM head + sampler: the thread that owns a step row turns its 256 logits of
+// the vocabulary tile into one (max, sum-exp, best noisy value, its logit, its
+// index) record, so logits never reach memory (nanovllm/layers/sampler.py:11-29
+// on top of the LM head of nanovllm/models/sdar.py).
 // Tiles are ordered so that consecutive CTAs share a weight tile: it is read
 // from HBM once and served from L2 to the others.
 #include "mdb_common.cuh"
 
 namespace mdb {
 
-enum TcEpilogue { kTcBf16 = 0, kTcSwiglu = 1 };
+enum TcEpilogue { kTcBf16 = 0, kTcSwiglu = 1, kTcLmHead = 2 };
 
 constexpr int kTcBM = 128, kTcBN = 256, kTcBK = 64;
 constexpr int kTcStages = 4;
@@ -30,6 +34,14 @@ struct TcArgs {
   int inter;          // swiglu: first up row of the weight
   bf16* y;
   int64_t ldy;
+  // LM head + sampler
+  const float* temperatures;   // per request
+  int block;                   // step rows per request
+  int noise_mode;              // 0 none, 2 counter-based Gumbel (explicit noise arrays take the materialising path)
+  uint32_t seed, step;
+  const uint32_t* step_dev;
+  float4* part_f;              // [tiles_n][m] (max, sum exp, best noisy value, its logit)
+  int* part_i;                 // [tiles_n][m] index of the best noisy value
 };
 
 template <int EPI>
@@ -171,7 +183,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             }
           }
         }
-      } else {
+      } else if (EPI == kTcSwiglu) {
         // columns [0,128) gate, [128,256) up of the same 128 intermediate columns
         bf16* dst = a.y + static_cast<int64_t>(row) * a.ldy + tn * 128;
 #pragma unroll 1
@@ -200,6 +212,46 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           }
         }
       }
+      if (EPI == kTcLmHead) {
+        const bool live = row < a.m;
+        const float temp = a.temperatures[(live ? row : 0) / a.block];
+        const uint32_t step = a.step + (a.step_dev != nullptr ? *a.step_dev : 0u);
+        float mx = -INFINITY, se = 0.f, bv = -INFINITY, bl = 0.f;
+        int bi = 0x7fffffff;
+#pragma unroll 1
+        for (int c = 0; c < kTcBN / 32; ++c) {
+          float v0[16], v1[16];
+          tmem_ld16(taddr + 32 * c, v0);
+          tmem_ld16(taddr + 32 * c + 16, v1);
+          tmem_ld_wait();
+          const int col0 = tn * kTcBN + 32 * c;
+          if (col0 >= a.n) break;            // uniform: the last vocabulary tile may be partly outside
+          float lg[32];
+          float cmax = -INFINITY;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float acc_v = i < 16 ? v0[i] : v1[i - 16];
+            const bool in = col0 + i < a.n;
+            lg[i] = in ? __fdiv_rn(bf16_round(acc_v), temp) : -INFINITY;
+            cmax = fmaxf(cmax, lg[i]);
+            if (in) {
+              float noisy = lg[i];
+              if (a.noise_mode == 2) noisy += gumbel_noise(a.seed, step, row, col0 + i);
+              if (noisy > bv) { bv = noisy; bl = lg[i]; bi = col0 + i; }   // ascending columns: first maximum kept
+            }
+          }
+          const float nm = fmaxf(mx, cmax);
+          float add = 0.f;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) add += __expf(lg[i] - nm);          // exp(-inf) = 0 for columns outside
+          se = (mx == -INFINITY ? 0.f : se * __expf(mx - nm)) + add;
+          mx = nm;
+        }
+        if (live) {
+          a.part_f[static_cast<int64_t>(tn) * a.m + row] = make_float4(mx, se, bv, bl);
+          a.part_i[static_cast<int64_t>(tn) * a.m + row] = bi;
+        }
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
@@ -217,7 +269,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
 // Shapes this kernel takes: k a multiple of 64, 16-byte aligned rows; swiglu additionally inter % 128 == 0.
 static bool tc_supported(int epi, int m, int n, int k, int64_t ldx, int64_t ldy) {
-  if (m < 1 || k % kTcBK != 0 || ldx % 8 != 0 || ldy % 8 != 0) return false;
+  if (m < 1 || k % kTcBK != 0 || ldx % 8 != 0) return false;
+  if (epi == kTcLmHead) return true;
+  if (ldy % 8 != 0) return false;
   if (epi == kTcSwiglu) return n % 128 == 0;
   return n % 8 == 0;
 }

@@ -428,11 +428,16 @@ def test_logits_sample_golden(mdb):
         assert int(counts.sum()) == int(g[p + "count"])
 
 
-@pytest.mark.parametrize("m,block", [(32, 32), (64, 32), (16, 8), (128, 32)])
+@pytest.mark.parametrize("m,block,v", [(32, 32, 4096), (64, 32, 4096), (16, 8, 4096), (128, 32, 4096),
+                                       (320, 32, 4096), (160, 32, 1000)])
 @pytest.mark.parametrize("mode", ["none", "explicit", "counter"])
-def test_lmhead_sample(mdb, stream_kernel, m, block, mode):
+def test_lmhead_sample(mdb, stream_kernel, m, block, v, mode):
+    """Short steps: weight-streaming kernels with the sampler in the epilogue.
+    Many rows (m > 64): the tcgen05 tile GEMM with the sampler epilogue, also
+    with a partial last row tile (320) and a partial last vocabulary tile
+    (1000); explicit noise arrays go through materialised logits."""
     gen = torch.Generator().manual_seed(m)
-    h, v = 256, 4096
+    h = 256
     hidden = torch.randn(m, h, generator=gen).to(BF)
     w = (0.05 * torch.randn(v, h, generator=gen)).to(BF)
     temps = torch.tensor([1.0, 0.5, 0.2, 2.0] * (m // block))[:m // block].contiguous()

@@ -4,8 +4,10 @@
 // weight tile as B (both K-major, 128-byte swizzle, staged by TMA through a
 // 4-stage ring of 48 KB), fp32 accumulators in tensor memory, double-buffered
 // (2 x 256 columns = all 512) so the epilogue of a tile overlaps the main loop
-// of the next.  Warp 4 = TMA producer, warp 5 = MMA issue, warps 0-3 =
-// epilogue (tcgen05.ld, one step row per thread).
+// of the next.  Warps 0-3 = epilogue (tcgen05.ld, one step row per thread),
+// then the TMA producer warp and the MMA issue warp.  The LM-head form has 16
+// epilogue warps (four per 32-lane quarter of tensor memory, 64 columns
+// each): its per-logit work would otherwise outlast the main loop.
 //
 // Epilogues: bf16 store; SiLU(gate)*up for weight tiles made of 128 gate rows
 // and their 128 up rows (the thread that owns a step row holds both halves);
@@ -25,8 +27,11 @@ constexpr int kTcBM = 128, kTcBN = 256, kTcBK = 64;
 constexpr int kTcStages = 4;
 constexpr int kTcABytes = kTcBM * kTcBK * 2;   // 16 KB
 constexpr int kTcBBytes = kTcBN * kTcBK * 2;   // 32 KB
-constexpr int kTcThreads = 192;
-constexpr int kTcSmemBytes = 1024 + kTcStages * (kTcABytes + kTcBBytes) + 256;
+constexpr int kTcLmEpiWarps = 16;
+constexpr int kTcLmRecBytes = 2 * kTcLmEpiWarps * 32 * 5 * 4;    // two buffers of per-warp sampler records
+constexpr int kTcSmemBytes = 1024 + kTcStages * (kTcABytes + kTcBBytes) + 256 + kTcLmRecBytes;
+__host__ __device__ constexpr int tc_epi_warps(int epi) { return epi == 2 ? kTcLmEpiWarps : 4; }
+__host__ __device__ constexpr int tc_threads(int epi) { return (tc_epi_warps(epi) + 2) * 32; }
 
 struct TcArgs {
   int m, n, k;        // n = output columns (swiglu: the intermediate size)
@@ -45,7 +50,7 @@ struct TcArgs {
 };
 
 template <int EPI>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(tc_threads(EPI), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
   extern __shared__ unsigned char tc_smem_raw[];
   const uint32_t raw = smem_u32(tc_smem_raw);
@@ -60,6 +65,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(gen_base + bars_off + 16 * kTcStages + 32);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int kEpiWarps = tc_epi_warps(EPI);
+  constexpr int kProducerWarp = kEpiWarps, kMmaWarp = kEpiWarps + 1;
   const int tiles = a.tiles_m * a.tiles_n;
   const int kchunks = a.k / kTcBK;
 
@@ -71,11 +78,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_acc_full + 8 * b, 1);
-      mbar_init(bar_acc_empty + 8 * b, 4);
+      mbar_init(bar_acc_empty + 8 * b, kEpiWarps);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     const uint32_t slot = smem_u32(const_cast<uint32_t*>(&misc[0]));
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(512u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -85,7 +92,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = misc[0];
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     if (lane == 0) {
       pdl_wait();   // activations come from the preceding kernel
       int stage = 0;
@@ -110,7 +117,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       }
       if (!ok) report_status(MDB_STATUS_WAIT_TIMEOUT);
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     if (lane == 0) {
       // bf16 x bf16 -> fp32, K-major operands, M = 128, N = 256
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kTcBN >> 3) << 17) |
@@ -144,18 +151,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   } else {
     int acc = 0;
     uint32_t acc_phase = 0;
+    uint32_t acc_phase_tile = 0;   // tiles done (LM head: picks the record buffer)
     pdl_wait();   // the output buffer may still be read by the preceding kernel
     for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
       const int tn = t / a.tiles_m, tm = t % a.tiles_m;
       bool ok = mbar_wait(bar_acc_full + 8 * acc, acc_phase);
       ok = __all_sync(0xffffffffu, ok);
+      // LM head: the warps of a quarter meet at a named barrier below, so they must agree on giving up
+      if (EPI == kTcLmHead) ok = named_bar_and(5 + (warp & 3), 128, ok);
       if (!ok) {
         if (lane == 0) report_status(MDB_STATUS_WAIT_TIMEOUT);
         break;
       }
       tc_fence_after();
-      const uint32_t taddr = tmem_base + acc * kTcBN + (static_cast<uint32_t>(32 * warp) << 16);
-      const int row = tm * kTcBM + 32 * warp + lane;
+      const int quarter = warp & 3;       // the 32 tensor-memory lanes this warp may read
+      const uint32_t taddr = tmem_base + acc * kTcBN + (static_cast<uint32_t>(32 * quarter) << 16);
+      const int row = tm * kTcBM + 32 * quarter + lane;
       if (EPI == kTcBf16) {
         bf16* dst = a.y + static_cast<int64_t>(row) * a.ldy + tn * kTcBN;
 #pragma unroll 1
@@ -213,44 +224,81 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
       }
       if (EPI == kTcLmHead) {
+        // this warp: columns [64 g, 64 g + 64) of the tile for its 32 step rows
+        const int grp = warp >> 2;
         const bool live = row < a.m;
-        const float temp = a.temperatures[(live ? row : 0) / a.block];
+        const float inv_temp = __frcp_rn(a.temperatures[(live ? row : 0) / a.block]);
         const uint32_t step = a.step + (a.step_dev != nullptr ? *a.step_dev : 0u);
+        const uint32_t key = gumbel_row_key(a.seed, step, row);
+        constexpr float kLog2e = 1.4426950408889634f;
         float mx = -INFINITY, se = 0.f, bv = -INFINITY, bl = 0.f;
         int bi = 0x7fffffff;
 #pragma unroll 1
-        for (int c = 0; c < kTcBN / 32; ++c) {
-          float v0[16], v1[16];
-          tmem_ld16(taddr + 32 * c, v0);
-          tmem_ld16(taddr + 32 * c + 16, v1);
+        for (int half = 0; half < 2; ++half) {
+          const int col0 = tn * kTcBN + 64 * grp + 32 * half;
+          if (col0 >= a.n) break;            // uniform; the last vocabulary tile may be partly outside
+          float v[32];
+          tmem_ld16(taddr + 64 * grp + 32 * half, *reinterpret_cast<float(*)[16]>(v));
+          tmem_ld16(taddr + 64 * grp + 32 * half + 16, *reinterpret_cast<float(*)[16]>(v + 16));
           tmem_ld_wait();
-          const int col0 = tn * kTcBN + 32 * c;
-          if (col0 >= a.n) break;            // uniform: the last vocabulary tile may be partly outside
-          float lg[32];
-          float cmax = -INFINITY;
+          const bool full = col0 + 32 <= a.n;
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const float acc_v = i < 16 ? v0[i] : v1[i - 16];
-            const bool in = col0 + i < a.n;
-            lg[i] = in ? __fdiv_rn(bf16_round(acc_v), temp) : -INFINITY;
-            cmax = fmaxf(cmax, lg[i]);
-            if (in) {
-              float noisy = lg[i];
-              if (a.noise_mode == 2) noisy += gumbel_noise(a.seed, step, row, col0 + i);
-              if (noisy > bv) { bv = noisy; bl = lg[i]; bi = col0 + i; }   // ascending columns: first maximum kept
-            }
+            v[i] = bf16_round(v[i]) * inv_temp;
+            if (!full && col0 + i >= a.n) v[i] = -INFINITY;
           }
-          const float nm = fmaxf(mx, cmax);
-          float add = 0.f;
+          float m0 = fmaxf(v[0], v[1]), m1 = fmaxf(v[2], v[3]);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) add += __expf(lg[i] - nm);          // exp(-inf) = 0 for columns outside
-          se = (mx == -INFINITY ? 0.f : se * __expf(mx - nm)) + add;
+          for (int i = 4; i < 32; i += 4) {
+            m0 = fmaxf(m0, fmaxf(v[i], v[i + 1]));
+            m1 = fmaxf(m1, fmaxf(v[i + 2], v[i + 3]));
+          }
+          const float nm = fmaxf(mx, fmaxf(m0, m1));
+          const float nm2 = nm * kLog2e;
+          float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            s0 += ex2_approx(fmaf(v[i], kLog2e, -nm2));          // 2^-inf = 0 for columns outside
+            s1 += ex2_approx(fmaf(v[i + 1], kLog2e, -nm2));
+          }
+          se = (mx == -INFINITY ? 0.f : se * ex2_approx(fmaf(mx, kLog2e, -nm2))) + s0 + s1;
           mx = nm;
+          if (a.noise_mode == 2) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float noisy = v[i] + gumbel_from_key(key, col0 + i);   // -inf stays -inf
+              if (noisy > bv) { bv = noisy; bl = v[i]; bi = col0 + i; }    // ascending columns: first maximum kept
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (v[i] > bv) { bv = v[i]; bl = v[i]; bi = col0 + i; }
+          }
         }
-        if (live) {
-          a.part_f[static_cast<int64_t>(tn) * a.m + row] = make_float4(mx, se, bv, bl);
-          a.part_i[static_cast<int64_t>(tn) * a.m + row] = bi;
+        // the four warps of a quarter merge their records through shared memory (two buffers, one barrier per tile)
+        float* rec = reinterpret_cast<float*>(gen_base + bars_off + 256) + ((acc_phase_tile & 1) * kTcLmEpiWarps + warp) * 160;
+        rec[lane] = mx; rec[32 + lane] = se; rec[64 + lane] = bv; rec[96 + lane] = bl;
+        rec[128 + lane] = __int_as_float(bi);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + quarter) : "memory");
+        if (grp == 0) {
+          SampleRec r = {mx, se, bv, bl, bi};
+#pragma unroll
+          for (int g2 = 1; g2 < 4; ++g2) {
+            const float* o = rec + g2 * 4 * 160;
+            const SampleRec t = {o[lane], o[32 + lane], o[64 + lane], o[96 + lane], __float_as_int(o[128 + lane])};
+            merge_rec(r, t);
+          }
+          if (live) {
+            a.part_f[static_cast<int64_t>(tn) * a.m + row] = make_float4(r.mx, r.se, r.bv, r.bl);
+            a.part_i[static_cast<int64_t>(tn) * a.m + row] = r.bi;
+          }
         }
+        ++acc_phase_tile;
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        continue;
       }
       tc_fence_before();
       __syncwarp();
@@ -261,7 +309,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
   }
@@ -298,7 +346,7 @@ static int launch_tc(const bf16* x, int64_t ldx, const bf16* w, int w_rows, TcAr
     attr_set = true;
   }
   const int tiles = a.tiles_m * a.tiles_n;
-  return mdb_launch(gemm_tc_kernel<EPI>, dim3(tiles < sm_count ? tiles : sm_count), dim3(kTcThreads), kTcSmemBytes, st,
+  return mdb_launch(gemm_tc_kernel<EPI>, dim3(tiles < sm_count ? tiles : sm_count), dim3(tc_threads(EPI)), kTcSmemBytes, st,
                     map_x, map_w, a);
 }
 

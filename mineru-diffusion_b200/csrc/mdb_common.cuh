@@ -179,6 +179,26 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
 // one ldmatrix phase fall in 8 distinct bank groups.
 __device__ __forceinline__ int swz_chunk(int row, int chunk) { return chunk ^ (row & 7); }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Named barrier over `threads` threads that also ANDs a predicate across them.
+__device__ __forceinline__ bool named_bar_and(int id, int threads, bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.and.pred p, %2, %3, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"(static_cast<uint32_t>(pred)), "r"(id), "r"(threads)
+      : "memory");
+  return r != 0;
+}
+
 // ---- counter-based Gumbel noise ---------------------------------------------
 // One value per (seed, step, row, column); the LM-head scan and the noise dump
 // entry point call the same function so a test can hand the exact noise to a
@@ -190,15 +210,21 @@ __device__ __forceinline__ uint32_t mix32(uint32_t x) {
   return x;
 }
 
-__device__ __forceinline__ float gumbel_noise(uint32_t seed, uint32_t step, uint32_t row, uint32_t col) {
+// The (seed, step, row) part of the hash, for callers that walk many columns of one row.
+__device__ __forceinline__ uint32_t gumbel_row_key(uint32_t seed, uint32_t step, uint32_t row) {
   uint32_t h = mix32(seed ^ 0x9e3779b9u);
   h = mix32(h ^ (step * 0x85ebca6bu + 0xc2b2ae35u));
-  h = mix32(h ^ (row * 0x27d4eb2fu + 0x165667b1u));
-  h = mix32(h ^ col);
+  return mix32(h ^ (row * 0x27d4eb2fu + 0x165667b1u));
+}
+__device__ __forceinline__ float gumbel_from_key(uint32_t row_key, uint32_t col) {
+  const uint32_t h = mix32(row_key ^ col);
   // uniform in (0,1): 24 random bits, centred
   float u = (static_cast<float>(h >> 8) + 0.5f) * (1.0f / 16777216.0f);
   float e = -__logf(u);          // Exp(1)
   return -__logf(e);             // Gumbel(0,1), as -log(Exp(1)) in the reference sampler
+}
+__device__ __forceinline__ float gumbel_noise(uint32_t seed, uint32_t step, uint32_t row, uint32_t col) {
+  return gumbel_from_key(gumbel_row_key(seed, step, row), col);
 }
 
 }  // namespace mdb

@@ -173,6 +173,19 @@ int mdb_qknorm_rope_commit(const void* qkv, int64_t ld_qkv, const float* partial
                            void* v_out, void* k_cache, void* v_cache, int64_t num_slots, int m, int hq, int hkv,
                            mdb_stream_t stream);
 
+/* qkv_proj and everything mdb_qknorm_rope_commit does, in one kernel for many
+ * rows (prefill, batched decode): y = x w_qkv^T on the tcgen05 tile GEMM whose
+ * epilogue rounds the projection to bf16, applies the per-head q/k RMSNorm and
+ * the rotary embedding and stores q, k, v (NV/models/sdar.py:73-82,
+ * NV/layers/sdar_attention.py:37-38) -- the [m, (hq+2hkv)*128] projection
+ * never reaches memory.  x bf16 [m,k] (row stride ldx), w_qkv bf16
+ * [(hq+2hkv)*128, k]; other arguments as mdb_qknorm_rope_commit.
+ * MDB_ERR_UNSUPPORTED unless k % 64 == 0 and ldx % 8 == 0. */
+int mdb_gemm_qkv_rope_commit(const void* x, int64_t ldx, const void* w_qkv, int m, int k, const int64_t* positions,
+                             const float* rope_table, int max_pos, const void* q_norm_w, const void* k_norm_w,
+                             float eps, const int32_t* slot_mapping, void* q_out, void* k_out, void* v_out,
+                             void* k_cache, void* v_cache, int64_t num_slots, int hq, int hkv, mdb_stream_t stream);
+
 /* Row gather: out[i,:] = table[ids[i],:] (F.embedding at
  * NV/layers/embed_head.py:38; also the last-block row pick of the LM head at
  * NV/layers/embed_head.py:63-66). */

@@ -60,6 +60,8 @@ SIGNATURES = {
     "mdb_add_rmsnorm": (_i, [_p, _p, _i, _p, _p, _f, _p, _p, _i, _i, _p]),
     "mdb_qknorm_rope_commit": (_i, [_p, _i64, _p, _i, _p, _p, _i, _p, _p, _f, _p, _p, _p, _p, _p, _p, _i64, _i, _i,
                                     _i, _p]),
+    "mdb_gemm_qkv_rope_commit": (_i, [_p, _i64, _p, _i, _i, _p, _p, _i, _p, _p, _f, _p, _p, _p, _p, _p, _p, _i64, _i, _i,
+                                      _p]),
     "mdb_gather_rows": (_i, [_p, _i64, _p, _p, _i, _i, _p]),
     "mdb_lmhead_workspace_bytes": (_i64, [_i, _i]),
     "mdb_lmhead_sample": (_i, [_p, _i64, _p, _i, _i, _i, _p, _i, _i, _p, _u32, _u32, _p, _p, _i64, _p, _p, _p]),

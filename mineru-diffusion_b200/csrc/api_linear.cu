@@ -188,6 +188,39 @@ int mdb_gemm_bf16(const void* x, int64_t ldx, const void* w, void* y, int64_t ld
                            m, n, k, st);
 }
 
+int mdb_gemm_qkv_rope_commit(const void* x, int64_t ldx, const void* w_qkv, int m, int k, const int64_t* positions,
+                             const float* rope_table, int max_pos, const void* q_norm_w, const void* k_norm_w,
+                             float eps, const int32_t* slot_mapping, void* q_out, void* k_out, void* v_out,
+                             void* k_cache, void* v_cache, int64_t num_slots, int hq, int hkv, mdb_stream_t stream) {
+  MDB_REQUIRE(m >= 0 && k > 0 && hq > 0 && hkv > 0 && max_pos > 0, MDB_ERR_ARG);
+  if (m == 0) return MDB_OK;
+  MDB_REQUIRE(x && w_qkv && positions && rope_table && q_norm_w && k_norm_w && q_out && ldx >= k, MDB_ERR_ARG);
+  MDB_REQUIRE(slot_mapping == nullptr || (k_cache && v_cache && num_slots > 0), MDB_ERR_ARG);
+  MDB_REQUIRE(mdb_aligned16(x) && mdb_aligned16(w_qkv) && mdb_aligned16(rope_table) && mdb_aligned16(q_out) &&
+                  mdb_aligned16(k_out) && mdb_aligned16(v_out) && mdb_aligned16(k_cache) && mdb_aligned16(v_cache) &&
+                  mdb_aligned16(q_norm_w) && mdb_aligned16(k_norm_w),
+              MDB_ERR_ALIGN);
+  const int n = (hq + 2 * hkv) * kHeadDim;
+  MDB_REQUIRE(g_opt_stream_kernel == 0 && tc_supported(kTcQkvRope, m, n, k, ldx, 0), MDB_ERR_UNSUPPORTED);
+  TcArgs a = {};
+  a.m = m; a.n = n; a.k = k;
+  a.hq = hq; a.hkv = hkv; a.max_pos = max_pos;
+  a.eps = eps;
+  a.positions = positions;
+  a.rope_table = rope_table;
+  a.q_norm_w = static_cast<const bf16*>(q_norm_w);
+  a.k_norm_w = static_cast<const bf16*>(k_norm_w);
+  a.slot_mapping = slot_mapping;
+  a.q_out = static_cast<bf16*>(q_out);
+  a.k_out = static_cast<bf16*>(k_out);
+  a.v_out = static_cast<bf16*>(v_out);
+  a.k_cache = static_cast<bf16*>(k_cache);
+  a.v_cache = static_cast<bf16*>(v_cache);
+  a.num_slots = num_slots;
+  return launch_tc<kTcQkvRope>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w_qkv), n, a,
+                               static_cast<cudaStream_t>(stream));
+}
+
 int64_t mdb_lmhead_workspace_bytes(int m, int vocab) {
   if (m <= 0 || vocab <= 0) return 0;
   return lmhead_layout(m, vocab).total;

@@ -14,14 +14,17 @@
 // LM head + sampler: the thread that owns a step row turns its 256 logits of
 // the vocabulary tile into one (max, sum-exp, best noisy value, its logit, its
 // index) record, so logits never reach memory (nanovllm/layers/sampler.py:11-29
-// on top of the LM head of nanovllm/models/sdar.py).
+// on top of the LM head of nanovllm/models/sdar.py); qkv projection with the
+// per-head q/k RMSNorm, rotary embedding and KV store (nanovllm/models/sdar.py:
+// 73-82, nanovllm/layers/sdar_attention.py:37-38): a 256-column tile is two
+// heads, and the thread that owns a step row holds a whole head of it.
 // Tiles are ordered so that consecutive CTAs share a weight tile: it is read
 // from HBM once and served from L2 to the others.
 #include "mdb_common.cuh"
 
 namespace mdb {
 
-enum TcEpilogue { kTcBf16 = 0, kTcSwiglu = 1, kTcLmHead = 2 };
+enum TcEpilogue { kTcBf16 = 0, kTcSwiglu = 1, kTcLmHead = 2, kTcQkvRope = 3 };
 
 constexpr int kTcBM = 128, kTcBN = 256, kTcBK = 64;
 constexpr int kTcStages = 4;
@@ -30,7 +33,7 @@ constexpr int kTcBBytes = kTcBN * kTcBK * 2;   // 32 KB
 constexpr int kTcLmEpiWarps = 16;
 constexpr int kTcLmRecBytes = 2 * kTcLmEpiWarps * 32 * 5 * 4;    // two buffers of per-warp sampler records
 constexpr int kTcSmemBytes = 1024 + kTcStages * (kTcABytes + kTcBBytes) + 256 + kTcLmRecBytes;
-__host__ __device__ constexpr int tc_epi_warps(int epi) { return epi == 2 ? kTcLmEpiWarps : 4; }
+__host__ __device__ constexpr int tc_epi_warps(int epi) { return epi == 2 ? kTcLmEpiWarps : (epi == 3 ? 8 : 4); }
 __host__ __device__ constexpr int tc_threads(int epi) { return (tc_epi_warps(epi) + 2) * 32; }
 
 struct TcArgs {
@@ -47,6 +50,20 @@ struct TcArgs {
   const uint32_t* step_dev;
   float4* part_f;              // [tiles_n][m] (max, sum exp, best noisy value, its logit)
   int* part_i;                 // [tiles_n][m] index of the best noisy value
+  // qkv projection + q/k norm + rotary embedding + KV store
+  int hq, hkv, max_pos;
+  float eps;
+  const int64_t* positions;
+  const float* rope_table;     // [max_pos][64 cos | 64 sin]
+  const bf16* q_norm_w;
+  const bf16* k_norm_w;
+  const int32_t* slot_mapping; // NULL: no cache write
+  bf16* q_out;                 // [m][hq][128]
+  bf16* k_out;                 // [m][hkv][128] or NULL
+  bf16* v_out;
+  bf16* k_cache;               // [slots][hkv][128]
+  bf16* v_cache;
+  int64_t num_slots;
 };
 
 template <int EPI>
@@ -223,6 +240,90 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           }
         }
       }
+      if (EPI == kTcQkvRope) {
+        // this warp: head 2 tn + g of the fused q|k|v output for its 32 step rows
+        const int grp = warp >> 2;
+        const int head = 2 * tn + grp;
+        const int nheads = a.hq + 2 * a.hkv;
+        float v[kHeadDim];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) tmem_ld16(taddr + kHeadDim * grp + 16 * c, *reinterpret_cast<float(*)[16]>(v + 16 * c));
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
+        if (row < a.m && head < nheads) {
+#pragma unroll
+          for (int i = 0; i < kHeadDim; ++i) v[i] = bf16_round(v[i]);       // the projection's bf16 output
+          const bool is_q = head < a.hq;
+          const bool is_k = !is_q && head < a.hq + a.hkv;
+          if (is_q || is_k) {
+            float ss0 = 0.f, ss1 = 0.f, ss2 = 0.f, ss3 = 0.f;
+#pragma unroll
+            for (int i = 0; i < kHeadDim; i += 4) {
+              ss0 = fmaf(v[i], v[i], ss0); ss1 = fmaf(v[i + 1], v[i + 1], ss1);
+              ss2 = fmaf(v[i + 2], v[i + 2], ss2); ss3 = fmaf(v[i + 3], v[i + 3], ss3);
+            }
+            const float rstd = 1.0f / sqrtf(((ss0 + ss1) + (ss2 + ss3)) / static_cast<float>(kHeadDim) + a.eps);
+            const uint4* nw = reinterpret_cast<const uint4*>(is_q ? a.q_norm_w : a.k_norm_w);
+#pragma unroll
+            for (int c = 0; c < kHeadDim / 8; ++c) {
+              const uint4 w8 = __ldg(nw + c);
+              const uint32_t ws[4] = {w8.x, w8.y, w8.z, w8.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 wf = unpack_bf16x2(ws[j]);
+                v[8 * c + 2 * j] = bf16_round(bf16_round(v[8 * c + 2 * j] * rstd) * wf.x);
+                v[8 * c + 2 * j + 1] = bf16_round(bf16_round(v[8 * c + 2 * j + 1] * rstd) * wf.y);
+              }
+            }
+            const int64_t pos = a.positions[row];
+            if (pos >= 0 && pos < a.max_pos) {
+              const float4* cs = reinterpret_cast<const float4*>(a.rope_table + pos * kHeadDim);
+#pragma unroll
+              for (int c = 0; c < 16; ++c) {
+                const float4 co = __ldg(cs + c), si = __ldg(cs + 16 + c);
+                const float cc[4] = {co.x, co.y, co.z, co.w}, sn[4] = {si.x, si.y, si.z, si.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float lo = v[4 * c + j], hi = v[4 * c + j + 64];
+                  // products rounded separately, as un-fused fp32 tensor ops do
+                  v[4 * c + j] = __fsub_rn(__fmul_rn(lo, cc[j]), __fmul_rn(hi, sn[j]));
+                  v[4 * c + j + 64] = __fadd_rn(__fmul_rn(hi, cc[j]), __fmul_rn(lo, sn[j]));
+                }
+              }
+            } else {
+              report_status(MDB_STATUS_BAD_POSITION);
+            }
+          }
+          uint4 o[16];
+#pragma unroll
+          for (int c = 0; c < 16; ++c)
+            o[c] = make_uint4(pack_bf16x2(v[8 * c], v[8 * c + 1]), pack_bf16x2(v[8 * c + 2], v[8 * c + 3]),
+                              pack_bf16x2(v[8 * c + 4], v[8 * c + 5]), pack_bf16x2(v[8 * c + 6], v[8 * c + 7]));
+          auto store = [&](bf16* dst) {
+            uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+            for (int c = 0; c < 16; ++c) d4[c] = o[c];
+          };
+          if (is_q) {
+            store(a.q_out + (static_cast<int64_t>(row) * a.hq + head) * kHeadDim);
+          } else {
+            const int kvh = is_k ? head - a.hq : head - a.hq - a.hkv;
+            bf16* contiguous = is_k ? a.k_out : a.v_out;
+            if (contiguous != nullptr) store(contiguous + (static_cast<int64_t>(row) * a.hkv + kvh) * kHeadDim);
+            if (a.slot_mapping != nullptr) {
+              const int slot = a.slot_mapping[row];
+              if (slot >= 0 && slot < a.num_slots)
+                store((is_k ? a.k_cache : a.v_cache) + (static_cast<int64_t>(slot) * a.hkv + kvh) * kHeadDim);
+              else if (slot != -1)
+                report_status(MDB_STATUS_BAD_SLOT);
+            }
+          }
+        }
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        continue;
+      }
       if (EPI == kTcLmHead) {
         // this warp: columns [64 g, 64 g + 64) of the tile for its 32 step rows
         const int grp = warp >> 2;
@@ -319,6 +420,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 static bool tc_supported(int epi, int m, int n, int k, int64_t ldx, int64_t ldy) {
   if (m < 1 || k % kTcBK != 0 || ldx % 8 != 0) return false;
   if (epi == kTcLmHead) return true;
+  if (epi == kTcQkvRope) return n % kHeadDim == 0;
   if (ldy % 8 != 0) return false;
   if (epi == kTcSwiglu) return n % 128 == 0;
   return n % 8 == 0;

@@ -199,6 +199,9 @@ class DecoderEngine:
                 ops.gemm_splitk_partials(x, lw.qkv, self.ks_qkv, parts)
                 ops.qknorm_rope_commit(None, pos, self.rope, lw.q_norm, lw.k_norm, eps, hq, hkv, slots, k_cache,
                                        v_cache, partials=parts, q_out=q, k_out=kb, v_out=vb)
+            elif ops.qkv_rope_commit_supported(m, h):
+                ops.qkv_proj_rope_commit(x, lw.qkv, pos, self.rope, lw.q_norm, lw.k_norm, eps, hq, hkv, slots, k_cache,
+                                         v_cache, q_out=q, k_out=kb, v_out=vb)
             else:
                 qkv = self.qkv_out[:m]
                 ops.linear(x, lw.qkv, out=qkv)

@@ -352,8 +352,13 @@ class ModelRunner:
         if self.fused_step and self.noise != "explicit" and self.engine.fused_supported(bs * self.block_size):
             return 2            # the one-kernel step and the unmask rule
         per_layer = 8 + (1 if nsplit > 1 else 0)
-        if bs * self.block_size > 64:
-            per_layer += 1      # stand-alone SiLU*mul on the tiled path
+        m = bs * self.block_size
+        if m > 64:
+            if ops.qkv_rope_commit_supported(m, self.dcfg.hidden_size):
+                per_layer -= 1  # q/k norm, rotary embedding and KV store run in the qkv GEMM's epilogue
+            if not (self.dcfg.intermediate_size % 128 == 0 and self.dcfg.hidden_size % 64 == 0
+                    and ops.get_option(ops.OPT_STREAM_KERNEL) == 0):
+                per_layer += 1  # stand-alone SiLU*mul on the mma.sync path
         return 1 + self.dcfg.num_hidden_layers * per_layer + 1 + 2 + 1
 
     # ------------------------------------------------------------------ CUDA graphs

@@ -91,6 +91,11 @@ def default_nsplit(bs: int, block: int, hq: int, hkv: int, max_ctx: int) -> int:
     return int(max(1, min(want, parts, 32)))
 
 
+def attn_workspace_bytes(bs: int, block: int, hq: int, nsplit: int) -> int:
+    """Scratch bytes ``block_attn_with_kvcache`` needs for ``nsplit`` key-range parts (0 for one part)."""
+    return int(_lib.lib().mdb_attn_paged_workspace_bytes(bs, block, hq, nsplit))
+
+
 def block_attn_with_kvcache(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                             cache_seqlens: torch.Tensor, block_table: torch.Tensor, softmax_scale: float | None = None,
                             nsplit: int | None = None, workspace: torch.Tensor | None = None,
@@ -292,6 +297,41 @@ def qknorm_rope_commit(qkv: torch.Tensor | None, positions: torch.Tensor, rope_t
                                                  float(eps), _ptr(slot_mapping), q_out.data_ptr(), _ptr(k_out),
                                                  _ptr(v_out), _ptr(k_cache), _ptr(v_cache), num_slots, m, hq, hkv,
                                                  _stream()), "mdb_qknorm_rope_commit")
+    return q_out, k_out, v_out
+
+
+def qkv_rope_commit_supported(m: int, k: int) -> bool:
+    """Whether ``qkv_proj_rope_commit`` takes this step: many rows, on the tcgen05 kernels."""
+    return m > 64 and k % 64 == 0 and get_option(OPT_STREAM_KERNEL) == 0
+
+
+def qkv_proj_rope_commit(x: torch.Tensor, w_qkv: torch.Tensor, positions: torch.Tensor, rope_table: torch.Tensor,
+                         q_norm_w: torch.Tensor, k_norm_w: torch.Tensor, eps: float, hq: int, hkv: int,
+                         slot_mapping: torch.Tensor | None = None, k_cache: torch.Tensor | None = None,
+                         v_cache: torch.Tensor | None = None, q_out: torch.Tensor | None = None,
+                         k_out: torch.Tensor | None = None, v_out: torch.Tensor | None = None):
+    """``qkv_proj`` + ``qknorm_rope_commit`` as one kernel for many rows
+    (nanovllm/models/sdar.py:73-82, nanovllm/layers/sdar_attention.py:37-38):
+    the projection output stays in tensor memory."""
+    _need(x, _BF16, "x")
+    _need(w_qkv, _BF16, "w_qkv")
+    _need(positions, torch.int64, "positions")
+    _need(rope_table, torch.float32, "rope_table")
+    m, k = x.shape
+    d = 128
+    if w_qkv.shape[0] != (hq + 2 * hkv) * d or w_qkv.shape[1] != k:
+        raise ValueError("w_qkv must be [(hq + 2 hkv) * 128, k]")
+    if q_out is None:
+        q_out = torch.empty((m, hq, d), dtype=_BF16, device=x.device)
+    num_slots = 0 if k_cache is None else k_cache.numel() // (hkv * d)
+    if slot_mapping is not None:
+        _need(slot_mapping, torch.int32, "slot_mapping")
+    _lib.check(_lib.lib().mdb_gemm_qkv_rope_commit(x.data_ptr(), _rows(x, "x"), w_qkv.data_ptr(), m, k,
+                                                   positions.data_ptr(), rope_table.data_ptr(), rope_table.shape[0],
+                                                   q_norm_w.data_ptr(), k_norm_w.data_ptr(), float(eps),
+                                                   _ptr(slot_mapping), q_out.data_ptr(), _ptr(k_out), _ptr(v_out),
+                                                   _ptr(k_cache), _ptr(v_cache), num_slots, hq, hkv, _stream()),
+               "mdb_gemm_qkv_rope_commit")
     return q_out, k_out, v_out
 
 

@@ -141,6 +141,54 @@ def test_qknorm_rope_commit(mdb, from_partials):
     _status_clean(mdb)
 
 
+@pytest.mark.parametrize("m,hq,hkv,k", [(200, 4, 2, 256), (129, 3, 1, 128), (2048, 16, 8, 2048)])
+def test_qkv_proj_rope_commit_fused(mdb, m, hq, hkv, k):
+    """qkv projection with the norm / rotary / KV-store epilogue (tcgen05 tile
+    GEMM, many rows) against the projection followed by the stand-alone kernel,
+    and, for the small shapes, against the oracle.  129 rows and 5 heads leave a
+    partial row tile and a half-empty column tile."""
+    gen = torch.Generator().manual_seed(m + hq)
+    n = (hq + 2 * hkv) * 128
+    x = torch.randn(m, k, generator=gen).to(BF)
+    w = (torch.randn(n, k, generator=gen) / k ** 0.5).to(BF)
+    pos = torch.randint(0, 4000, (m,), generator=gen)
+    qn = (1 + 0.1 * torch.randn(128, generator=gen)).to(BF)
+    kn = (1 + 0.1 * torch.randn(128, generator=gen)).to(BF)
+    table = orc.rope_table(4096, 128, 1e6)
+    pages = (m + 300 + 255) // 256
+    slots = torch.tensor([-1 if i % 9 == 0 else 250 + i for i in range(m)], dtype=torch.int32)
+    args = (pos.to(DEV), table.to(DEV), qn.to(DEV), kn.to(DEV), 1e-6, hq, hkv, slots.to(DEV))
+
+    def run(fused):
+        kc = torch.zeros(pages, 256, hkv, 128, dtype=BF, device=DEV)
+        vc = torch.zeros_like(kc)
+        kb = torch.zeros(m, hkv, 128, dtype=BF, device=DEV)
+        vb = torch.zeros_like(kb)
+        if fused:
+            q, _, _ = mdb.ops.qkv_proj_rope_commit(x.to(DEV), w.to(DEV), *args, kc, vc, k_out=kb, v_out=vb)
+        else:
+            qkv = mdb.ops.linear(x.to(DEV), w.to(DEV))
+            q, _, _ = mdb.ops.qknorm_rope_commit(qkv, *args, kc, vc, k_out=kb, v_out=vb)
+        return q, kb, vb, kc, vc
+
+    got, ref = run(True), run(False)
+    for g_t, r_t, name in zip(got, ref, ("q", "k", "v", "k_cache", "v_cache")):
+        diff = (g_t.float() - r_t.float()).abs()
+        # same bf16 projection; only the order of the 128-term sum of squares differs
+        assert float(diff.max()) <= 4e-2, name
+        assert float((diff == 0).float().mean()) >= 0.995, name
+    assert torch.equal(got[2], ref[2]) and torch.equal(got[4], ref[4])       # v passes through untouched
+    if m <= 256:
+        qkv = orc.linear(x, w)
+        q, kk, v = qkv.split([hq * 128, hkv * 128, hkv * 128], dim=-1)
+        q = orc.apply_rope(orc.rms_norm(q.reshape(m, hq, 128), qn, 1e-6), pos, table)
+        kk = orc.apply_rope(orc.rms_norm(kk.reshape(m, hkv, 128), kn, 1e-6), pos, table)
+        assert float((got[0].cpu().float() - q.float()).abs().max()) <= 6e-2
+        assert float((got[1].cpu().float() - kk.float()).abs().max()) <= 6e-2
+        assert float((got[0].cpu().float() - q.float()).abs().mean()) <= 2e-3
+    _status_clean(mdb)
+
+
 def test_rope_golden(mdb):
     g = load_golden("layers.npz")
     q, k = bf16_from_bits(g["rope_q"]), bf16_from_bits(g["rope_k"])

@@ -118,10 +118,12 @@ int mdb_attn_block_paged_noalloc(const void* q, const void* k_cache, const void*
  * q/out rows of hq*128, k/v rows of hkv*128, row strides in elements;
  * cu_seqlens: [nseq+1] int32 (queries and keys share it: self-attention).
  * Query i of a T-token sequence sees keys j <= ((i+pad)/S+1)*S-1-pad with
- * pad = ceil(T/S)*S - T.  stairs must be a power of two in [1,128]. */
+ * pad = ceil(T/S)*S - T.  stairs must be a power of two in [1,128].
+ * total_tokens = cu_seqlens[nseq] = the row count of q, k, v and out (the host
+ * knows it; the TMA descriptors of the tcgen05 kernel are bounded by it). */
 int mdb_attn_staircase_varlen(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
                               int64_t v_stride, void* out, int64_t out_stride, const int32_t* cu_seqlens, int nseq,
-                              int max_seqlen, int hq, int hkv, int stairs, mdb_stream_t stream);
+                              int max_seqlen, int64_t total_tokens, int hq, int hkv, int stairs, mdb_stream_t stream);
 
 /* ---- linear layers -------------------------------------------------------- */
 

@@ -50,7 +50,7 @@ SIGNATURES = {
     "mdb_attn_block_paged": (_i, [_p, _p, _p, _p, _p, _i, _p, _i, _i, _i, _i, _i, _f, _i, _p, _i64, _p]),
     "mdb_attn_block_paged_noalloc_limit": (_i64, []),
     "mdb_attn_block_paged_noalloc": (_i, [_p, _p, _p, _p, _p, _i, _p, _i, _i, _i, _i, _i, _f, _i, _p]),
-    "mdb_attn_staircase_varlen": (_i, [_p, _i64, _p, _i64, _p, _i64, _p, _i64, _p, _i, _i, _i, _i, _i, _p]),
+    "mdb_attn_staircase_varlen": (_i, [_p, _i64, _p, _i64, _p, _i64, _p, _i64, _p, _i, _i, _i64, _i, _i, _i, _p]),
     "mdb_gemm_bf16": (_i, [_p, _i64, _p, _p, _i64, _i, _i, _i, _p]),
     "mdb_gemm_pick_ksplit": (_i, [_i, _i, _i]),
     "mdb_gemm_splitk_workspace_bytes": (_i64, [_i, _i, _i]),

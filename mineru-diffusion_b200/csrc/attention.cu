@@ -39,6 +39,9 @@ struct AttnPagedArgs {
 // tcgen05/TMA form of the paged kernel (defined with the other tcgen05 kernels)
 static bool attn_tc_supported(int block, int hq, int hkv, float softmax_scale);
 static int attn_tc_launch(const AttnPagedArgs& a, int bs, cudaStream_t st);
+struct AttnStairArgs;
+static bool attn_stair_tc_supported(int hq, int hkv, int64_t q_stride, int64_t k_stride, int64_t v_stride);
+static int attn_stair_tc_launch(const AttnStairArgs& a, int nseq, int max_seqlen, int64_t total_tokens, cudaStream_t st);
 
 struct AttnStairArgs {
   const bf16* q;
@@ -521,8 +524,8 @@ int mdb_attn_block_paged(const void* q, const void* k_cache, const void* v_cache
 
 int mdb_attn_staircase_varlen(const void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
                               int64_t v_stride, void* out, int64_t out_stride, const int32_t* cu_seqlens, int nseq,
-                              int max_seqlen, int hq, int hkv, int stairs, mdb_stream_t stream) {
-  MDB_REQUIRE(nseq >= 0 && max_seqlen >= 0 && hq > 0 && hkv > 0, MDB_ERR_ARG);
+                              int max_seqlen, int64_t total_tokens, int hq, int hkv, int stairs, mdb_stream_t stream) {
+  MDB_REQUIRE(nseq >= 0 && max_seqlen >= 0 && hq > 0 && hkv > 0 && total_tokens >= 0, MDB_ERR_ARG);
   if (nseq == 0 || max_seqlen == 0) return MDB_OK;
   MDB_REQUIRE(q && k && v && out && cu_seqlens, MDB_ERR_ARG);
   MDB_REQUIRE(hq % hkv == 0, MDB_ERR_ARG);
@@ -557,6 +560,8 @@ int mdb_attn_staircase_varlen(const void* q, int64_t q_stride, const void* k, in
   while ((1 << lg) < stairs) ++lg;
   a.log2_stairs = lg;
   a.q_scale = 1.0f / sqrtf(static_cast<float>(kHeadDim)) * 1.44269504f;
+  if (g_opt_attn_kernel != 1 && total_tokens > 0 && attn_stair_tc_supported(hq, hkv, q_stride, k_stride, v_stride))
+    return attn_stair_tc_launch(a, nseq, max_seqlen, total_tokens, static_cast<cudaStream_t>(stream));
   dim3 grid((max_seqlen + kAttnRows - 1) / kAttnRows, hq, nseq);
   return mdb_launch(attn_staircase_kernel, grid, dim3(kAttnWarps * 32), kAttnSmemBytes,
                     static_cast<cudaStream_t>(stream), a);

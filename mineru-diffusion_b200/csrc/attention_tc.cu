@@ -1,30 +1,34 @@
-// Block attention over the paged KV cache on the 5th-generation tensor cores,
-// for steps with many requests or long prefixes (the decode form of
-// flash_attn_with_kvcache as nanovllm/layers/sdar_attention.py:50-55 calls it).
+// Attention on the 5th-generation tensor cores, in two forms that share one
+// warp-specialised pipeline:
+//   * block attention over the paged KV cache (decode: the masked block of
+//     every request against its committed prefix, every key visible;
+//     flash_attn_with_kvcache as nanovllm/layers/sdar_attention.py:50-55 calls it);
+//   * staircase attention over packed sequences (prefill: a query row sees the
+//     keys up to the right edge of its right-aligned block;
+//     nanovllm/layers/block_prefill_attention_v2.py:17-166).
 //
-// One work unit = (request, KV head, key-range split).  Its query rows are the
-// block's tokens times the query heads that share the KV head (at most 64),
-// row = token * group + head_in_group.  Persistent CTAs, one per SM, walk the
-// units; inside a CTA
-//   warp 4   TMA producer: the Q tile (3-D box: 64 channels x group x block)
-//            and 128-key K and V tiles straight out of the cache pages
-//            ([tokens, hkv*128] seen as a matrix, boxes of 128 rows x 64
-//            channels, 128-byte swizzle) into a 2-stage K ring and a 3-stage V ring;
-//   warp 5   MMA issue: S = Q K^T (tcgen05.mma M128 N128, both operands
-//            K-major) into one of two S buffers in tensor memory, one tile
-//            ahead of O += P V (P from shared memory K-major, V as the
-//            MN-major B operand: the cache rows are the K dimension);
-//   warps 0-1 softmax: one query row per thread, S read with tcgen05.ld,
-//            running maximum kept lazily (O is rescaled only when a row's
-//            maximum grows by more than 2^8, so the common tile needs no
+// One work unit = the query rows of `tokens x group` (tokens of one request or
+// sequence times the query heads that share a KV head; row = token * group +
+// head_in_group) against a key range.  ROWS = 64 or 128 rows per unit: the MMA
+// is always M = 128, with ROWS = 64 the upper operand rows are whatever follows
+// in shared memory and only feed accumulator lanes nobody reads.  Persistent
+// CTAs, one per SM, walk the units; inside a CTA
+//   producer warp  TMA: the Q tile (3-D box: 64 channels x group x tokens) and
+//            128-key K and V tiles ([tokens, hkv*128] seen as a matrix, boxes
+//            of 128 rows x 64 channels, 128-byte swizzle) into K and V rings;
+//   MMA warp       S = Q K^T (tcgen05.mma M128 N128, both operands K-major)
+//            into one of two S buffers in tensor memory, one tile ahead of
+//            O += P V (P from shared memory K-major, V as the MN-major B
+//            operand: its rows are the K dimension);
+//   softmax warps  one query row per thread: S read with tcgen05.ld, running
+//            maximum kept lazily (O is rescaled only when a row's maximum
+//            grows by more than 2^8, so the common tile needs no
 //            read-modify-write of O), P rounded to bf16 into shared memory,
 //            and at the end of the unit O/l to the output or the (max, sum,
 //            O) partial to the split workspace.
-// The MMA reads 128 operand rows although at most 64 are query rows; the rows
-// above them are whatever follows in shared memory, and only feed accumulator
-// lanes nobody reads.  Tensor memory: S0 | S1 | O, 128 columns each.
+// Tensor memory: S0 | S1 | O, 128 columns each.
 //
-// HBM traffic is K and V once: 512 bytes per key per KV head.
+// HBM traffic of the paged form is K and V once: 512 bytes per key per KV head.
 #include "mdb_common.cuh"
 
 namespace mdb {
@@ -32,25 +36,53 @@ namespace mdb {
 constexpr int kAtKeys = 128;                          // keys per tile
 constexpr int kAtHalfBytes = kAtKeys * 128;           // [128 keys][64 channels] bf16
 constexpr int kAtTileBytes = 2 * kAtHalfBytes;        // 32 KB
-constexpr int kAtKStages = 2, kAtVStages = 3;
-constexpr int kAtRows = 64;                           // query rows held per unit
-constexpr int kAtQBytes = 2 * kAtRows * 128;          // 16 KB: two channel halves of [64 rows][128 B]
-constexpr int kAtPBytes = 2 * kAtRows * 128;          // 16 KB: two key halves of [64 rows][128 B]
-constexpr int kAtThreads = 192;
-constexpr int kAtSoftmaxWarps = 2;
-constexpr int kAtOffQ = 0;
-constexpr int kAtOffP = kAtOffQ + 2 * kAtQBytes;
-constexpr int kAtOffK = kAtOffP + 2 * kAtPBytes;
-constexpr int kAtOffV = kAtOffK + kAtKStages * kAtTileBytes;
-constexpr int kAtOffBars = kAtOffV + kAtVStages * kAtTileBytes;
-constexpr int kAtSmemBytes = 1024 + kAtOffBars + 256 + 1024;   // + barriers and tensor-memory slot + request ranks
 constexpr float kAtRescaleStep = 8.0f;                // log2 units a row maximum may lag behind
+constexpr int kAtMaxRanked = 512;                     // batches above this are walked in request order
+
+// Shared-memory plan for ROWS query rows per unit (224 KB of tiles either way).
+template <int ROWS>
+struct AtPlan {
+  static constexpr int kQBufs = ROWS == 64 ? 2 : 1;
+  static constexpr int kKStages = 2;
+  static constexpr int kVStages = ROWS == 64 ? 3 : 2;
+  static constexpr int kQBytes = 2 * ROWS * 128;      // two channel halves of [ROWS][128 B]
+  static constexpr int kPBytes = 2 * ROWS * 128;      // two key halves of [ROWS][128 B]
+  static constexpr int kSoftmaxWarps = ROWS / 32;
+  static constexpr int kProducerWarp = kSoftmaxWarps, kMmaWarp = kSoftmaxWarps + 1;
+  static constexpr int kThreads = (kSoftmaxWarps + 2) * 32;
+  static constexpr int kOffQ = 0;
+  static constexpr int kOffP = kOffQ + kQBufs * kQBytes;
+  static constexpr int kOffK = kOffP + 2 * kPBytes;
+  static constexpr int kOffV = kOffK + kKStages * kAtTileBytes;
+  static constexpr int kOffBars = kOffV + kVStages * kAtTileBytes;
+  static constexpr int kSmemBytes = 1024 + kOffBars + 256 + 2 * kAtMaxRanked;   // + barriers, tensor-memory slot, ranks
+};
 
 // barrier slots (8 bytes each) after the tiles
 enum {
   kAtBarQFull = 0, kAtBarQEmpty = 2, kAtBarKFull = 4, kAtBarKEmpty = 6, kAtBarVFull = 8, kAtBarVEmpty = 11,
   kAtBarSFull = 14, kAtBarSEmpty = 16, kAtBarPFull = 18, kAtBarPEmpty = 20, kAtBarOFull = 22, kAtBarOEmpty = 23,
-  kAtBarCount = 24
+  kAtBarQReady = 24, kAtBarCount = 26
+};
+
+struct AtArgs {
+  // common
+  const bf16* q;
+  bf16* out;
+  int hq, hkv, group;
+  int tokens_per_unit;      // tokens of one unit: ROWS / group, at most the block in the paged form
+  float scale_log2;         // multiplies S before the softmax (1 in the staircase form: q is scaled instead)
+  // paged form
+  const int32_t* block_table;
+  const int32_t* ctx_lens;
+  float* part_o;            // [bs][nsplit][hq][block][128]
+  float* part_ml;           // [bs][nsplit][hq][block][2]  (max in log2 units, sum)
+  int table_stride, block, num_pages, nsplit, bs, row_blocks;
+  // staircase form
+  const int32_t* cu_seqlens;
+  int64_t out_stride;
+  int nseq, max_qtiles, log2_stairs;
+  float q_scale;            // log2(e) / sqrt(D), applied to q and rounded to bf16 as the reference kernel does
 };
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
@@ -92,6 +124,7 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+
 // V tile as the B operand of O += P V: N = channels (contiguous, 64 per 128-byte
 // row, the two channel halves kAtHalfBytes apart), K = keys (rows of 128 bytes,
 // groups of 8 keys 1024 bytes apart).
@@ -105,28 +138,60 @@ __device__ __forceinline__ uint64_t umma_desc_sw128_mn(uint32_t smem_addr) {
   return d;
 }
 
-// The unit list every role walks the same way.  Requests are ranked by context
-// length (longest first; the ranks sit in shared memory) and the ranked units
-// are dealt to the CTAs in alternating direction, wave by wave, so that every
-// CTA gets about the same number of key tiles however ragged the batch is.
-constexpr int kAtMaxRanked = 512;   // batches above this are walked in request order
+// The unit list every role walks the same way.
+//
+// Paged form: requests are ranked by context length (longest first; the ranks
+// sit in shared memory) and the ranked units are dealt to the CTAs in
+// alternating direction, wave by wave, so that every CTA gets about the same
+// number of key tiles however ragged the batch is.
+// Staircase form: units are (query tile, sequence, KV head) with the late
+// (long) query tiles first.
 struct AtUnit {
-  int req, kvh, split, kbeg, kend, ntiles;
   bool valid;
+  int ntiles;       // 128-key tiles
+  int kbeg, kend;   // keys [kbeg, kend)
+  int kvh;
+  int q_tok0;       // row of the unit's first token in the q tensor
+  int req, split, tok0;        // paged: request, key-range part, first token of the block covered
+  int seq_start, m0, T;        // staircase: first packed row of the sequence, first token of the unit, length
 };
-__device__ __forceinline__ AtUnit at_unit(const AttnPagedArgs& a, const uint16_t* order, int bs, int units, int wave) {
-  AtUnit w;
+
+template <bool STAIR>
+__device__ __forceinline__ AtUnit at_unit(const AtArgs& a, const uint16_t* order, int units, int wave) {
+  AtUnit w = {};
   const int G = static_cast<int>(gridDim.x), c = static_cast<int>(blockIdx.x);
+  if (STAIR) {
+    const int p = wave * G + c;
+    if (p >= units) return w;
+    const int per_tile = a.nseq * a.hkv;
+    const int qt = a.max_qtiles - 1 - p / per_tile;
+    const int rest = p % per_tile;
+    const int seq = rest / a.hkv;
+    w.kvh = rest % a.hkv;
+    w.seq_start = a.cu_seqlens[seq];
+    w.T = a.cu_seqlens[seq + 1] - w.seq_start;
+    w.m0 = qt * a.tokens_per_unit;
+    if (w.m0 >= w.T) return w;
+    w.valid = true;
+    w.q_tok0 = w.seq_start + w.m0;
+    const int S = 1 << a.log2_stairs;
+    const int pad = ((w.T + S - 1) >> a.log2_stairs << a.log2_stairs) - w.T;
+    const int last = min(w.m0 + a.tokens_per_unit, w.T) - 1;
+    w.kbeg = 0;
+    w.kend = min(w.T, ((((last + pad) >> a.log2_stairs) + 1) << a.log2_stairs) - pad);
+    w.ntiles = (w.kend + kAtKeys - 1) / kAtKeys;
+    return w;
+  }
   const int p = wave * G + ((wave & 1) ? G - 1 - c : c);
-  w.valid = p < units;
-  w.ntiles = 0;
-  w.req = w.kvh = w.split = w.kbeg = w.kend = 0;
-  if (!w.valid) return w;
-  const int per_req = a.hkv * a.nsplit;
+  if (p >= units) return w;
+  w.valid = true;
+  const int per_req = a.hkv * a.row_blocks * a.nsplit;
   const int ranked = p / per_req, rem = p % per_req;
-  w.req = bs <= kAtMaxRanked ? static_cast<int>(order[ranked]) : ranked;
-  w.kvh = rem / a.nsplit;
+  w.req = a.bs <= kAtMaxRanked ? static_cast<int>(order[ranked]) : ranked;
+  w.kvh = rem / (a.row_blocks * a.nsplit);
+  w.tok0 = (rem / a.nsplit) % a.row_blocks * a.tokens_per_unit;
   w.split = rem % a.nsplit;
+  w.q_tok0 = w.req * a.block + w.tok0;
   const int ctx = a.ctx_lens[w.req];
   int chunk = ctx > 0 ? (ctx + a.nsplit - 1) / a.nsplit : 0;
   chunk = (chunk + kAtKeys - 1) / kAtKeys * kAtKeys;
@@ -145,30 +210,32 @@ struct AtRing {
   }
 };
 
-__global__ void __launch_bounds__(kAtThreads, 1)
-attn_paged_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                     const __grid_constant__ CUtensorMap map_v, const AttnPagedArgs a, const int bs, const int units) {
+template <int ROWS, bool STAIR>
+__global__ void __launch_bounds__(AtPlan<ROWS>::kThreads, 1)
+attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+               const __grid_constant__ CUtensorMap map_v, const AtArgs a, const int units) {
+  using P = AtPlan<ROWS>;
   extern __shared__ unsigned char at_smem_raw[];
   const uint32_t raw = smem_u32(at_smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char* gen_base = at_smem_raw + (base - raw);
-  const uint32_t bars = base + kAtOffBars;
+  const uint32_t bars = base + P::kOffBars;
   auto bar = [&](int slot) { return bars + 8u * static_cast<uint32_t>(slot); };
-  volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(gen_base + kAtOffBars + 8 * kAtBarCount);
-  uint16_t* order = reinterpret_cast<uint16_t*>(gen_base + kAtOffBars + 256);
+  volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(gen_base + P::kOffBars + 8 * kAtBarCount);
+  uint16_t* order = reinterpret_cast<uint16_t*>(gen_base + P::kOffBars + 256);
   const int waves = (units + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int group = a.hq / a.hkv;
-  const int rows_total = group * a.block;
+  const int group = a.group;
+  const int rows_used = group * a.tokens_per_unit;      // <= ROWS
 
   pdl_launch_dependents();
-  if (bs <= kAtMaxRanked) {
+  if (!STAIR && a.bs <= kAtMaxRanked) {
     // context lengths are step inputs, not written by the kernels this one is chained to
-    for (int r = threadIdx.x; r < bs; r += kAtThreads) {
+    for (int r = threadIdx.x; r < a.bs; r += P::kThreads) {
       const int mine = a.ctx_lens[r];
       int rank = 0;
-      for (int o = 0; o < bs; ++o) {
+      for (int o = 0; o < a.bs; ++o) {
         const int other = a.ctx_lens[o];
         rank += (other > mine || (other == mine && o < r)) ? 1 : 0;
       }
@@ -178,12 +245,12 @@ attn_paged_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   if (threadIdx.x == 0) {
     for (int s = 0; s < kAtBarCount; ++s) {
       const bool by_softmax = (s >= kAtBarSEmpty && s < kAtBarSEmpty + 2) || (s >= kAtBarPFull && s < kAtBarPFull + 2) ||
-                              s == kAtBarOEmpty;
-      mbar_init(bar(s), by_softmax ? kAtSoftmaxWarps : 1);
+                              s == kAtBarOEmpty || s >= kAtBarQReady;
+      mbar_init(bar(s), by_softmax ? P::kSoftmaxWarps : 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 5) {
+  if (warp == P::kMmaWarp) {
     const uint32_t slot = smem_u32(const_cast<uint32_t*>(&misc[0]));
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(512u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -193,9 +260,9 @@ attn_paged_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   tc_fence_after();
   const uint32_t tmem_base = misc[0];
   const uint32_t tmem_o = tmem_base + 256;
-  pdl_wait();   // q and the cache rows of this step come from the preceding kernel
+  pdl_wait();   // q and the K/V rows of this step come from the preceding kernel
 
-  if (warp == 4) {
+  if (warp == P::kProducerWarp) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
       AtRing kr, vr, qr;
@@ -216,21 +283,22 @@ attn_paged_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         return true;
       };
       for (int wave = 0; wave < waves && ok; ++wave) {
-        const AtUnit w = at_unit(a, order, bs, units, wave);
+        const AtUnit w = at_unit<STAIR>(a, order, units, wave);
         if (w.ntiles == 0) continue;
         if (!mbar_wait(bar(kAtBarQEmpty + qr.stage), qr.phase ^ 1)) { ok = false; break; }
         {
           const uint32_t full = bar(kAtBarQFull + qr.stage);
-          const uint32_t dst = base + kAtOffQ + qr.stage * kAtQBytes;
-          mbar_arrive_expect_tx(full, static_cast<uint32_t>(rows_total) * 256u);
-          tma_load_3d(dst, &map_q, 0, w.kvh * group, w.req * a.block, full);
-          tma_load_3d(dst + kAtRows * 128, &map_q, 64, w.kvh * group, w.req * a.block, full);
+          const uint32_t dst = base + P::kOffQ + qr.stage * P::kQBytes;
+          mbar_arrive_expect_tx(full, static_cast<uint32_t>(rows_used) * 256u);
+          tma_load_3d(dst, &map_q, 0, w.kvh * group, w.q_tok0, full);
+          tma_load_3d(dst + ROWS * 128, &map_q, 64, w.kvh * group, w.q_tok0, full);
           pend_q |= 1u << qr.stage;
           par_q = (par_q & ~(1u << qr.stage)) | (qr.phase << qr.stage);
-          qr.advance(2);
+          qr.advance(P::kQBufs);
         }
         auto token_row = [&](int tile) {
           const int key0 = w.kbeg + tile * kAtKeys;
+          if (STAIR) return w.seq_start + key0;
           int page = a.block_table[static_cast<int64_t>(w.req) * a.table_stride + key0 / kPage];
           if (page < 0 || page >= a.num_pages) {
             report_status(MDB_STATUS_BAD_PAGE);
@@ -240,21 +308,23 @@ attn_paged_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         };
         // in the order the MMA warp needs them: K0 K1 V0 K2 V1 ...
         for (int j = 0; j < w.ntiles && ok; ++j) {
-          if (j == 0) ok = load_tile(&map_k, base + kAtOffK, kAtBarKFull, kAtBarKEmpty, kAtKStages, kr, pend_k, par_k, w.kvh, token_row(0));
+          if (j == 0)
+            ok = load_tile(&map_k, base + P::kOffK, kAtBarKFull, kAtBarKEmpty, P::kKStages, kr, pend_k, par_k, w.kvh, token_row(0));
           if (ok && j + 1 < w.ntiles)
-            ok = load_tile(&map_k, base + kAtOffK, kAtBarKFull, kAtBarKEmpty, kAtKStages, kr, pend_k, par_k, w.kvh, token_row(j + 1));
-          if (ok) ok = load_tile(&map_v, base + kAtOffV, kAtBarVFull, kAtBarVEmpty, kAtVStages, vr, pend_v, par_v, w.kvh, token_row(j));
+            ok = load_tile(&map_k, base + P::kOffK, kAtBarKFull, kAtBarKEmpty, P::kKStages, kr, pend_k, par_k, w.kvh, token_row(j + 1));
+          if (ok)
+            ok = load_tile(&map_v, base + P::kOffV, kAtBarVFull, kAtBarVEmpty, P::kVStages, vr, pend_v, par_v, w.kvh, token_row(j));
         }
       }
       if (!ok) {
         report_status(MDB_STATUS_WAIT_TIMEOUT);
         // let the copies already issued land before the CTA gives its shared memory back
-        for (int s = 0; s < kAtKStages; ++s) if (pend_k >> s & 1) mbar_wait(bar(kAtBarKFull + s), par_k >> s & 1);
-        for (int s = 0; s < kAtVStages; ++s) if (pend_v >> s & 1) mbar_wait(bar(kAtBarVFull + s), par_v >> s & 1);
-        for (int s = 0; s < 2; ++s) if (pend_q >> s & 1) mbar_wait(bar(kAtBarQFull + s), par_q >> s & 1);
+        for (int s = 0; s < P::kKStages; ++s) if (pend_k >> s & 1) mbar_wait(bar(kAtBarKFull + s), par_k >> s & 1);
+        for (int s = 0; s < P::kVStages; ++s) if (pend_v >> s & 1) mbar_wait(bar(kAtBarVFull + s), par_v >> s & 1);
+        for (int s = 0; s < P::kQBufs; ++s) if (pend_q >> s & 1) mbar_wait(bar(kAtBarQFull + s), par_q >> s & 1);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == P::kMmaWarp) {
     // ----------------------------------------------------------------- MMA issue
     if (lane == 0) {
       // bf16 x bf16 -> fp32, M = 128, N = 128; bit 16 set: B operand MN-major
@@ -266,26 +336,27 @@ attn_paged_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       uint32_t o_phase = 0;             // parity of the o_empty phase to wait for
       bool ok = true;
       for (int wave = 0; wave < waves && ok; ++wave) {
-        const AtUnit w = at_unit(a, order, bs, units, wave);
+        const AtUnit w = at_unit<STAIR>(a, order, units, wave);
         if (w.ntiles == 0) continue;
-        if (!mbar_wait(bar(kAtBarQFull + qr.stage), qr.phase)) { ok = false; break; }
-        const uint32_t q_tile = base + kAtOffQ + qr.stage * kAtQBytes;
+        // staircase form: the softmax warps scale q in place first
+        if (!mbar_wait(bar((STAIR ? kAtBarQReady : kAtBarQFull) + qr.stage), qr.phase)) { ok = false; break; }
+        const uint32_t q_tile = base + P::kOffQ + qr.stage * P::kQBytes;
         auto issue_s = [&](int j) {
           if (!mbar_wait(bar(kAtBarKFull + kr.stage), kr.phase)) return false;
           if (!mbar_wait(bar(kAtBarSEmpty + sr.stage), sr.phase ^ 1)) return false;
           tc_fence_after();
-          const uint32_t k_tile = base + kAtOffK + kr.stage * kAtTileBytes;
+          const uint32_t k_tile = base + P::kOffK + kr.stage * kAtTileBytes;
           const uint32_t d_tmem = tmem_base + sr.stage * kAtKeys;
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
-            const uint64_t adesc = umma_desc_sw128(q_tile + (kk >> 2) * (kAtRows * 128)) + 2 * (kk & 3);
+            const uint64_t adesc = umma_desc_sw128(q_tile + (kk >> 2) * (ROWS * 128)) + 2 * (kk & 3);
             const uint64_t bdesc = umma_desc_sw128(k_tile + (kk >> 2) * kAtHalfBytes) + 2 * (kk & 3);
             umma_bf16(d_tmem, adesc, bdesc, idesc_s, kk > 0 ? 1u : 0u);
           }
           umma_commit(bar(kAtBarKEmpty + kr.stage));
           umma_commit(bar(kAtBarSFull + sr.stage));
           if (j == w.ntiles - 1) umma_commit(bar(kAtBarQEmpty + qr.stage));
-          kr.advance(kAtKStages);
+          kr.advance(P::kKStages);
           sr.advance(2);
           return true;
         };
@@ -301,42 +372,56 @@ attn_paged_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             o_phase ^= 1;
           }
           tc_fence_after();
-          const uint32_t p_tile = base + kAtOffP + pr.stage * kAtPBytes;
-          const uint32_t v_tile = base + kAtOffV + vr.stage * kAtTileBytes;
+          const uint32_t p_tile = base + P::kOffP + pr.stage * P::kPBytes;
+          const uint32_t v_tile = base + P::kOffV + vr.stage * kAtTileBytes;
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
-            const uint64_t adesc = umma_desc_sw128(p_tile + (kk >> 2) * (kAtRows * 128)) + 2 * (kk & 3);
+            const uint64_t adesc = umma_desc_sw128(p_tile + (kk >> 2) * (ROWS * 128)) + 2 * (kk & 3);
             const uint64_t bdesc = umma_desc_sw128_mn(v_tile + kk * 2048);
             umma_bf16(tmem_o, adesc, bdesc, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
           }
           umma_commit(bar(kAtBarVEmpty + vr.stage));
           umma_commit(bar(kAtBarPEmpty + pr.stage));
           if (j == w.ntiles - 1) umma_commit(bar(kAtBarOFull));
-          vr.advance(kAtVStages);
+          vr.advance(P::kVStages);
           pr.advance(2);
         }
-        qr.advance(2);
+        qr.advance(P::kQBufs);
       }
       if (!ok) report_status(MDB_STATUS_WAIT_TIMEOUT);
     }
-  } else if (warp < kAtSoftmaxWarps) {
+  } else {
     // ------------------------------------------------------------------- softmax
     const int row = 32 * warp + lane;
-    const bool row_valid = row < rows_total;
-    const int tok = row_valid ? row / group : 0;
-    const int head_in_group = row_valid ? row % group : 0;
+    const int tok_local = row / group, head_in_group = row % group;
     const uint32_t lane_field = static_cast<uint32_t>(32 * warp) << 16;
-    AtRing sr, pr, vr;                 // positions of the tile being handled in the S, P and V rings
+    AtRing sr, pr, vr, qr;             // positions of the tile being handled in the S, P, V and Q rings
     uint32_t prev_p_stage = 0, prev_p_phase = 0;   // P ring position of the previous tile (its P V frees O for a rescale)
     uint32_t o_phase = 0;
     bool ok = true;
     for (int wave = 0; wave < waves && ok; ++wave) {
-      const AtUnit w = at_unit(a, order, bs, units, wave);
+      const AtUnit w = at_unit<STAIR>(a, order, units, wave);
       if (!w.valid) continue;
       const int head = w.kvh * group + head_in_group;
-      const int64_t prow = ((static_cast<int64_t>(w.req) * a.nsplit + w.split) * a.hq + head) * a.block + tok;
-      bf16* out_row = a.out + ((static_cast<int64_t>(w.req) * a.block + tok) * a.hq + head) * kHeadDim;
-      if (w.ntiles == 0) {
+      bool row_valid = row < rows_used;
+      int limit = 0;                 // staircase form: last key this row sees
+      bf16* out_row;
+      int64_t prow = 0;
+      if (STAIR) {
+        const int i = w.m0 + tok_local;
+        row_valid = row_valid && i < w.T;
+        const int S = 1 << a.log2_stairs;
+        const int pad = ((w.T + S - 1) >> a.log2_stairs << a.log2_stairs) - w.T;
+        limit = row_valid ? min(w.T - 1, ((((i + pad) >> a.log2_stairs) + 1) << a.log2_stairs) - 1 - pad) : -1;
+        out_row = a.out + static_cast<int64_t>(w.seq_start + (row_valid ? i : 0)) * a.out_stride + head * kHeadDim;
+      } else {
+        const int tok = w.tok0 + tok_local;
+        row_valid = row_valid && tok < a.block;
+        const int tk = row_valid ? tok : 0;
+        prow = ((static_cast<int64_t>(w.req) * a.nsplit + w.split) * a.hq + head) * a.block + tk;
+        out_row = a.out + ((static_cast<int64_t>(w.req) * a.block + tk) * a.hq + head) * kHeadDim;
+      }
+      if (w.ntiles == 0) {           // paged form only: an empty key range
         if (row_valid) {
           if (a.nsplit == 1) {
 #pragma unroll
@@ -350,6 +435,30 @@ attn_paged_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
         continue;
       }
+      if (STAIR) {
+        // q * log2(e)/sqrt(D) rounded to bf16, in place (elementwise, so the swizzle does not matter)
+        ok = mbar_wait(bar(kAtBarQFull + qr.stage), qr.phase);
+        if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+        if (row < rows_used) {
+          const uint32_t q_row = base + P::kOffQ + qr.stage * P::kQBytes + row * 128;
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            const uint32_t addr = q_row + (c >> 3) * (ROWS * 128) + (c & 7) * 16;
+            uint32_t x[4];
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3]) : "r"(addr));
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = unpack_bf16x2(x[e]);
+              x[e] = pack_bf16x2(f.x * a.q_scale, f.y * a.q_scale);
+            }
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x[0]), "r"(x[1]), "r"(x[2]), "r"(x[3]) : "memory");
+          }
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(kAtBarQReady + qr.stage));
+        qr.advance(P::kQBufs);
+      }
       float m_ref = -INFINITY, l = 0.f;
       for (int j = 0; j < w.ntiles; ++j) {
         ok = mbar_wait(bar(kAtBarSFull + sr.stage), sr.phase);
@@ -357,7 +466,8 @@ attn_paged_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         tc_fence_after();
         const uint32_t s_addr = tmem_base + sr.stage * kAtKeys + lane_field;
         const int key0 = w.kbeg + j * kAtKeys;
-        const int nvalid = min(kAtKeys, w.kend - key0);      // >= 1
+        // keys of this tile the row sees: [0, nvalid)
+        const int nvalid = STAIR ? max(0, min(kAtKeys, limit + 1 - key0)) : min(kAtKeys, w.kend - key0);
         // the whole score row into registers, then the S buffer goes back to the MMA warp
         float s[kAtKeys];
 #pragma unroll
@@ -379,7 +489,8 @@ attn_paged_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         float mx = fmaxf(mx0, mx1);
         if (!row_valid) mx = 0.f;                             // rows past the block hold whatever the tile held
         const float m_tile = mx * a.scale_log2;
-        const bool grow = m_tile > m_ref + kAtRescaleStep || m_ref == -INFINITY;
+        // a row that sees no key of this tile (staircase form, rows above the tile's diagonal) keeps its state
+        const bool grow = m_tile > m_ref + kAtRescaleStep || (m_ref == -INFINITY && m_tile != -INFINITY);
         if (__any_sync(0xffffffffu, grow)) {
           const float m_new = fmaxf(m_ref, m_tile);
           const float f = m_ref == -INFINITY ? 0.f : ex2_approx(m_ref - m_new);
@@ -403,12 +514,13 @@ attn_paged_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           m_ref = m_new;
         }
         // P = 2^(s * scale - m_ref) rounded to bf16; a masked key gives 2^-inf = 0
+        const float m_use = m_ref == -INFINITY ? 0.f : m_ref;   // nothing seen yet: every s is -inf, P = 0
         uint32_t pk[kAtKeys / 2];
         float l0 = 0.f, l1 = 0.f;
 #pragma unroll
         for (int i = 0; i < kAtKeys; i += 2) {
-          const float p0 = ex2_approx(fmaf(s[i], a.scale_log2, -m_ref));
-          const float p1 = ex2_approx(fmaf(s[i + 1], a.scale_log2, -m_ref));
+          const float p0 = ex2_approx(fmaf(s[i], a.scale_log2, -m_use));
+          const float p1 = ex2_approx(fmaf(s[i + 1], a.scale_log2, -m_use));
           l0 += p0;
           l1 += p1;
           pk[i >> 1] = pack_bf16x2(p0, p1);
@@ -418,20 +530,20 @@ attn_paged_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         ok = mbar_wait(bar(kAtBarPEmpty + pr.stage), pr.phase ^ 1);
         if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
         // K-major swizzled P tile: 16-byte chunk q of key half h holds keys 64 h + 8 q .. + 7
-        const uint32_t p_row = base + kAtOffP + pr.stage * kAtPBytes + row * 128;
+        const uint32_t p_row = base + P::kOffP + pr.stage * P::kPBytes + row * 128;
 #pragma unroll
         for (int q = 0; q < 16; ++q) {
           const uint32_t chunk = static_cast<uint32_t>(q & 7) ^ static_cast<uint32_t>(row & 7);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + (q >> 3) * (kAtRows * 128) + (chunk << 4)),
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + (q >> 3) * (ROWS * 128) + (chunk << 4)),
                        "r"(pk[4 * q]), "r"(pk[4 * q + 1]), "r"(pk[4 * q + 2]), "r"(pk[4 * q + 3])
                        : "memory");
         }
-        if (nvalid < kAtKeys) {
+        if (!STAIR && nvalid < kAtKeys) {
           // stale cache rows past the context end must not reach O through 0 * (Inf or NaN): clear them in V
           ok = mbar_wait(bar(kAtBarVFull + vr.stage), vr.phase);
           if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-          const uint32_t v_tile = base + kAtOffV + vr.stage * kAtTileBytes;
-          for (int r = nvalid + row; r < kAtKeys; r += 32 * kAtSoftmaxWarps) {
+          const uint32_t v_tile = base + P::kOffV + vr.stage * kAtTileBytes;
+          for (int r = nvalid + row; r < kAtKeys; r += ROWS) {
 #pragma unroll
             for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -448,7 +560,7 @@ attn_paged_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         prev_p_phase = pr.phase;
         sr.advance(2);
         pr.advance(2);
-        vr.advance(kAtVStages);
+        vr.advance(P::kVStages);
       }
       if (!ok) break;
       // ------------------------------------------------------------- unit epilogue
@@ -456,7 +568,7 @@ attn_paged_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
       o_phase ^= 1;
       tc_fence_after();
-      if (a.nsplit == 1) {
+      if (STAIR || a.nsplit == 1) {
         const float inv = l > 0.f ? 1.0f / l : 0.f;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
@@ -494,7 +606,7 @@ attn_paged_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == P::kMmaWarp) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
   }
@@ -503,24 +615,28 @@ attn_paged_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 // ---- host side ---------------------------------------------------------------
 struct QMapKey {
   const void* ptr;
-  int64_t tokens;
-  int hq, group, block;
+  int64_t tokens, row_stride;
+  int hq, group, box_tokens;
   bool operator==(const QMapKey& o) const {
-    return ptr == o.ptr && tokens == o.tokens && hq == o.hq && group == o.group && block == o.block;
+    return ptr == o.ptr && tokens == o.tokens && row_stride == o.row_stride && hq == o.hq && group == o.group &&
+           box_tokens == o.box_tokens;
   }
 };
 struct QMapKeyHash {
   size_t operator()(const QMapKey& k) const {
     return reinterpret_cast<size_t>(k.ptr) ^ static_cast<size_t>(k.tokens) * 0x9e3779b97f4a7c15ull ^
-           static_cast<size_t>(k.hq * 131 + k.group * 17 + k.block);
+           static_cast<size_t>(k.row_stride) * 0xc2b2ae3d27d4eb4full ^
+           static_cast<size_t>(k.hq * 131 + k.group * 17 + k.box_tokens);
   }
 };
 
-// Tensor map of q [tokens, hq, 128] bf16 read in boxes of 64 channels x group heads x block tokens.
-static bool get_q_tensor_map(const void* ptr, int64_t tokens, int hq, int group, int block, CUtensorMap* out) {
+// Tensor map of q [tokens, hq, 128] bf16 (token stride row_stride elements) read in boxes of
+// 64 channels x group heads x box_tokens tokens.
+static bool get_q_tensor_map(const void* ptr, int64_t tokens, int64_t row_stride, int hq, int group, int box_tokens,
+                             CUtensorMap* out) {
   static std::mutex mu;
   static std::unordered_map<QMapKey, CUtensorMap, QMapKeyHash> cache;
-  const QMapKey key{ptr, tokens, hq, group, block};
+  const QMapKey key{ptr, tokens, row_stride, hq, group, box_tokens};
   std::lock_guard<std::mutex> lock(mu);
   auto it = cache.find(key);
   if (it != cache.end()) {
@@ -531,8 +647,8 @@ static bool get_q_tensor_map(const void* ptr, int64_t tokens, int hq, int group,
   if (enc == nullptr) return false;
   CUtensorMap m;
   const cuuint64_t dims[3] = {static_cast<cuuint64_t>(kHeadDim), static_cast<cuuint64_t>(hq), static_cast<cuuint64_t>(tokens)};
-  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(kHeadDim) * 2, static_cast<cuuint64_t>(hq) * kHeadDim * 2};
-  const cuuint32_t box[3] = {64u, static_cast<cuuint32_t>(group), static_cast<cuuint32_t>(block)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(kHeadDim) * 2, static_cast<cuuint64_t>(row_stride) * 2};
+  const cuuint32_t box[3] = {64u, static_cast<cuuint32_t>(group), static_cast<cuuint32_t>(box_tokens)};
   const cuuint32_t estr[3] = {1, 1, 1};
   if (enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -544,13 +660,7 @@ static bool get_q_tensor_map(const void* ptr, int64_t tokens, int hq, int group,
   return true;
 }
 
-static bool attn_tc_supported(int block, int hq, int hkv, float softmax_scale) {
-  if (hkv <= 0 || hq % hkv != 0) return false;
-  const int group = hq / hkv;
-  return group * block <= kAtRows && block <= 256 && group <= 256 && softmax_scale > 0.f;
-}
-
-static int attn_tc_launch(const AttnPagedArgs& a, int bs, cudaStream_t st) {
+static int at_sm_count() {
   static int sm_count = 0;
   if (sm_count == 0) {
     int dev = 0;
@@ -558,22 +668,90 @@ static int attn_tc_launch(const AttnPagedArgs& a, int bs, cudaStream_t st) {
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (sm_count <= 0) sm_count = 148;
   }
-  CUtensorMap map_q, map_k, map_v;
-  const int64_t cache_rows = static_cast<int64_t>(a.num_pages) * kPage;
-  if (!get_q_tensor_map(a.q, static_cast<int64_t>(bs) * a.block, a.hq, a.hq / a.hkv, a.block, &map_q)) return MDB_ERR_CUDA;
-  if (!get_tensor_map(a.k_cache, cache_rows, a.hkv * kHeadDim, a.hkv * kHeadDim, kAtKeys, &map_k)) return MDB_ERR_CUDA;
-  if (!get_tensor_map(a.v_cache, cache_rows, a.hkv * kHeadDim, a.hkv * kHeadDim, kAtKeys, &map_v)) return MDB_ERR_CUDA;
+  return sm_count;
+}
+
+template <int ROWS, bool STAIR>
+static int at_launch(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, const AtArgs& a,
+                     int64_t units, cudaStream_t st) {
+  using P = AtPlan<ROWS>;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(attn_paged_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAtSmemBytes) != cudaSuccess)
+    if (cudaFuncSetAttribute(attn_tc_kernel<ROWS, STAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, P::kSmemBytes) !=
+        cudaSuccess)
       return MDB_ERR_CUDA;
     attr_set = true;
   }
-  const int64_t units = static_cast<int64_t>(bs) * a.hkv * a.nsplit;
   if (units > (1 << 30)) return MDB_ERR_UNSUPPORTED;
-  const int grid = units < sm_count ? static_cast<int>(units) : sm_count;
-  return mdb_launch(attn_paged_tc_kernel, dim3(grid), dim3(kAtThreads), kAtSmemBytes, st, map_q, map_k, map_v, a, bs,
+  const int sms = at_sm_count();
+  const int grid = units < sms ? static_cast<int>(units) : sms;
+  return mdb_launch(attn_tc_kernel<ROWS, STAIR>, dim3(grid), dim3(P::kThreads), P::kSmemBytes, st, map_q, map_k, map_v, a,
                     static_cast<int>(units));
+}
+
+// ---- paged form ----
+static bool attn_tc_supported(int block, int hq, int hkv, float softmax_scale) {
+  if (hkv <= 0 || hq % hkv != 0) return false;
+  const int group = hq / hkv;
+  return group <= 128 && block >= 1 && block <= 256 && softmax_scale > 0.f;
+}
+
+static int attn_tc_launch(const AttnPagedArgs& pa, int bs, cudaStream_t st) {
+  AtArgs a = {};
+  a.q = pa.q;
+  a.out = pa.out;
+  a.hq = pa.hq; a.hkv = pa.hkv; a.group = pa.hq / pa.hkv;
+  a.scale_log2 = pa.scale_log2;
+  a.block_table = pa.block_table;
+  a.ctx_lens = pa.ctx_lens;
+  a.part_o = pa.part_o;
+  a.part_ml = pa.part_ml;
+  a.table_stride = pa.table_stride;
+  a.block = pa.block;
+  a.num_pages = pa.num_pages;
+  a.nsplit = pa.nsplit;
+  a.bs = bs;
+  const int rows = a.group * pa.block <= 64 ? 64 : 128;
+  a.tokens_per_unit = rows / a.group < pa.block ? rows / a.group : pa.block;
+  a.row_blocks = (pa.block + a.tokens_per_unit - 1) / a.tokens_per_unit;
+  CUtensorMap map_q, map_k, map_v;
+  const int64_t cache_rows = static_cast<int64_t>(pa.num_pages) * kPage;
+  if (!get_q_tensor_map(pa.q, static_cast<int64_t>(bs) * pa.block, static_cast<int64_t>(pa.hq) * kHeadDim, pa.hq, a.group,
+                        a.tokens_per_unit, &map_q))
+    return MDB_ERR_CUDA;
+  if (!get_tensor_map(pa.k_cache, cache_rows, pa.hkv * kHeadDim, pa.hkv * kHeadDim, kAtKeys, &map_k)) return MDB_ERR_CUDA;
+  if (!get_tensor_map(pa.v_cache, cache_rows, pa.hkv * kHeadDim, pa.hkv * kHeadDim, kAtKeys, &map_v)) return MDB_ERR_CUDA;
+  const int64_t units = static_cast<int64_t>(bs) * pa.hkv * a.row_blocks * pa.nsplit;
+  return rows == 64 ? at_launch<64, false>(map_q, map_k, map_v, a, units, st)
+                    : at_launch<128, false>(map_q, map_k, map_v, a, units, st);
+}
+
+// ---- staircase form ----
+static bool attn_stair_tc_supported(int hq, int hkv, int64_t q_stride, int64_t k_stride, int64_t v_stride) {
+  if (hkv <= 0 || hq % hkv != 0 || hq / hkv > 128) return false;
+  return q_stride % 8 == 0 && k_stride % 8 == 0 && v_stride % 8 == 0;
+}
+
+static int attn_stair_tc_launch(const AttnStairArgs& sa, int nseq, int max_seqlen, int64_t total_tokens, cudaStream_t st) {
+  AtArgs a = {};
+  a.q = sa.q;
+  a.out = sa.out;
+  a.hq = sa.hq; a.hkv = sa.hkv; a.group = sa.hq / sa.hkv;
+  a.scale_log2 = 1.0f;
+  a.q_scale = sa.q_scale;
+  a.cu_seqlens = sa.cu_seqlens;
+  a.out_stride = sa.out_stride;
+  a.nseq = nseq;
+  a.log2_stairs = sa.log2_stairs;
+  a.tokens_per_unit = 128 / a.group;
+  a.max_qtiles = (max_seqlen + a.tokens_per_unit - 1) / a.tokens_per_unit;
+  a.nsplit = 1;
+  CUtensorMap map_q, map_k, map_v;
+  if (!get_q_tensor_map(sa.q, total_tokens, sa.q_stride, sa.hq, a.group, a.tokens_per_unit, &map_q)) return MDB_ERR_CUDA;
+  if (!get_tensor_map(sa.k, total_tokens, sa.hkv * kHeadDim, sa.k_stride, kAtKeys, &map_k)) return MDB_ERR_CUDA;
+  if (!get_tensor_map(sa.v, total_tokens, sa.hkv * kHeadDim, sa.v_stride, kAtKeys, &map_v)) return MDB_ERR_CUDA;
+  const int64_t units = static_cast<int64_t>(a.max_qtiles) * nseq * sa.hkv;
+  return at_launch<128, true>(map_q, map_k, map_v, a, units, st);
 }
 
 }  // namespace mdb

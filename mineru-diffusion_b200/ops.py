@@ -185,7 +185,7 @@ def sparse_attn_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seq
         out = torch.empty((n, hq, d), dtype=_BF16, device=q.device)
     _lib.check(_lib.lib().mdb_attn_staircase_varlen(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(),
                                                     v.stride(0), out.data_ptr(), out.stride(0),
-                                                    cu_seqlens_q.data_ptr(), nseq, max_seqlen, hq, hkv,
+                                                    cu_seqlens_q.data_ptr(), nseq, max_seqlen, n, hq, hkv,
                                                     staircase_size, _stream()), "mdb_attn_staircase_varlen")
     return out
 

@@ -416,8 +416,8 @@ def test_attn_paged_properties_at_full_size(mdb, attn_kernel):
 
 # --------------------------------------------------------------------- staircase prefill attention
 @pytest.mark.parametrize("stairs", [8, 32])
-@pytest.mark.parametrize("hq,hkv", [(16, 2), (4, 2)])
-def test_attn_staircase_vs_oracle(mdb, stairs, hq, hkv):
+@pytest.mark.parametrize("hq,hkv", [(16, 2), (4, 2), (4, 4), (6, 2)])
+def test_attn_staircase_vs_oracle(mdb, attn_kernel, stairs, hq, hkv):
     gen = torch.Generator().manual_seed(stairs + hq)
     lens = [288 + 5, 32, 1, 700, 95]
     cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32)
@@ -432,7 +432,7 @@ def test_attn_staircase_vs_oracle(mdb, stairs, hq, hkv):
     _status_clean(mdb)
 
 
-def test_attn_staircase_config1_and_golden(mdb):
+def test_attn_staircase_config1_and_golden(mdb, attn_kernel):
     """BASELINE config 1 prefill form (every row of prefix+block is a query)
     and the reference Triton kernel's own fp32 outputs."""
     gen = torch.Generator().manual_seed(1)
@@ -453,6 +453,32 @@ def test_attn_staircase_config1_and_golden(mdb):
         got = mdb.ops.sparse_attn_varlen(q.to(DEV), k.to(DEV), v.to(DEV), cu.to(DEV), cu.to(DEV), stairs).cpu()
         ref = torch.from_numpy(g[f"out_fp32_s{stairs}"])       # fp32 kernel on fp16-rounded inputs
         assert (got.float() - ref).abs().max() <= 3e-2
+
+
+def test_attn_staircase_long_sequences_kernels_agree(mdb):
+    """Prefill shapes too long for the CPU oracle (the decoder's 16 query / 8 KV
+    heads, sequences up to 3001 tokens, lengths around the 128-key tile edges):
+    the tcgen05 kernel against the mma.sync kernel, which the oracle pins on
+    the short cases above, and one short sequence of the batch against the oracle."""
+    gen = torch.Generator(device=DEV).manual_seed(11)
+    lens = [1, 31, 32, 33, 127, 128, 129, 1000, 3001, 257]
+    cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32)
+    n = int(cu[-1])
+    q = torch.randn(n, 16, 128, generator=gen, device=DEV).to(BF)
+    k = torch.randn(n, 8, 128, generator=gen, device=DEV).to(BF)
+    v = torch.randn(n, 8, 128, generator=gen, device=DEV).to(BF)
+    outs = {}
+    for name, opt in (("mma", 1), ("tc", 2)):
+        mdb.ops.set_option(mdb.ops.OPT_ATTN_KERNEL, opt)
+        outs[name] = mdb.ops.sparse_attn_varlen(q, k, v, cu.to(DEV), cu.to(DEV), 32)
+    mdb.ops.set_option(mdb.ops.OPT_ATTN_KERNEL, 0)
+    err = (outs["tc"].float() - outs["mma"].float()).abs()
+    assert float(err.max()) <= 2e-2 and float(err.mean()) <= 3e-4, (float(err.max()), float(err.mean()))
+    a, b = int(cu[4]), int(cu[5])           # the 127-token sequence
+    one = torch.tensor([0, b - a], dtype=torch.int32)
+    want = orc.attn_staircase_varlen(q[a:b].cpu(), k[a:b].cpu(), v[a:b].cpu(), one, one, 32, mirror_rounding=True)
+    assert float((outs["tc"][a:b].cpu().float() - want.float()).abs().max()) <= 2e-2
+    _status_clean(mdb)
 
 
 # --------------------------------------------------------------------- LM head + sampler

@@ -303,6 +303,12 @@ __device__ __forceinline__ void attn_combine_row(const float* __restrict__ part_
   const int64_t p0 = (static_cast<int64_t>(req) * nsplit * hq + head) * block + tok;   // split 0
   const int64_t pstride = static_cast<int64_t>(hq) * block;                             // between splits
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  // The O rows of the first eight parts are requested before anything depends on the (max, sum) records, so
+  // that records and rows come back in one L2 round trip (every part's row is written, empty parts with zeros).
+  float4 first[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    if (i < nsplit) first[i] = *reinterpret_cast<const float4*>(part_o + (p0 + i * pstride) * kHeadDim + lane * 4);
   float mmax = -INFINITY;
   for (int s0 = 0; s0 < nsplit; s0 += 32) {   // running max over all splits
     const int s = s0 + lane;
@@ -322,12 +328,23 @@ __device__ __forceinline__ void attn_combine_row(const float* __restrict__ part_
       }
       lsum += w * l;
       const int cnt = min(32, nsplit - s0);
-#pragma unroll 4
-      for (int j = 0; j < cnt; ++j) {
-        const float wj = __shfl_sync(0xffffffffu, w, j);
-        if (wj != 0.f) {
-          const float4 v = *reinterpret_cast<const float4*>(part_o + (p0 + (s0 + j) * pstride) * kHeadDim + lane * 4);
-          acc[0] += wj * v.x; acc[1] += wj * v.y; acc[2] += wj * v.z; acc[3] += wj * v.w;
+      for (int j0 = 0; j0 < cnt; j0 += 8) {     // eight parts' rows in flight together, accumulated in part order
+        float4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (j0 + i < cnt) {
+            if (s0 + j0 == 0) v[i] = first[i];
+            else v[i] = *reinterpret_cast<const float4*>(part_o + (p0 + (s0 + j0 + i) * pstride) * kHeadDim + lane * 4);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (j0 + i < cnt) {
+            const float wj = __shfl_sync(0xffffffffu, w, j0 + i);
+            if (wj != 0.f) {
+              acc[0] += wj * v[i].x; acc[1] += wj * v[i].y; acc[2] += wj * v[i].z; acc[3] += wj * v[i].w;
+            }
+          }
         }
       }
     }
@@ -343,11 +360,14 @@ __device__ __forceinline__ void attn_combine_row(const float* __restrict__ part_
 
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     bf16* __restrict__ out, int bs, int block, int hq, int nsplit) {
+  if (threadIdx.x == 0) trace_event(31, 0);
   pdl_launch_dependents();
   pdl_wait();
+  if (threadIdx.x == 0) trace_event(31, 1);
   const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (warp_global >= bs * hq * block) return;
   attn_combine_row(part_o, part_ml, out, block, hq, nsplit, warp_global, threadIdx.x & 31);
+  if (threadIdx.x == 0) trace_event(31, 2);
 }
 
 // ---------------------------------------------------------------------------

@@ -38,6 +38,8 @@ __global__ void kv_commit_kernel(const bf16* __restrict__ key, int64_t key_strid
 constexpr int kNormThreads = 256;
 constexpr int kNormMaxChunks = 4;  // h <= 256 * 4 * 8 = 8192
 
+// PARTIALS: the input row is the sum of fp32 slices (short steps; latency-bound, loads batched) or a bf16 row.
+template <bool PARTIALS>
 __global__ void __launch_bounds__(kNormThreads)
 add_rmsnorm_kernel(const bf16* __restrict__ x, const float* __restrict__ partials, int nparts,
                    const bf16* __restrict__ residual_in, const bf16* __restrict__ weight, float eps,
@@ -57,15 +59,30 @@ add_rmsnorm_kernel(const bf16* __restrict__ x, const float* __restrict__ partial
     const int c = threadIdx.x + it * kNormThreads;
     if (c < chunks) {
       float a[8];
-      if (partials != nullptr) {
+      if (PARTIALS) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) a[j] = 0.f;
-        for (int p = 0; p < nparts; ++p) {
-          const float4* src =
-              reinterpret_cast<const float4*>(partials + (static_cast<int64_t>(p) * m + row) * h + c * 8);
-          const float4 lo = src[0], hi = src[1];
-          a[0] += lo.x; a[1] += lo.y; a[2] += lo.z; a[3] += lo.w;
-          a[4] += hi.x; a[5] += hi.y; a[6] += hi.z; a[7] += hi.w;
+        // slices are summed in slice order; the loads of eight slices go out together (one L2 round trip
+        // instead of eight dependent ones: this kernel is pure latency at 32 rows)
+        const int64_t pstride = static_cast<int64_t>(m) * h;
+        const float* src0 = partials + static_cast<int64_t>(row) * h + c * 8;
+        for (int p0 = 0; p0 < nparts; p0 += 8) {
+          float4 lo[8], hi[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (p0 + i < nparts) {
+              const float4* src = reinterpret_cast<const float4*>(src0 + (p0 + i) * pstride);
+              lo[i] = src[0];
+              hi[i] = src[1];
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (p0 + i < nparts) {
+              a[0] += lo[i].x; a[1] += lo[i].y; a[2] += lo[i].z; a[3] += lo[i].w;
+              a[4] += hi[i].x; a[5] += hi[i].y; a[6] += hi[i].z; a[7] += hi[i].w;
+            }
+          }
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) a[j] = bf16_round(a[j]);  // the rounding F.linear applies to its output
@@ -153,11 +170,21 @@ __device__ __forceinline__ void qknorm_rope_commit_warp(
   float a[4];  // elements 2l, 2l+1, 2l+64, 2l+65
   if (partials != nullptr) {
     a[0] = a[1] = a[2] = a[3] = 0.f;
-    for (int p = 0; p < nparts; ++p) {
-      const float* src = partials + (static_cast<int64_t>(p) * m + token) * ncols + col0;
-      const float2 lo = *reinterpret_cast<const float2*>(src);
-      const float2 hi = *reinterpret_cast<const float2*>(src + 64);
-      a[0] += lo.x; a[1] += lo.y; a[2] += hi.x; a[3] += hi.y;
+    const int64_t pstride = static_cast<int64_t>(m) * ncols;
+    const float* src0 = partials + static_cast<int64_t>(token) * ncols + col0;
+    for (int p0 = 0; p0 < nparts; p0 += 8) {      // eight slices' loads in flight together, summed in slice order
+      float2 lo[8], hi[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (p0 + i < nparts) {
+          lo[i] = *reinterpret_cast<const float2*>(src0 + (p0 + i) * pstride);
+          hi[i] = *reinterpret_cast<const float2*>(src0 + (p0 + i) * pstride + 64);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (p0 + i < nparts) { a[0] += lo[i].x; a[1] += lo[i].y; a[2] += hi[i].x; a[3] += hi[i].y; }
+      }
     }
 #pragma unroll
     for (int j = 0; j < 4; ++j) a[j] = bf16_round(a[j]);
@@ -233,11 +260,14 @@ qknorm_rope_commit_kernel(const bf16* __restrict__ qkv, int64_t ld_qkv, const fl
                           const int32_t* __restrict__ slot_mapping, bf16* __restrict__ q_out,
                           bf16* __restrict__ k_out, bf16* __restrict__ v_out, bf16* __restrict__ k_cache,
                           bf16* __restrict__ v_cache, int64_t num_slots, int m, int hq, int hkv) {
+  if (threadIdx.x == 0) trace_event(32, 0);
   pdl_launch_dependents();
   pdl_wait();
+  if (threadIdx.x == 0) trace_event(32, 1);
   qknorm_rope_commit_warp(blockIdx.x, blockIdx.y * kRopeWarps + (threadIdx.x >> 5), threadIdx.x & 31, qkv, ld_qkv,
                           partials, nparts, positions, rope_table, max_pos, q_norm_w, k_norm_w, eps, slot_mapping,
                           q_out, k_out, v_out, k_cache, v_cache, num_slots, m, hq, hkv);
+  if (threadIdx.x == 0) trace_event(32, 2);
 }
 
 // ---------------------------------------------------------------------------
@@ -385,7 +415,12 @@ static int add_rmsnorm_impl(const void* x, const float* partials, int nparts, co
   MDB_REQUIRE(mdb_aligned16(x) && mdb_aligned16(partials) && mdb_aligned16(residual_in) && mdb_aligned16(weight) &&
                   mdb_aligned16(y_out) && mdb_aligned16(residual_out),
               MDB_ERR_ALIGN);
-  return mdb_launch(add_rmsnorm_kernel, dim3(m), dim3(kNormThreads), 0, static_cast<cudaStream_t>(stream),
+  if (partials != nullptr)
+    return mdb_launch(add_rmsnorm_kernel<true>, dim3(m), dim3(kNormThreads), 0, static_cast<cudaStream_t>(stream),
+                      static_cast<const bf16*>(x), partials, nparts, static_cast<const bf16*>(residual_in),
+                      static_cast<const bf16*>(weight), eps, static_cast<bf16*>(y_out),
+                      static_cast<bf16*>(residual_out), m, h, tp);
+  return mdb_launch(add_rmsnorm_kernel<false>, dim3(m), dim3(kNormThreads), 0, static_cast<cudaStream_t>(stream),
                     static_cast<const bf16*>(x), partials, nparts, static_cast<const bf16*>(residual_in),
                     static_cast<const bf16*>(weight), eps, static_cast<bf16*>(y_out),
                     static_cast<bf16*>(residual_out), m, h, tp);

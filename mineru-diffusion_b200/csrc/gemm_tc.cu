@@ -110,61 +110,58 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   const uint32_t tmem_base = misc[0];
 
   if (warp == kProducerWarp) {
-    if (lane == 0) {
-      pdl_wait();   // activations come from the preceding kernel
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-        const int tn = t / a.tiles_m, tm = t % a.tiles_m;   // consecutive CTAs: same weight tile
-        for (int c = 0; c < kchunks; ++c) {
-          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1)) { ok = false; break; }
-          const uint32_t full = bar_full + 8 * stage;
-          mbar_arrive_expect_tx(full, kTcABytes + kTcBBytes);
-          tma_load_2d(a_tiles + stage * kTcABytes, &map_x, c * kTcBK, tm * kTcBM, full);
-          const uint32_t bdst = b_tiles + stage * kTcBBytes;
-          if (EPI == kTcSwiglu) {
-            tma_load_2d(bdst, &map_w, c * kTcBK, tn * 128, full);                             // 128 gate rows
-            tma_load_2d(bdst + kTcBBytes / 2, &map_w, c * kTcBK, a.inter + tn * 128, full);   // their up rows
-          } else {
-            tma_load_2d(bdst, &map_w, c * kTcBK, tn * kTcBN, full);
-          }
-          if (++stage == kTcStages) { stage = 0; phase ^= 1; }
+    // the whole warp walks the loop (warp-uniform operands), one elected lane issues each instruction
+    pdl_wait();   // activations come from the preceding kernel
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+      const int tn = t / a.tiles_m, tm = t % a.tiles_m;   // consecutive CTAs: same weight tile
+      for (int c = 0; c < kchunks; ++c) {
+        if (!mbar_wait_w(bar_empty + 8 * stage, phase ^ 1)) { ok = false; break; }
+        const uint32_t full = bar_full + 8 * stage;
+        mbar_arrive_expect_tx_w(full, kTcABytes + kTcBBytes);
+        tma_load_2d_w(a_tiles + stage * kTcABytes, &map_x, c * kTcBK, tm * kTcBM, full);
+        const uint32_t bdst = b_tiles + stage * kTcBBytes;
+        if (EPI == kTcSwiglu) {
+          tma_load_2d_w(bdst, &map_w, c * kTcBK, tn * 128, full);                             // 128 gate rows
+          tma_load_2d_w(bdst + kTcBBytes / 2, &map_w, c * kTcBK, a.inter + tn * 128, full);   // their up rows
+        } else {
+          tma_load_2d_w(bdst, &map_w, c * kTcBK, tn * kTcBN, full);
         }
+        if (++stage == kTcStages) { stage = 0; phase ^= 1; }
       }
-      if (!ok) report_status(MDB_STATUS_WAIT_TIMEOUT);
     }
+    if (!ok && lane == 0) report_status(MDB_STATUS_WAIT_TIMEOUT);
   } else if (warp == kMmaWarp) {
-    if (lane == 0) {
-      // bf16 x bf16 -> fp32, K-major operands, M = 128, N = 256
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kTcBN >> 3) << 17) |
-                             (static_cast<uint32_t>(kTcBM >> 4) << 24);
-      int stage = 0;
-      uint32_t phase = 0;
-      int acc = 0;
-      uint32_t acc_phase = 0;
-      bool ok = true;
-      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-        if (!mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1)) { ok = false; break; }
+    // bf16 x bf16 -> fp32, K-major operands, M = 128, N = 256
+    const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kTcBN >> 3) << 17) |
+                           (static_cast<uint32_t>(kTcBM >> 4) << 24);
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+      if (!mbar_wait_w(bar_acc_empty + 8 * acc, acc_phase ^ 1)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * kTcBN;
+      for (int c = 0; c < kchunks; ++c) {
+        if (!mbar_wait_w(bar_full + 8 * stage, phase)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * kTcBN;
-        for (int c = 0; c < kchunks; ++c) {
-          if (!mbar_wait(bar_full + 8 * stage, phase)) { ok = false; break; }
-          tc_fence_after();
-          const uint64_t adesc = umma_desc_sw128(a_tiles + stage * kTcABytes);
-          const uint64_t bdesc = umma_desc_sw128(b_tiles + stage * kTcBBytes);
+        const uint64_t adesc = umma_desc_sw128(a_tiles + stage * kTcABytes);
+        const uint64_t bdesc = umma_desc_sw128(b_tiles + stage * kTcBBytes);
 #pragma unroll
-          for (int k16 = 0; k16 < kTcBK / 16; ++k16)
-            umma_bf16(d_tmem, adesc + 2 * k16, bdesc + 2 * k16, idesc, (c > 0 || k16 > 0) ? 1u : 0u);
-          umma_commit(bar_empty + 8 * stage);
-          if (++stage == kTcStages) { stage = 0; phase ^= 1; }
-        }
-        if (!ok) break;
-        umma_commit(bar_acc_full + 8 * acc);
-        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        for (int k16 = 0; k16 < kTcBK / 16; ++k16)
+          umma_bf16_w(d_tmem, adesc + 2 * k16, bdesc + 2 * k16, idesc, (c > 0 || k16 > 0) ? 1u : 0u);
+        umma_commit_w(bar_empty + 8 * stage);
+        if (++stage == kTcStages) { stage = 0; phase ^= 1; }
       }
-      if (!ok) report_status(MDB_STATUS_WAIT_TIMEOUT);
+      if (!ok) break;
+      umma_commit_w(bar_acc_full + 8 * acc);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
+    if (!ok && lane == 0) report_status(MDB_STATUS_WAIT_TIMEOUT);
   } else {
     int acc = 0;
     uint32_t acc_phase = 0;

@@ -155,6 +155,50 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ---- warp-collective forms --------------------------------------------------
+// Every lane of a converged warp makes the call with the same arguments and one elected lane issues the
+// instruction.  With the operands warp-uniform the compiler keeps descriptors, coordinates and barrier
+// addresses in the uniform datapath the TMA and tcgen05 instructions read from; issued from a single
+// divergent lane instead, each tcgen05.mma costs ~165 cycles and each TMA tile load ~115 cycles of issue
+// time (measured), against ~50 and ~27 this way -- enough to make small-N MMAs issue-bound.
+__device__ __forceinline__ bool mbar_wait_w(uint32_t bar, uint32_t parity) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity)) != 0;
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx_w(uint32_t bar, uint32_t bytes) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "@q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}"
+      ::"r"(bar), "r"(bytes)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_w(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "@q cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n\t}"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16_w(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_w(uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+      ::"r"(bar)
+      : "memory");
+}
+
 // ---- kernel ------------------------------------------------------------------
 template <int EPI>
 __global__ void __launch_bounds__(kWsThreads, 1)
@@ -214,95 +258,87 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
   if (warp == 4) {
     // ---------------- producer: TMA loads ----------------
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool deps_ready = false;
-      int deferred = 0;           // stages whose activation tile still has to be issued
-      int deferred_stage0 = 0;
-      int deferred_k[16];
-      bool ok = true;
-      for (int task = blockIdx.x; task < tasks && ok; task += gridDim.x) {
-        const int tile = task_tile(task), slice = task_slice(task);
-        const int nchunks = slice_chunks(slice);
-        const int chunk0 = slice * a.chunks_per_slice;
-        for (int c = 0; c < nchunks; ++c) {
-          if (!deps_ready && deferred == a.stages) {
-            // ring full of weight tiles: now the activations are needed
-            trace_event(EPI, 2);
-            pdl_wait();
-            trace_event(EPI, 3);
-            deps_ready = true;
-            for (int d = 0; d < deferred; ++d) {
-              const int s = (deferred_stage0 + d) % a.stages;
-              tma_load_2d(x_tiles + s * x_tile_bytes, &map_x, deferred_k[d], 0, bar_full + 8 * s);
-            }
-            deferred = 0;
-          }
-          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1)) { ok = false; break; }
-          const int kcol = (chunk0 + c) * kWsBK;
-          const uint32_t full = bar_full + 8 * stage;
-          mbar_arrive_expect_tx(full, kWsWTileBytes + x_tile_bytes);
-          const uint32_t wdst = w_tiles + stage * kWsWTileBytes;
-          if (EPI == kWsSwiglu) {
-            tma_load_2d(wdst, &map_w, kcol, tile * 64, full);                       // 64 gate rows
-            tma_load_2d(wdst + kWsWTileBytes / 2, &map_w, kcol, a.inter + tile * 64, full);   // their up rows
-          } else {
-            tma_load_2d(wdst, &map_w, kcol, tile * kWsTileRows, full);
-          }
-          if (deps_ready) {
-            tma_load_2d(x_tiles + stage * x_tile_bytes, &map_x, kcol, 0, full);
-          } else {
-            if (deferred == 0) deferred_stage0 = stage;
-            deferred_k[deferred++] = kcol;
-          }
-          if (++stage == a.stages) { stage = 0; phase ^= 1; }
-        }
+    // The whole warp walks the loop with warp-uniform operands; one elected lane issues each instruction.
+    int stage = 0;
+    uint32_t phase = 0;
+    bool deps_ready = false;
+    int deferred = 0;             // leading chunks (stage d for chunk d) whose activation tile is still to be issued
+    bool ok = true;
+    // k column of the d-th chunk this CTA processes
+    auto kcol_of = [&](int d) {
+      for (int task = blockIdx.x; task < tasks; task += gridDim.x) {
+        const int slice = task_slice(task);
+        const int n = slice_chunks(slice);
+        if (d < n) return (slice * a.chunks_per_slice + d) * kWsBK;
+        d -= n;
       }
-      if (!deps_ready) {
-        trace_event(EPI, 2);
-        pdl_wait();
-        trace_event(EPI, 3);
-        for (int d = 0; d < deferred; ++d) {
-          const int s = (deferred_stage0 + d) % a.stages;
-          tma_load_2d(x_tiles + s * x_tile_bytes, &map_x, deferred_k[d], 0, bar_full + 8 * s);
+      return 0;
+    };
+    auto flush_deferred = [&]() {
+      if (lane == 0) trace_event(EPI, 2);
+      pdl_wait();
+      if (lane == 0) trace_event(EPI, 3);
+      deps_ready = true;
+      for (int d = 0; d < deferred; ++d)
+        tma_load_2d_w(x_tiles + d * x_tile_bytes, &map_x, kcol_of(d), 0, bar_full + 8 * d);
+      deferred = 0;
+    };
+    for (int task = blockIdx.x; task < tasks && ok; task += gridDim.x) {
+      const int tile = task_tile(task), slice = task_slice(task);
+      const int nchunks = slice_chunks(slice);
+      const int chunk0 = slice * a.chunks_per_slice;
+      for (int c = 0; c < nchunks; ++c) {
+        // ring full of weight tiles: now the activations are needed
+        if (!deps_ready && deferred == a.stages) flush_deferred();
+        if (!mbar_wait_w(bar_empty + 8 * stage, phase ^ 1)) { ok = false; break; }
+        const int kcol = (chunk0 + c) * kWsBK;
+        const uint32_t full = bar_full + 8 * stage;
+        mbar_arrive_expect_tx_w(full, kWsWTileBytes + x_tile_bytes);
+        const uint32_t wdst = w_tiles + stage * kWsWTileBytes;
+        if (EPI == kWsSwiglu) {
+          tma_load_2d_w(wdst, &map_w, kcol, tile * 64, full);                       // 64 gate rows
+          tma_load_2d_w(wdst + kWsWTileBytes / 2, &map_w, kcol, a.inter + tile * 64, full);   // their up rows
+        } else {
+          tma_load_2d_w(wdst, &map_w, kcol, tile * kWsTileRows, full);
         }
+        if (deps_ready) tma_load_2d_w(x_tiles + stage * x_tile_bytes, &map_x, kcol, 0, full);
+        else ++deferred;          // the first chunks sit in stages 0, 1, ... in order
+        if (++stage == a.stages) { stage = 0; phase ^= 1; }
       }
-      if (!ok) { misc[1] = 1; report_status(MDB_STATUS_WAIT_TIMEOUT); }
     }
+    if (!deps_ready) flush_deferred();
+    if (!ok && lane == 0) { misc[1] = 1; report_status(MDB_STATUS_WAIT_TIMEOUT); }
   } else if (warp == 5) {
-    // ---------------- MMA issue ----------------
-    if (lane == 0) {
-      const uint32_t idesc = umma_idesc_bf16(a.ntok);
-      int stage = 0;
-      uint32_t phase = 0;
-      int acc = 0;
-      uint32_t acc_phase = 0;
-      bool ok = true;
-      for (int task = blockIdx.x; task < tasks && ok; task += gridDim.x) {
-        const int nchunks = slice_chunks(task_slice(task));
-        if (!mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1)) { ok = false; break; }
+    // ---------------- MMA issue (warp-collective, see above) ----------------
+    const uint32_t idesc = umma_idesc_bf16(a.ntok);
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int task = blockIdx.x; task < tasks && ok; task += gridDim.x) {
+      const int nchunks = slice_chunks(task_slice(task));
+      if (!mbar_wait_w(bar_acc_empty + 8 * acc, acc_phase ^ 1)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * a.ntok;
+      for (int c = 0; c < nchunks; ++c) {
+        if (!mbar_wait_w(bar_full + 8 * stage, phase)) { ok = false; break; }
+        if (c == 0 && lane == 0) trace_event(EPI, 4);
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * a.ntok;
-        for (int c = 0; c < nchunks; ++c) {
-          if (!mbar_wait(bar_full + 8 * stage, phase)) { ok = false; break; }
-          if (c == 0) trace_event(EPI, 4);
-          tc_fence_after();
-          const uint64_t adesc = umma_desc_sw128(w_tiles + stage * kWsWTileBytes);
-          const uint64_t bdesc = umma_desc_sw128(x_tiles + stage * x_tile_bytes);
+        const uint64_t adesc = umma_desc_sw128(w_tiles + stage * kWsWTileBytes);
+        const uint64_t bdesc = umma_desc_sw128(x_tiles + stage * x_tile_bytes);
 #pragma unroll
-          for (int k16 = 0; k16 < kWsBK / 16; ++k16)   // 32 bytes further along k inside the swizzle atom
-            umma_bf16(d_tmem, adesc + 2 * k16, bdesc + 2 * k16, idesc, (c > 0 || k16 > 0) ? 1u : 0u);
-          umma_commit(bar_empty + 8 * stage);          // stage reusable once these MMAs have read it
-          if (++stage == a.stages) { stage = 0; phase ^= 1; }
-        }
-        if (!ok) break;
-        umma_commit(bar_acc_full + 8 * acc);           // accumulator complete
-        trace_event(EPI, 5);
-        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        for (int k16 = 0; k16 < kWsBK / 16; ++k16)   // 32 bytes further along k inside the swizzle atom
+          umma_bf16_w(d_tmem, adesc + 2 * k16, bdesc + 2 * k16, idesc, (c > 0 || k16 > 0) ? 1u : 0u);
+        umma_commit_w(bar_empty + 8 * stage);          // stage reusable once these MMAs have read it
+        if (++stage == a.stages) { stage = 0; phase ^= 1; }
       }
-      if (!ok) { misc[1] = 1; report_status(MDB_STATUS_WAIT_TIMEOUT); }
+      if (!ok) break;
+      umma_commit_w(bar_acc_full + 8 * acc);           // accumulator complete
+      if (lane == 0) trace_event(EPI, 5);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
+    if (!ok && lane == 0) { misc[1] = 1; report_status(MDB_STATUS_WAIT_TIMEOUT); }
   } else {
     // ---------------- epilogue warps 0..3: tensor-memory lanes 32*warp .. +31 ----------------
     int acc = 0;

@@ -36,7 +36,9 @@ import torch.nn.functional as F
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MINERU_DIFFUSION_REFERENCE", "")
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("usage: make_golden.py <checkout of the reference repository>  (or MINERU_DIFFUSION_REFERENCE=...)")
 sys.path.insert(0, os.path.join(REF, "engines", "nano_dvlm"))
 sys.path.insert(0, REF)
 sys.path.insert(0, ROOT)

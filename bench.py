@@ -48,6 +48,7 @@ TEXT_IDS = 32
 NEW_TOKENS = 1024
 THRESHOLD = 0.9
 REQUESTS = 1
+VISUAL_MAX = 4096      # upper end of the per-request visual row count when several requests run
 WEIGHT_SEED = 20260320
 
 
@@ -127,15 +128,15 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if nreq > 1:
         # config 3: per-request visual rows uniform in [512, 4096]; pages for every request's full length
         vg = torch.Generator().manual_seed(3 + rank)
-        visual_rows = torch.randint(512, 4097, (nreq,), generator=vg).tolist()
+        visual_rows = torch.randint(512, VISUAL_MAX + 1, (nreq,), generator=vg).tolist()
         pages = sum((v + TEXT_IDS + NEW_TOKENS + BLOCK + 255) // 256 for v in visual_rows) + 2
-        max_len = (4096 + TEXT_IDS + NEW_TOKENS + BLOCK + 255) // 256 * 256
+        max_len = (VISUAL_MAX + TEXT_IDS + NEW_TOKENS + BLOCK + 255) // 256 * 256
     else:
         visual_rows = [VISUAL_ROWS]
         pages = (total_len + 255) // 256 + 1
     cfg = pkg.Config(max_num_batched_tokens=max(max_len, 16384 if nreq > 1 else 0), max_num_seqs=nreq,
                      max_model_len=max_len, enforce_eager=False, num_kvcache_blocks=pages, decoder_config=dcfg,
-                     tensor_parallel_size=args.tp)
+                     tensor_parallel_size=args.tp, block_size=BLOCK)
     # tensor-parallel pair: both ranks serve the same request with the same noise; replicas: one request each
     seed = 2 if args.tp == 2 else 2 + rank
     runner = pkg.ModelRunner(cfg, rank=rank if args.tp == 2 else 0, weight_seed=WEIGHT_SEED, noise="gumbel",
@@ -367,12 +368,19 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="config2", choices=["config2", "config3", "config4"],
+    ap.add_argument("--workload", default="config2", choices=["config2", "config3", "config4", "config5"],
                     help="config3: 64 concurrent requests, visual rows uniform in [512, 4096], 2048 new tokens each; "
-                         "config4: one request, 4096 visual rows, 4096 new tokens (the TP=2 vs TP=1 comparison)")
+                         "config4: one request, 4096 visual rows, 4096 new tokens (the TP=2 vs TP=1 comparison); "
+                         "config5: one point of the request-parallel sweep (64 requests in flight per GPU out of the "
+                         "512 / N share, visual rows uniform in [512, 8192], --block and --threshold set the point)")
+    ap.add_argument("--block", type=int, default=32, choices=[8, 16, 32, 64], help="denoising block size")
+    ap.add_argument("--threshold", type=float, default=0.9, help="confidence threshold of the unmask rule")
     ap.add_argument("--tp", type=int, default=1, choices=[1, 2], help="2: the two ranks form one tensor-parallel pair")
     args = ap.parse_args()
-    global VISUAL_ROWS, NEW_TOKENS, REQUESTS
+    global VISUAL_ROWS, NEW_TOKENS, REQUESTS, BLOCK, THRESHOLD, VISUAL_MAX
+    BLOCK, THRESHOLD = args.block, args.threshold
+    if args.workload == "config5":
+        NEW_TOKENS, REQUESTS, VISUAL_MAX = 2048, 64, 8192
     if args.workload == "config4":
         VISUAL_ROWS, NEW_TOKENS = 4096, 4096
     if args.workload == "config3":
@@ -409,6 +417,12 @@ def main():
         config["workload"] = ("config3: full decoder, 64 concurrent requests on one GPU, visual rows uniform in "
                               "[512, 4096] + 32 text ids, 2048 new tokens each, block 32, threshold 0.9, temperature 1.0")
         config["requests_per_gpu"] = 64
+    if args.workload == "config5":
+        config["workload"] = (f"config5 sweep point: full decoder, 64 requests in flight per GPU (of 512 / N), visual "
+                              f"rows uniform in [512, 8192] + 32 text ids, block {BLOCK}, threshold {THRESHOLD}, "
+                              "temperature 1.0")
+        config["requests_per_gpu"] = 64
+    config["block_size"] = BLOCK
     if args.workload == "config4":
         config["workload"] = ("config4: full decoder, 1 request, 4096 synthetic visual rows + 32 text ids, 4096 new "
                               "tokens, block 32, threshold 0.9, temperature 1.0")

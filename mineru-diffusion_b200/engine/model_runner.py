@@ -310,8 +310,7 @@ class ModelRunner:
             hidden = self.engine.final[:bs * b]     # final-norm rows of the step (graph replays write here too)
         with torch.inference_mode():
             # sampler state: the host copy of each block is the source of truth, as in the reference
-            for i, seq in enumerate(seqs):
-                self.h_block_ids[i] = seq.current_denoising_block
+            torch.stack([seq.current_denoising_block for seq in seqs], out=self.h_block_ids[:bs])
             self.block_ids[:bs].copy_(self.h_block_ids[:bs], non_blocking=True)
             sp = seqs[0].sampling_params
             if sp.denoising_strategy != "low_confidence_dynamic":
@@ -331,15 +330,15 @@ class ModelRunner:
                 self.last = dict(x0=self.engine.x0[:m].clone(), conf=self.engine.conf[:m].clone(),
                                  hidden=None if hidden is None else hidden.clone())
             torch.cuda.current_stream().synchronize()
-        total = 0
+        # one copy of the results for the whole batch; every request keeps a row of it
+        blocks = self.h_block_ids[:bs].clone()
+        moved = self.h_transfer[:bs].bool()
         for i, seq in enumerate(seqs):
-            seq.current_denoising_block = self.h_block_ids[i].clone()
-            moved = self.h_transfer[i].bool()
-            seq.current_step_map[moved] = seq.current_denoise_step
+            seq.current_denoising_block = blocks[i]
+            seq.current_step_map[moved[i]] = seq.current_denoise_step
             seq.current_denoise_step += 1
-            total += int(self.h_counts[i])
         self.step_index += 1
-        return total
+        return int(self.h_counts[:bs].sum())
 
     def launches_per_decode_step(self, bs: int = 1) -> int:
         """Kernels of libmdb200 launched by one decode-form step: row gather,

@@ -72,10 +72,11 @@ class Scheduler:
     def postprocess(self, seqs: list[Sequence]):
         for seq in seqs:
             if not seq.is_caching:
-                if not bool((seq.current_denoising_block == seq.mask_token_id).any()):
+                if not bool((seq.current_denoising_block.numpy() == seq.mask_token_id).any()):   # numpy view: no dispatch cost
                     seq.status = SequenceStatus.CACHING
                 continue
-            hit_stop = any(bool((seq.current_denoising_block == t).any()) for t in seq.sampling_params.stop_token_ids)
+            block_np = seq.current_denoising_block.numpy()
+            hit_stop = any(bool((block_np == t).any()) for t in seq.sampling_params.stop_token_ids)
             seq.append_block()
             if (not seq.ignore_eos and hit_stop) or seq.num_completion_tokens >= seq.max_new_tokens:
                 seq.status = SequenceStatus.FINISHED

@@ -47,17 +47,24 @@ def build_prefill_inputs(seqs: list[Sequence], block_size: int) -> dict:
 
 
 def build_decode_inputs(seqs: list[Sequence], block_size: int) -> dict:
-    """The block being denoised of every request against its cached prefix."""
+    """The block being denoised of every request against its cached prefix.
+    Vectorised over the requests (a step of 64 requests spends more host time
+    here than anywhere else otherwise); slot = page_id * page + offset, -1
+    where a request holds no page."""
     bs = len(seqs)
-    ids = np.empty((bs, block_size), dtype=np.int64)
-    pos = np.empty((bs, block_size), dtype=np.int64)
-    slots = np.empty((bs, block_size), dtype=np.int32)
-    ctx = np.empty(bs, dtype=np.int32)
-    for i, seq in enumerate(seqs):
-        n = len(seq)
-        ids[i] = seq.current_denoising_block.numpy()
-        pos[i] = np.arange(n, n + block_size, dtype=np.int64)
-        slots[i] = seq.get_slots(n, n + block_size)
-        ctx[i] = n + block_size
-    return dict(input_ids=ids, positions=pos, slot_mapping=slots, context_lens=ctx,
-                block_tables=pad_block_tables(seqs))
+    lens = np.fromiter((len(seq) for seq in seqs), dtype=np.int64, count=bs)
+    ids = np.stack([seq.current_denoising_block.numpy() for seq in seqs]).astype(np.int64, copy=False)
+    pos = lens[:, None] + np.arange(block_size, dtype=np.int64)[None, :]
+    tables = pad_block_tables(seqs)
+    page = Sequence.kvcache_block_size
+    if tables.shape[1] == 0:
+        slots = np.full((bs, block_size), -1, dtype=np.int32)
+    else:
+        page_idx = pos // page
+        held = np.fromiter((len(seq.block_table) for seq in seqs), dtype=np.int64, count=bs)
+        if bool(((held > 0)[:, None] & (page_idx >= held[:, None])).any()):
+            raise IndexError("block position beyond the request's page table")
+        page_ids = np.take_along_axis(tables.astype(np.int64), np.minimum(page_idx, tables.shape[1] - 1), axis=1)
+        slots = np.where(held[:, None] > 0, page_ids * page + pos % page, -1).astype(np.int32)
+    ctx = (lens + block_size).astype(np.int32)
+    return dict(input_ids=ids, positions=pos, slot_mapping=slots, context_lens=ctx, block_tables=tables)

@@ -75,6 +75,35 @@ def test_get_slots_cases(mdb):
     assert seq.get_slots(5, 9) == [-1] * 4
 
 
+def test_decode_inputs_match_per_request_form(mdb):
+    """The vectorised decode-step builder against the per-request statement of the same contract
+    (NV/engine/model_runner.py:169-185): ids, positions, slots through get_slots, context lengths,
+    for ragged lengths around page edges, several block sizes and a request that holds no page."""
+    import numpy as np
+    import torch
+    si = mdb.engine.step_inputs if hasattr(mdb, "engine") else __import__("importlib").import_module(
+        "mineru-diffusion_b200.engine.step_inputs")
+    gen = torch.Generator().manual_seed(0)
+    for block in (8, 32, 64):
+        seqs = []
+        for n in (1, 255, 256, 257, 511, 700, 1024 - block, 3000):
+            sp = mdb.SamplingParams(temperature=1.0, max_new_tokens=64, ignore_eos=True)
+            seq = mdb.Sequence(torch.randint(0, 100, (n,), generator=gen).tolist(), sp, denoising_block_size=block,
+                               mask_token_id=1000)
+            pages = (n + block + 255) // 256
+            seq.block_table = torch.randperm(64, generator=gen)[:pages].tolist()
+            seqs.append(seq)
+        seqs[3].block_table = []          # a warm-up style request: no pages, every slot -1
+        got = si.build_decode_inputs(seqs, block)
+        for i, seq in enumerate(seqs):
+            n = len(seq)
+            assert np.array_equal(got["input_ids"][i], seq.current_denoising_block.numpy())
+            assert np.array_equal(got["positions"][i], np.arange(n, n + block))
+            assert np.array_equal(got["slot_mapping"][i], np.asarray(seq.get_slots(n, n + block), dtype=np.int32))
+            assert got["context_lens"][i] == n + block
+        assert got["slot_mapping"].dtype == np.int32 and got["positions"].dtype == np.int64
+
+
 def test_preemption_when_pages_run_out(mdb):
     from types import SimpleNamespace
     cfg = SimpleNamespace(max_num_seqs=4, max_num_batched_tokens=4096, eos=-1, num_kvcache_blocks=2,

@@ -53,8 +53,11 @@ int mdb_version(void);
  * with programmatic dependent launch (default), 0 = plain stream order.
  * MDB_OPT_ATTN_KERNEL: which kernel mdb_attn_block_paged runs: 0 = chosen by
  * the amount of work (default), 1 = the mma.sync kernel, 2 = the tcgen05/TMA
- * kernel whenever the shape allows (block * hq / hkv <= 64). */
-enum { MDB_OPT_STREAM_KERNEL = 0, MDB_OPT_PDL = 1, MDB_OPT_ATTN_KERNEL = 2 };
+ * kernel whenever the shape allows (at most 128 query heads per KV head).
+ * MDB_OPT_GEMM_PAIR: GEMMs of many rows on pairs of CTAs (tcgen05.mma.
+ * cta_group::2, tiles of 256 x 256): 1 = from 2048 rows (default), 2 = from 256
+ * rows, 0 = never. */
+enum { MDB_OPT_STREAM_KERNEL = 0, MDB_OPT_PDL = 1, MDB_OPT_ATTN_KERNEL = 2, MDB_OPT_GEMM_PAIR = 3 };
 int mdb_set_option(int option, int value);
 /* Measurement aid: registers a device buffer (uint64 count, then (kernel,
  * event, globaltimer ns) triples) that block 0 of the traced kernels appends

@@ -358,6 +358,10 @@ int mdb_set_option(int option, int value) {
   switch (option) {
     case MDB_OPT_STREAM_KERNEL: g_opt_stream_kernel = value ? 1 : 0; return MDB_OK;
     case MDB_OPT_PDL: g_opt_pdl = value ? 1 : 0; return MDB_OK;
+    case MDB_OPT_GEMM_PAIR:
+      if (value < 0 || value > 2) return MDB_ERR_ARG;
+      g_opt_gemm_pair = value;
+      return MDB_OK;
     case MDB_OPT_ATTN_KERNEL:
       if (value < 0 || value > 2) return MDB_ERR_ARG;
       g_opt_attn_kernel = value;
@@ -371,6 +375,7 @@ int mdb_get_option(int option) {
     case MDB_OPT_STREAM_KERNEL: return g_opt_stream_kernel;
     case MDB_OPT_PDL: return g_opt_pdl;
     case MDB_OPT_ATTN_KERNEL: return g_opt_attn_kernel;
+    case MDB_OPT_GEMM_PAIR: return g_opt_gemm_pair;
     default: return MDB_ERR_ARG;
   }
 }

@@ -20,6 +20,20 @@
 // heads, and the thread that owns a step row holds a whole head of it.
 // Tiles are ordered so that consecutive CTAs share a weight tile: it is read
 // from HBM once and served from L2 to the others.
+//
+// PAIR form (steps of 256 rows and more): a cluster of two CTAs owns a tile of
+// 256 step rows x 256 weight rows (tcgen05.mma.cta_group::2).  Each CTA stages
+// its own 128 step rows (A) and its own 128 of the 256 weight rows (B) per k
+// stage -- 32 KB instead of 48 KB for half the output -- and the MMA, issued by
+// the leader CTA for both, reads the B halves of both CTAs, so shared-memory
+// traffic per flop falls by a third; that traffic (operand reads + TMA fills
+// above 128 B/clk at the tensor peak) is what bounds the one-CTA form.  Both
+// producers' TMA loads complete on the leader's "full" barrier
+// (cp.async.bulk.tensor with .cta_group::2), tcgen05.commit with a CTA mask
+// arrives on the "empty" / "accumulator full" barriers of both CTAs, the
+// peer's epilogue warps arrive on the leader's "accumulator empty" barrier
+// through its cluster address, and a cluster barrier before the tensor memory
+// is freed keeps either CTA's shared memory alive while the other may read it.
 #include "mdb_common.cuh"
 
 namespace mdb {
@@ -30,6 +44,7 @@ constexpr int kTcBM = 128, kTcBN = 256, kTcBK = 64;
 constexpr int kTcStages = 4;
 constexpr int kTcABytes = kTcBM * kTcBK * 2;   // 16 KB
 constexpr int kTcBBytes = kTcBN * kTcBK * 2;   // 32 KB
+constexpr int kTcPairStages = 6;               // PAIR: 16 KB of A + 16 KB of B per stage and CTA
 constexpr int kTcLmEpiWarps = 16;
 constexpr int kTcLmRecBytes = 2 * kTcLmEpiWarps * 32 * 5 * 4;    // two buffers of per-warp sampler records
 constexpr int kTcSmemBytes = 1024 + kTcStages * (kTcABytes + kTcBBytes) + 256 + kTcLmRecBytes;
@@ -66,108 +81,190 @@ struct TcArgs {
   int64_t num_slots;
 };
 
-template <int EPI>
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// warp-collective forms of the pair instructions
+__device__ __forceinline__ void tma_load_2d_pair_w(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t leader_bar) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "@q cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n\t}"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(leader_bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair_w(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrives on the barrier at this shared-memory offset in both CTAs of the pair once the MMAs issued so far are done
+__device__ __forceinline__ void umma_commit_pair_w(uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t.reg .b16 m;\n\t"
+      "mov.b16 m, 3;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n\t}"
+      ::"r"(bar)
+      : "memory");
+}
+
+template <int EPI, bool PAIR>
 __global__ void __launch_bounds__(tc_threads(EPI), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
   extern __shared__ unsigned char tc_smem_raw[];
+  constexpr int kStages = PAIR ? kTcPairStages : kTcStages;
+  constexpr int kBBytes = PAIR ? kTcBBytes / 2 : kTcBBytes;      // PAIR: this CTA's 128 of the tile's 256 weight rows
+  constexpr int kRowsPerTile = PAIR ? 2 * kTcBM : kTcBM;
   const uint32_t raw = smem_u32(tc_smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;
+  const uint32_t base = (raw + 1023u) & ~1023u;                  // PAIR: same offset in both CTAs (same kernel, same layout)
   unsigned char* gen_base = tc_smem_raw + (base - raw);
   const uint32_t a_tiles = base;
-  const uint32_t b_tiles = base + kTcStages * kTcABytes;
-  const uint32_t bars_off = kTcStages * (kTcABytes + kTcBBytes);
+  const uint32_t b_tiles = base + kStages * kTcABytes;
+  const uint32_t bars_off = kStages * (kTcABytes + kBBytes);
   const uint32_t bars = base + bars_off;
-  const uint32_t bar_full = bars, bar_empty = bars + 8 * kTcStages;
-  const uint32_t bar_acc_full = bars + 16 * kTcStages, bar_acc_empty = bar_acc_full + 16;
-  volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(gen_base + bars_off + 16 * kTcStages + 32);
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * kStages;
+  const uint32_t bar_acc_full = bars + 16 * kStages, bar_acc_empty = bar_acc_full + 16;
+  volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(gen_base + bars_off + 16 * kStages + 32);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int kEpiWarps = tc_epi_warps(EPI);
   constexpr int kProducerWarp = kEpiWarps, kMmaWarp = kEpiWarps + 1;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;           // 0 = the CTA that issues the MMAs
+  const int work0 = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int work_stride = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
   const int tiles = a.tiles_m * a.tiles_n;
   const int kchunks = a.k / kTcBK;
 
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kTcStages; ++s) {
-      mbar_init(bar_full + 8 * s, 1);
-      mbar_init(bar_empty + 8 * s, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);      // PAIR: used in the leader; its producer's arrive + bytes from both CTAs
+      mbar_init(bar_empty + 8 * s, 1);     // PAIR: one commit, multicast to both CTAs
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_acc_full + 8 * b, 1);
-      mbar_init(bar_acc_empty + 8 * b, kEpiWarps);
+      mbar_init(bar_acc_empty + 8 * b, PAIR ? 2 * kEpiWarps : kEpiWarps);   // PAIR: the epilogue warps of both CTAs
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == kMmaWarp) {
     const uint32_t slot = smem_u32(const_cast<uint32_t*>(&misc[0]));
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(512u) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(512u) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(512u) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
-  __syncthreads();
+  if (PAIR) cluster_sync_all();            // the barriers of both CTAs exist before anyone signals across
+  else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = misc[0];
+  // where an epilogue warp reports that it has drained an accumulator buffer
+  const uint32_t acc_empty_target = PAIR ? map_to_cta(bar_acc_empty, 0) : bar_acc_empty;
+  auto arrive_acc_empty = [&](int acc_buf) {
+    if (PAIR) mbar_arrive_cluster(acc_empty_target + 8 * acc_buf);
+    else mbar_arrive(acc_empty_target + 8 * acc_buf);
+  };
 
   if (warp == kProducerWarp) {
     // the whole warp walks the loop (warp-uniform operands), one elected lane issues each instruction
     pdl_wait();   // activations come from the preceding kernel
+    const uint32_t full_target = PAIR ? map_to_cta(bar_full, 0) : bar_full;
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+    for (int t = work0; t < tiles && ok; t += work_stride) {
       const int tn = t / a.tiles_m, tm = t % a.tiles_m;   // consecutive CTAs: same weight tile
       for (int c = 0; c < kchunks; ++c) {
         if (!mbar_wait_w(bar_empty + 8 * stage, phase ^ 1)) { ok = false; break; }
-        const uint32_t full = bar_full + 8 * stage;
-        mbar_arrive_expect_tx_w(full, kTcABytes + kTcBBytes);
-        tma_load_2d_w(a_tiles + stage * kTcABytes, &map_x, c * kTcBK, tm * kTcBM, full);
-        const uint32_t bdst = b_tiles + stage * kTcBBytes;
-        if (EPI == kTcSwiglu) {
-          tma_load_2d_w(bdst, &map_w, c * kTcBK, tn * 128, full);                             // 128 gate rows
-          tma_load_2d_w(bdst + kTcBBytes / 2, &map_w, c * kTcBK, a.inter + tn * 128, full);   // their up rows
+        const uint32_t full = full_target + 8 * stage;
+        const uint32_t adst = a_tiles + stage * kTcABytes;
+        const uint32_t bdst = b_tiles + stage * kBBytes;
+        if (PAIR) {
+          // own 128 step rows, own 128 weight rows (SiLU form: the leader holds the gate rows, the peer the up rows)
+          if (rank == 0) mbar_arrive_expect_tx_w(bar_full + 8 * stage, 2 * (kTcABytes + kBBytes));
+          tma_load_2d_pair_w(adst, &map_x, c * kTcBK, tm * kRowsPerTile + static_cast<int>(rank) * kTcBM, full);
+          const int brow = EPI == kTcSwiglu ? (rank == 0 ? tn * 128 : a.inter + tn * 128)
+                                            : tn * kTcBN + static_cast<int>(rank) * 128;
+          tma_load_2d_pair_w(bdst, &map_w, c * kTcBK, brow, full);
         } else {
-          tma_load_2d_w(bdst, &map_w, c * kTcBK, tn * kTcBN, full);
+          mbar_arrive_expect_tx_w(full, kTcABytes + kTcBBytes);
+          tma_load_2d_w(adst, &map_x, c * kTcBK, tm * kTcBM, full);
+          if (EPI == kTcSwiglu) {
+            tma_load_2d_w(bdst, &map_w, c * kTcBK, tn * 128, full);                             // 128 gate rows
+            tma_load_2d_w(bdst + kTcBBytes / 2, &map_w, c * kTcBK, a.inter + tn * 128, full);   // their up rows
+          } else {
+            tma_load_2d_w(bdst, &map_w, c * kTcBK, tn * kTcBN, full);
+          }
         }
-        if (++stage == kTcStages) { stage = 0; phase ^= 1; }
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
     }
     if (!ok && lane == 0) report_status(MDB_STATUS_WAIT_TIMEOUT);
   } else if (warp == kMmaWarp) {
-    // bf16 x bf16 -> fp32, K-major operands, M = 128, N = 256
-    const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kTcBN >> 3) << 17) |
-                           (static_cast<uint32_t>(kTcBM >> 4) << 24);
-    int stage = 0;
-    uint32_t phase = 0;
-    int acc = 0;
-    uint32_t acc_phase = 0;
-    bool ok = true;
-    for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-      if (!mbar_wait_w(bar_acc_empty + 8 * acc, acc_phase ^ 1)) { ok = false; break; }
-      tc_fence_after();
-      const uint32_t d_tmem = tmem_base + acc * kTcBN;
-      for (int c = 0; c < kchunks; ++c) {
-        if (!mbar_wait_w(bar_full + 8 * stage, phase)) { ok = false; break; }
+    if (rank == 0) {
+      // bf16 x bf16 -> fp32, K-major operands, M = 128 (PAIR: 256, 128 per CTA), N = 256
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kTcBN >> 3) << 17) |
+                             (static_cast<uint32_t>(kRowsPerTile >> 4) << 24);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = work0; t < tiles && ok; t += work_stride) {
+        if (!mbar_wait_w(bar_acc_empty + 8 * acc, acc_phase ^ 1)) { ok = false; break; }
         tc_fence_after();
-        const uint64_t adesc = umma_desc_sw128(a_tiles + stage * kTcABytes);
-        const uint64_t bdesc = umma_desc_sw128(b_tiles + stage * kTcBBytes);
+        const uint32_t d_tmem = tmem_base + acc * kTcBN;
+        for (int c = 0; c < kchunks; ++c) {
+          if (!mbar_wait_w(bar_full + 8 * stage, phase)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t adesc = umma_desc_sw128(a_tiles + stage * kTcABytes);
+          const uint64_t bdesc = umma_desc_sw128(b_tiles + stage * kBBytes);
 #pragma unroll
-        for (int k16 = 0; k16 < kTcBK / 16; ++k16)
-          umma_bf16_w(d_tmem, adesc + 2 * k16, bdesc + 2 * k16, idesc, (c > 0 || k16 > 0) ? 1u : 0u);
-        umma_commit_w(bar_empty + 8 * stage);
-        if (++stage == kTcStages) { stage = 0; phase ^= 1; }
+          for (int k16 = 0; k16 < kTcBK / 16; ++k16) {
+            if (PAIR) umma_bf16_pair_w(d_tmem, adesc + 2 * k16, bdesc + 2 * k16, idesc, (c > 0 || k16 > 0) ? 1u : 0u);
+            else umma_bf16_w(d_tmem, adesc + 2 * k16, bdesc + 2 * k16, idesc, (c > 0 || k16 > 0) ? 1u : 0u);
+          }
+          if (PAIR) umma_commit_pair_w(bar_empty + 8 * stage);
+          else umma_commit_w(bar_empty + 8 * stage);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        if (PAIR) umma_commit_pair_w(bar_acc_full + 8 * acc);
+        else umma_commit_w(bar_acc_full + 8 * acc);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
-      if (!ok) break;
-      umma_commit_w(bar_acc_full + 8 * acc);
-      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      if (!ok && lane == 0) report_status(MDB_STATUS_WAIT_TIMEOUT);
     }
-    if (!ok && lane == 0) report_status(MDB_STATUS_WAIT_TIMEOUT);
   } else {
     int acc = 0;
     uint32_t acc_phase = 0;
     uint32_t acc_phase_tile = 0;   // tiles done (LM head: picks the record buffer)
     pdl_wait();   // the output buffer may still be read by the preceding kernel
-    for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
+    for (int t = work0; t < tiles; t += work_stride) {
       const int tn = t / a.tiles_m, tm = t % a.tiles_m;
       bool ok = mbar_wait(bar_acc_full + 8 * acc, acc_phase);
       ok = __all_sync(0xffffffffu, ok);
@@ -180,7 +277,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       tc_fence_after();
       const int quarter = warp & 3;       // the 32 tensor-memory lanes this warp may read
       const uint32_t taddr = tmem_base + acc * kTcBN + (static_cast<uint32_t>(32 * quarter) << 16);
-      const int row = tm * kTcBM + 32 * quarter + lane;
+      const int row = tm * kRowsPerTile + static_cast<int>(rank) * kTcBM + 32 * quarter + lane;
       if (EPI == kTcBf16) {
         bf16* dst = a.y + static_cast<int64_t>(row) * a.ldy + tn * kTcBN;
 #pragma unroll 1
@@ -248,7 +345,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
+        if (lane == 0) arrive_acc_empty(acc);
         if (row < a.m && head < nheads) {
 #pragma unroll
           for (int i = 0; i < kHeadDim; ++i) v[i] = bf16_round(v[i]);       // the projection's bf16 output
@@ -379,7 +476,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         rec[128 + lane] = __int_as_float(bi);
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
+        if (lane == 0) arrive_acc_empty(acc);
         asm volatile("bar.sync %0, 128;" ::"r"(1 + quarter) : "memory");
         if (grp == 0) {
           SampleRec r = {mx, se, bv, bl, bi};
@@ -400,16 +497,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
+      if (lane == 0) arrive_acc_empty(acc);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
   }
 
   tc_fence_before();
-  __syncthreads();
+  if (PAIR) cluster_sync_all();            // neither CTA leaves while the other may still read its shared memory
+  else __syncthreads();
   if (warp == kMmaWarp) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
   }
 }
 
@@ -423,8 +522,8 @@ static bool tc_supported(int epi, int m, int n, int k, int64_t ldx, int64_t ldy)
   return n % 8 == 0;
 }
 
-template <int EPI>
-static int launch_tc(const bf16* x, int64_t ldx, const bf16* w, int w_rows, TcArgs& a, cudaStream_t st) {
+template <int EPI, bool PAIR>
+static int launch_tc_impl(const bf16* x, int64_t ldx, const bf16* w, int w_rows, TcArgs& a, cudaStream_t st) {
   static int sm_count = 0;
   if (sm_count == 0) {
     int dev = 0;
@@ -432,21 +531,59 @@ static int launch_tc(const bf16* x, int64_t ldx, const bf16* w, int w_rows, TcAr
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (sm_count <= 0) sm_count = 148;
   }
-  a.tiles_m = (a.m + kTcBM - 1) / kTcBM;
+  constexpr int kRowsPerTile = PAIR ? 2 * kTcBM : kTcBM;
+  constexpr int kSmem = PAIR ? 1024 + kTcPairStages * (kTcABytes + kTcBBytes / 2) + 256 + kTcLmRecBytes : kTcSmemBytes;
+  a.tiles_m = (a.m + kRowsPerTile - 1) / kRowsPerTile;
   a.tiles_n = (EPI == kTcSwiglu) ? a.n / 128 : (a.n + kTcBN - 1) / kTcBN;
   CUtensorMap map_x, map_w;
   if (!get_tensor_map(x, a.m, a.k, ldx, kTcBM, &map_x)) return MDB_ERR_CUDA;
-  if (!get_tensor_map(w, w_rows, a.k, a.k, (EPI == kTcSwiglu) ? 128 : kTcBN, &map_w)) return MDB_ERR_CUDA;
+  if (!get_tensor_map(w, w_rows, a.k, a.k, (PAIR || EPI == kTcSwiglu) ? 128 : kTcBN, &map_w)) return MDB_ERR_CUDA;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_tc_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_tc_kernel<EPI, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess)
       return MDB_ERR_CUDA;
     attr_set = true;
   }
   const int tiles = a.tiles_m * a.tiles_n;
-  return mdb_launch(gemm_tc_kernel<EPI>, dim3(tiles < sm_count ? tiles : sm_count), dim3(tc_threads(EPI)), kTcSmemBytes, st,
-                    map_x, map_w, a);
+  if (!PAIR)
+    return mdb_launch(gemm_tc_kernel<EPI, PAIR>, dim3(tiles < sm_count ? tiles : sm_count), dim3(tc_threads(EPI)), kSmem,
+                      st, map_x, map_w, a);
+  // clusters of two CTAs, with programmatic dependent launch like every other kernel of the library
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(sm_count / 2 * 2);
+  cfg.blockDim = dim3(tc_threads(EPI));
+  cfg.dynamicSmemBytes = kSmem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  // CTA pairs the device holds at once (an odd SM of a processing cluster cannot host a pair)
+  static int max_pairs = 0;
+  if (max_pairs == 0) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<EPI, PAIR>, &cfg) != cudaSuccess || n <= 0) n = sm_count / 2;
+    max_pairs = n;
+  }
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.numAttrs = g_opt_pdl ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<EPI, PAIR>, map_x, map_w, a) == cudaSuccess ? MDB_OK : MDB_ERR_CUDA;
+}
+
+// CTA pairs from 2048 rows on (measured: +12 .. 15 % on the bf16-store projections at 4096 and 16384 rows, even at
+// 2048, where eight 256-row tiles per weight tile leave the pair form no room); MDB_OPT_GEMM_PAIR = 2 takes them
+// from 256 rows, 0 never.
+template <int EPI>
+static int launch_tc(const bf16* x, int64_t ldx, const bf16* w, int w_rows, TcArgs& a, cudaStream_t st) {
+  const int from_rows = g_opt_gemm_pair == 2 ? 2 * kTcBM : 2048;
+  if (g_opt_gemm_pair != 0 && a.m >= from_rows) return launch_tc_impl<EPI, true>(x, ldx, w, w_rows, a, st);
+  return launch_tc_impl<EPI, false>(x, ldx, w, w_rows, a, st);
 }
 
 }  // namespace mdb

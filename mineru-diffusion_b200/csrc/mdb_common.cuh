@@ -240,6 +240,7 @@ static inline bool mdb_aligned16(const void* p) { return (reinterpret_cast<uintp
 // process-wide options (mdb_set_option)
 static int g_opt_stream_kernel = 0;   // 0: tcgen05/TMA streaming kernel where possible, 1: register-streaming kernel
 static int g_opt_pdl = 1;             // programmatic dependent launch between the library's kernels
+static int g_opt_gemm_pair = 1;       // many-row GEMMs on CTA pairs (tcgen05.mma.cta_group::2): 1 from 2048 rows, 2 from 256, 0 never
 static int g_opt_attn_kernel = 0;     // block attention: 0 = by size, 1 = mma.sync kernel, 2 = tcgen05 kernel where it applies
 
 // Launch with the programmatic-stream-serialization attribute when enabled.

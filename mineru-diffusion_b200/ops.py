@@ -40,6 +40,7 @@ def _rows(t: torch.Tensor, name: str) -> int:
 OPT_STREAM_KERNEL = 0   # 0: tcgen05/TMA streaming kernel for short steps (default), 1: register-streaming kernel
 OPT_PDL = 1             # programmatic dependent launch between kernels (default on)
 OPT_ATTN_KERNEL = 2     # block attention kernel: 0 by size (default), 1 mma.sync, 2 tcgen05/TMA where the shape allows
+OPT_GEMM_PAIR = 3       # many-row GEMMs on CTA pairs (tcgen05.mma.cta_group::2): 1 from 2048 rows (default), 2 from 256, 0 never
 
 
 def set_option(option: int, value: int) -> None:

@@ -291,6 +291,42 @@ def test_gemm_tiled(mdb, stream_kernel, m, n, k):
     assert torch.equal(y2.float(), y.float() * 2)
 
 
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (300, 520, 128), (512, 640, 128), (1088, 2048, 512), (2048, 4096, 2048)])
+def test_gemm_cta_pair_matches_single_cta(mdb, m, n, k):
+    """Steps of 256 rows and more run on pairs of CTAs (tcgen05.mma.cta_group::2, tiles of 256 x 256).
+    Same products, same accumulation order: every epilogue must give the single-CTA kernel's bits
+    (bf16 store, SiLU*mul, qkv + norm + rotary + KV store, LM head + sampler records), including
+    partial row and column tiles."""
+    gen = torch.Generator().manual_seed(m + n)
+    x = torch.randn(m, k, generator=gen).to(BF).to(DEV)
+    w = (torch.randn(n, k, generator=gen) / k ** 0.5).to(BF).to(DEV)
+    res = {}
+    for pair in (0, 2):
+        mdb.ops.set_option(mdb.ops.OPT_GEMM_PAIR, pair)
+        out = [mdb.ops.linear(x, w)]
+        if n % 256 == 0:
+            out.append(mdb.ops.gateup_swiglu(x, w))
+        if n % 128 == 0 and n >= 384:
+            hq, hkv = n // 128 - 2, 1
+            pos = torch.arange(m, device=DEV) % 1000
+            table = orc.rope_table(1024, 128, 1e6).to(DEV)
+            ones = torch.ones(128, dtype=BF, device=DEV)
+            slots = torch.arange(m, dtype=torch.int32, device=DEV)
+            kc = torch.zeros((m + 255) // 256, 256, hkv, 128, dtype=BF, device=DEV)
+            vc = torch.zeros_like(kc)
+            q, _, _ = mdb.ops.qkv_proj_rope_commit(x, w, pos, table, ones, ones, 1e-6, hq, hkv, slots, kc, vc)
+            out += [q, kc, vc]
+        temps = torch.ones(1, device=DEV)
+        x0, conf = mdb.ops.lm_head_sample(x, w, temps, m, seed=7, step=1)
+        out += [x0, conf]
+        res[pair] = out
+    mdb.ops.set_option(mdb.ops.OPT_GEMM_PAIR, 1)
+    for a_t, b_t in zip(res[0], res[2]):
+        assert torch.equal(a_t, b_t)
+    _close_gemm(res[2][0], x.cpu().float() @ w.cpu().float().t())
+    _status_clean(mdb)
+
+
 def test_gemm_rejects_bad_arguments(mdb):
     x = torch.zeros(4, 100, dtype=BF, device=DEV)
     w = torch.zeros(64, 100, dtype=BF, device=DEV)

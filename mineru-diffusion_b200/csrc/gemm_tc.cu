@@ -48,7 +48,7 @@ constexpr int kTcPairStages = 6;               // PAIR: 16 KB of A + 16 KB of B 
 constexpr int kTcLmEpiWarps = 16;
 constexpr int kTcLmRecBytes = 2 * kTcLmEpiWarps * 32 * 5 * 4;    // two buffers of per-warp sampler records
 constexpr int kTcSmemBytes = 1024 + kTcStages * (kTcABytes + kTcBBytes) + 256 + kTcLmRecBytes;
-__host__ __device__ constexpr int tc_epi_warps(int epi) { return epi == 2 ? kTcLmEpiWarps : (epi == 3 ? 8 : 4); }
+__host__ __device__ constexpr int tc_epi_warps(int epi) { return epi == 2 ? kTcLmEpiWarps : (epi == 0 ? 4 : 8); }
 __host__ __device__ constexpr int tc_threads(int epi) { return (tc_epi_warps(epi) + 2) * 32; }
 
 struct TcArgs {
@@ -306,13 +306,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           }
         }
       } else if (EPI == kTcSwiglu) {
-        // columns [0,128) gate, [128,256) up of the same 128 intermediate columns
-        bf16* dst = a.y + static_cast<int64_t>(row) * a.ldy + tn * 128;
+        // columns [0,128) gate, [128,256) up of the same 128 intermediate columns; two warps per quarter,
+        // 64 of the 128 outputs each (with four warps the SiLU work outlasts the main loop)
+        const int grp = warp >> 2;
+        bf16* dst = a.y + static_cast<int64_t>(row) * a.ldy + tn * 128 + 64 * grp;
 #pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < 4; ++c) {
           float g[16], u[16];
-          tmem_ld16(taddr + 16 * c, g);
-          tmem_ld16(taddr + 128 + 16 * c, u);
+          tmem_ld16(taddr + 64 * grp + 16 * c, g);
+          tmem_ld16(taddr + 128 + 64 * grp + 16 * c, u);
           tmem_ld_wait();
           if (row < a.m) {
             uint32_t o[8];
@@ -323,7 +325,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
               for (int e = 0; e < 2; ++e) {
                 const float gt = bf16_round(g[2 * i + e]);
                 const float up = bf16_round(u[2 * i + e]);
-                const float sl = gt * __frcp_rn(1.0f + __expf(-gt));
+                const float sl = gt * rcp_approx(1.0f + __expf(-gt));   // fp32 SiLU, rounded to bf16 below
                 r[e] = bf16_round(sl) * up;
               }
               o[i] = pack_bf16x2(r[0], r[1]);

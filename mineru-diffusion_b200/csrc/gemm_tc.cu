@@ -4,10 +4,11 @@
 // weight tile as B (both K-major, 128-byte swizzle, staged by TMA through a
 // 4-stage ring of 48 KB), fp32 accumulators in tensor memory, double-buffered
 // (2 x 256 columns = all 512) so the epilogue of a tile overlaps the main loop
-// of the next.  Warps 0-3 = epilogue (tcgen05.ld, one step row per thread),
-// then the TMA producer warp and the MMA issue warp.  The LM-head form has 16
-// epilogue warps (four per 32-lane quarter of tensor memory, 64 columns
-// each): its per-logit work would otherwise outlast the main loop.
+// of the next.  Epilogue warps first (tcgen05.ld, one step row per thread),
+// then the TMA producer warp and the MMA issue warp.  The bf16-store form has
+// four epilogue warps; the SiLU and qkv forms eight (two per 32-lane quarter
+// of tensor memory) and the LM-head form sixteen (four per quarter, 64
+// columns each): their per-element work would otherwise outlast the main loop.
 //
 // Epilogues: bf16 store; SiLU(gate)*up for weight tiles made of 128 gate rows
 // and their 128 up rows (the thread that owns a step row holds both halves);
@@ -21,7 +22,7 @@
 // Tiles are ordered so that consecutive CTAs share a weight tile: it is read
 // from HBM once and served from L2 to the others.
 //
-// PAIR form (steps of 256 rows and more): a cluster of two CTAs owns a tile of
+// PAIR form (taken from 2048 rows on): a cluster of two CTAs owns a tile of
 // 256 step rows x 256 weight rows (tcgen05.mma.cta_group::2).  Each CTA stages
 // its own 128 step rows (A) and its own 128 of the 256 weight rows (B) per k
 // stage -- 32 KB instead of 48 KB for half the output -- and the MMA, issued by

@@ -1,6 +1,7 @@
 """Per-kernel timings of the decode-step operators on the current GPU.
 
     python mineru-diffusion_b200/microbench.py attn --bs 64 --ctx 1536 5120
+    python mineru-diffusion_b200/microbench.py stair --lens 4096 4096 4096 4096
     python mineru-diffusion_b200/microbench.py gemm --m 2048
     python mineru-diffusion_b200/microbench.py lmhead --m 2048
     python mineru-diffusion_b200/microbench.py elementwise --m 2048
@@ -112,6 +113,27 @@ def bench_attn(a) -> None:
              r["bytes"])
 
 
+def bench_stair(a) -> None:
+    """Staircase (prefill) attention over packed sequences of the given lengths; flops are counted over the
+    visible part of the mask only (T^2 / 2 + T * block / 2 query-key pairs per head)."""
+    import numpy as np
+    lens = a.lens
+    cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32, device=DEV)
+    n = int(cu[-1])
+    g = torch.Generator(device=DEV).manual_seed(a.seed)
+    q = torch.randn(n, a.hq, 128, generator=g, device=DEV).to(BF)
+    k = torch.randn(n, a.hkv, 128, generator=g, device=DEV).to(BF)
+    v = torch.randn(n, a.hkv, 128, generator=g, device=DEV).to(BF)
+    out = torch.empty_like(q)
+    flops = sum(4.0 * a.hq * 128 * (t * t / 2 + t * a.block / 2) for t in lens)
+    for kern in a.kernel:
+        ops.set_option(ops.OPT_ATTN_KERNEL, kern)
+        ms = timed(lambda: ops.sparse_attn_varlen(q, k, v, cu, cu, a.block, max_seqlen=max(lens), out=out), a.reps, a.plain)
+        name = {0: "auto", 1: "mma.sync", 2: "tcgen05"}[kern]
+        line(f"staircase[{name}] {len(lens)} seqs, {n} tokens", ms, flops)
+    ops.set_option(ops.OPT_ATTN_KERNEL, 0)
+
+
 def bench_gemm(a) -> None:
     g = torch.Generator(device=DEV).manual_seed(a.seed)
     m, h, inter = a.m, a.hidden, a.inter
@@ -160,7 +182,7 @@ def bench_elementwise(a) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("op", choices=["attn", "gemm", "lmhead", "elementwise"])
+    ap.add_argument("op", choices=["attn", "stair", "gemm", "lmhead", "elementwise"])
     ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--plain", action="store_true", help="launch without a CUDA graph")
     ap.add_argument("--seed", type=int, default=3)
@@ -175,11 +197,12 @@ def main() -> None:
     ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--nsplit", type=int, default=0, help="key-range parts per request (0: the library's choice)")
     ap.add_argument("--kernel", type=int, nargs="+", default=[1, 2], help="attention kernels: 1 mma.sync, 2 tcgen05")
+    ap.add_argument("--lens", type=int, nargs="+", default=[4096] * 4, help="stair: sequence lengths of the packed batch")
     ap.add_argument("--only", nargs="*", default=None, help="gemm: subset of qkv o_proj down_proj gate_up")
     a = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("needs a GPU")
-    {"attn": bench_attn, "gemm": bench_gemm, "lmhead": bench_lmhead, "elementwise": bench_elementwise}[a.op](a)
+    {"attn": bench_attn, "stair": bench_stair, "gemm": bench_gemm, "lmhead": bench_lmhead, "elementwise": bench_elementwise}[a.op](a)
     status = pkg._lib.device_status()
     print("device status", status)
     if status:

@@ -466,7 +466,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       for (int j = 0; j < w.ntiles; ++j) {
         ok = mbar_wait(bar(kAtBarSFull + sr.stage), sr.phase);
         if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-        if (threadIdx.x == 0) trace_event(30, 3);
         tc_fence_after();
         const uint32_t s_addr = tmem_base + sr.stage * kAtKeys + lane_field;
         const int key0 = w.kbeg + j * kAtKeys;
@@ -560,7 +559,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         fence_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(kAtBarPFull + pr.stage));
-        if (threadIdx.x == 0) trace_event(30, 4);
         prev_p_stage = pr.stage;
         prev_p_phase = pr.phase;
         sr.advance(2);
@@ -572,7 +570,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       ok = mbar_wait(bar(kAtBarOFull), o_phase);
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
       o_phase ^= 1;
-      if (threadIdx.x == 0) trace_event(30, 5);
       tc_fence_after();
       if (STAIR || a.nsplit == 1) {
         const float inv = l > 0.f ? 1.0f / l : 0.f;
@@ -606,7 +603,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kAtBarOEmpty));
-      if (threadIdx.x == 0) trace_event(30, 6);
     }
     if (!ok && lane == 0) report_status(MDB_STATUS_WAIT_TIMEOUT);
   }

@@ -56,6 +56,7 @@ struct TcArgs {
   int m, n, k;        // n = output columns (swiglu: the intermediate size)
   int tiles_m, tiles_n;
   int inter;          // swiglu: first up row of the weight
+  int n_fastest;      // tile order: 0 = consecutive CTAs share a weight tile, 1 = they share an activation tile
   bf16* y;
   int64_t ldy;
   // LM head + sampler
@@ -198,7 +199,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     uint32_t phase = 0;
     bool ok = true;
     for (int t = work0; t < tiles && ok; t += work_stride) {
-      const int tn = t / a.tiles_m, tm = t % a.tiles_m;   // consecutive CTAs: same weight tile
+      const int tn = a.n_fastest ? t % a.tiles_n : t / a.tiles_m;   // consecutive CTAs share a weight tile, or,
+      const int tm = a.n_fastest ? t / a.tiles_n : t % a.tiles_m;   // when the activations outgrow L2, an activation tile
       for (int c = 0; c < kchunks; ++c) {
         if (!mbar_wait_w(bar_empty + 8 * stage, phase ^ 1)) { ok = false; break; }
         const uint32_t full = full_target + 8 * stage;
@@ -266,7 +268,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     uint32_t acc_phase_tile = 0;   // tiles done (LM head: picks the record buffer)
     pdl_wait();   // the output buffer may still be read by the preceding kernel
     for (int t = work0; t < tiles; t += work_stride) {
-      const int tn = t / a.tiles_m, tm = t % a.tiles_m;
+      const int tn = a.n_fastest ? t % a.tiles_n : t / a.tiles_m;
+      const int tm = a.n_fastest ? t / a.tiles_n : t % a.tiles_m;
       bool ok = mbar_wait(bar_acc_full + 8 * acc, acc_phase);
       ok = __all_sync(0xffffffffu, ok);
       // LM head: the warps of a quarter meet at a named barrier below, so they must agree on giving up
@@ -538,6 +541,10 @@ static int launch_tc_impl(const bf16* x, int64_t ldx, const bf16* w, int w_rows,
   constexpr int kSmem = PAIR ? 1024 + kTcPairStages * (kTcABytes + kTcBBytes / 2) + 256 + kTcLmRecBytes : kTcSmemBytes;
   a.tiles_m = (a.m + kRowsPerTile - 1) / kRowsPerTile;
   a.tiles_n = (EPI == kTcSwiglu) ? a.n / 128 : (a.n + kTcBN - 1) / kTcBN;
+  // Activations that do not fit in L2 next to the weights (a 16K-row step of down_proj: 201 MB) would be
+  // re-read from HBM once per weight tile; then the tiles of one activation band run back to back instead.
+  a.n_fastest = static_cast<int64_t>(a.m) * a.k * 2 > (96ll << 20) &&
+                static_cast<int64_t>(w_rows) * a.k * 2 < static_cast<int64_t>(a.m) * a.k * 2 ? 1 : 0;
   CUtensorMap map_x, map_w;
   if (!get_tensor_map(x, a.m, a.k, ldx, kTcBM, &map_x)) return MDB_ERR_CUDA;
   if (!get_tensor_map(w, w_rows, a.k, a.k, (PAIR || EPI == kTcSwiglu) ? 128 : kTcBN, &map_w)) return MDB_ERR_CUDA;

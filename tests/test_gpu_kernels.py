@@ -327,6 +327,21 @@ def test_gemm_cta_pair_matches_single_cta(mdb, m, n, k):
     _status_clean(mdb)
 
 
+def test_gemm_activation_band_order(mdb):
+    """A step whose activations outgrow L2 (16384 rows x 6144: 201 MB) walks its tiles one activation band
+    after the other instead of one weight tile after the other; same products, checked against an fp32
+    matmul on the device (the CPU oracle would need minutes)."""
+    gen = torch.Generator(device=DEV).manual_seed(3)
+    m, n, k = 16384, 2048, 6144
+    x = torch.randn(m, k, generator=gen, device=DEV).to(BF)
+    w = (torch.randn(n, k, generator=gen, device=DEV) / k ** 0.5).to(BF)
+    got = mdb.ops.linear(x, w)
+    for r0 in (0, 5120, m - 1024):           # three 1024-row bands: first, middle, last
+        exact = x[r0:r0 + 1024].float() @ w.float().t()
+        _close_gemm(got[r0:r0 + 1024], exact.cpu())
+    _status_clean(mdb)
+
+
 def test_gemm_rejects_bad_arguments(mdb):
     x = torch.zeros(4, 100, dtype=BF, device=DEV)
     w = torch.zeros(64, 100, dtype=BF, device=DEV)

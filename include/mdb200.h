@@ -61,7 +61,10 @@ enum { MDB_OPT_STREAM_KERNEL = 0, MDB_OPT_PDL = 1, MDB_OPT_ATTN_KERNEL = 2, MDB_
 int mdb_set_option(int option, int value);
 /* Measurement aid: registers a device buffer (uint64 count, then (kernel,
  * event, globaltimer ns) triples) that block 0 of the traced kernels appends
- * to; NULL switches tracing off. */
+ * to; NULL switches tracing off.  The stamps exist only in a library built
+ * with -DMDB_TRACE (MDB_TRACE=1 python mineru-diffusion_b200/build.py); in the
+ * normal build the call registers the buffer and nothing is ever written to
+ * it: even testing the buffer pointer in the kernels costs 7 % of a short step. */
 int mdb_set_trace(void* buffer, int64_t bytes);
 int mdb_get_option(int option);
 

@@ -46,6 +46,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not os.path.exists(nvcc):
         raise RuntimeError("nvcc not found: libmdb200.so cannot be built on this machine")
     cmd = [nvcc, *NVCC_FLAGS]
+    if os.environ.get("MDB_TRACE") == "1":      # timeline stamps in the kernels (mdb_set_trace); off: compiled out
+        cmd += ["-DMDB_TRACE"]
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += ["-o", OUT, SRC]

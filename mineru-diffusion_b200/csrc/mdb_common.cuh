@@ -42,7 +42,15 @@ struct TraceBuf {
 __device__ TraceBuf g_trace = {nullptr, 0};
 
 __device__ __forceinline__ void trace_event(unsigned int kernel_id, unsigned int event_id) {
-  if (g_trace.data == nullptr || blockIdx.x != 0 || blockIdx.y != 0 || blockIdx.z != 0) return;
+#ifndef MDB_TRACE
+  // compiled out unless the library is built with -DMDB_TRACE: even the test of the buffer pointer is a global
+  // load on the critical path of block 0 of every kernel
+  (void)kernel_id;
+  (void)event_id;
+  return;
+#endif
+  if (blockIdx.x != 0 || blockIdx.y != 0 || blockIdx.z != 0) return;
+  if (g_trace.data == nullptr) return;
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   const unsigned long long slot = atomicAdd(g_trace.data, 1ull);

@@ -19,6 +19,15 @@ namespace mdb {
 constexpr int kAttnWarps = 4;
 constexpr int kAttnRows = kAttnWarps * 16;  // query rows per CTA
 constexpr int kAttnKeys = 64;               // keys per tile
+
+// Keys per key-range part of one request: an even share of its context rounded up to whole key tiles, but
+// never fewer than 256 keys, so that a part count chosen for the longest admissible context does not cut a
+// short one into single-tile parts (the trailing parts are then empty and cost one zero record each).
+__host__ __device__ __forceinline__ int attn_part_keys(int ctx, int nsplit, int tile_keys) {
+  if (ctx <= 0) return 0;
+  const int share = ((ctx + nsplit - 1) / nsplit + tile_keys - 1) / tile_keys * tile_keys;
+  return nsplit > 1 && share < 256 ? 256 : share;
+}
 constexpr int kAttnTileBytes = kAttnKeys * kHeadDim * 2;
 constexpr int kAttnSmemBytes = 2 /*stages*/ * 2 /*K,V*/ * kAttnTileBytes;  // 64 KB
 constexpr int64_t kAttnTcMinTiles = 0;       // 128-key tiles (upper bound) from which the tcgen05 kernel is chosen: measured no slower at any size
@@ -183,8 +192,7 @@ __device__ __forceinline__ void attn_paged_item(const AttnPagedArgs& a, uint32_t
 
   const int ctx = a.ctx_lens[req];
   // equal key ranges per split, rounded to whole tiles
-  int chunk = ctx > 0 ? (ctx + a.nsplit - 1) / a.nsplit : 0;
-  chunk = (chunk + kAttnKeys - 1) / kAttnKeys * kAttnKeys;
+  const int chunk = attn_part_keys(ctx, a.nsplit, kAttnKeys);
   const int kbeg = split * chunk;
   const int kend = min(ctx, kbeg + chunk);
   const int ntiles = kend > kbeg ? (kend - kbeg + kAttnKeys - 1) / kAttnKeys : 0;
@@ -334,7 +342,8 @@ __device__ __forceinline__ void attn_combine_row(const float* __restrict__ part_
         for (int i = 0; i < 8; ++i) {
           if (j0 + i < cnt) {
             if (s0 + j0 == 0) v[i] = first[i];
-            else v[i] = *reinterpret_cast<const float4*>(part_o + (p0 + (s0 + j0 + i) * pstride) * kHeadDim + lane * 4);
+            else if (__shfl_sync(0xffffffffu, w, j0 + i) != 0.f)   // empty parts are not fetched
+              v[i] = *reinterpret_cast<const float4*>(part_o + (p0 + (s0 + j0 + i) * pstride) * kHeadDim + lane * 4);
           }
         }
 #pragma unroll

@@ -193,8 +193,7 @@ __device__ __forceinline__ AtUnit at_unit(const AtArgs& a, const uint16_t* order
   w.split = rem % a.nsplit;
   w.q_tok0 = w.req * a.block + w.tok0;
   const int ctx = a.ctx_lens[w.req];
-  int chunk = ctx > 0 ? (ctx + a.nsplit - 1) / a.nsplit : 0;
-  chunk = (chunk + kAtKeys - 1) / kAtKeys * kAtKeys;
+  const int chunk = attn_part_keys(ctx, a.nsplit, kAtKeys);
   w.kbeg = w.split * chunk;
   w.kend = min(ctx, w.kbeg + chunk);
   w.ntiles = w.kend > w.kbeg ? (w.kend - w.kbeg + kAtKeys - 1) / kAtKeys : 0;

@@ -139,14 +139,13 @@ class ModelRunner:
             # word 1 of the step slot is the flag epoch: step index + 1, so that real steps never reuse the
             # sequence numbers of the warm-up launches made while graphs are captured (epoch 0)
             self.engine.attach_tp(self.tp_pair, self.dv["step"][1:2])
-        # sampler state on the device and its pinned mirror: ids int64 | transfer u8 | counts i32
-        n = self.max_bs * b
-        self.block_ids = torch.zeros(self.max_bs, b, dtype=torch.int64, device=self.device)
-        self.transfer = torch.zeros(self.max_bs, b, dtype=torch.uint8, device=self.device)
-        self.counts = torch.zeros(self.max_bs, dtype=torch.int32, device=self.device)
-        self.h_block_ids = torch.zeros(self.max_bs, b, dtype=torch.int64, pin_memory=True)
-        self.h_transfer = torch.zeros(self.max_bs, b, dtype=torch.uint8, pin_memory=True)
-        self.h_counts = torch.zeros(self.max_bs, dtype=torch.int32, pin_memory=True)
+        # sampler state: one flat device buffer and its pinned mirror, laid out per batch size as
+        # ids int64 [bs, B] | counts int32 [bs] | transfer u8 [bs, B], so the results of a step come back in one copy
+        self.res_dev = torch.zeros(self.max_bs * (9 * b + 4), dtype=torch.uint8, device=self.device)
+        self.res_host = torch.zeros(self.max_bs * (9 * b + 4), dtype=torch.uint8, pin_memory=True)
+        self._res_views: dict[int, tuple] = {}
+        self._decode_key = None       # requests and lengths the pinned step inputs were last built for
+        self._decode_max_ctx = 0
         self.graphs: dict[int, tuple[torch.cuda.CUDAGraph, int]] = {}
         self.graph_bs: list[int] = []
         self.last: dict = {}
@@ -197,27 +196,54 @@ class ModelRunner:
                       self.block_size)
         return up(inp["input_ids"]), up(inp["positions"]), ctx, inp["cu_seqlens"].tolist()
 
-    def prepare_decode(self, seqs: list[Sequence]):
-        """Fills the packed pinned buffer and starts its copy; returns the longest context."""
+    def _result_views(self, bs: int):
+        """Views of the sampler-state buffers for a step of ``bs`` requests:
+        (device bytes, pinned bytes, device ids/counts/transfer, pinned ids and numpy views of the pinned
+        counts/transfer)."""
+        v = self._res_views.get(bs)
+        if v is None:
+            b = self.block_size
+            o1, o2, o3 = bs * b * 8, bs * b * 8 + bs * 4, bs * (9 * b + 4)
+            def split(buf):
+                return (buf[:o1].view(torch.int64).view(bs, b), buf[o1:o2].view(torch.int32), buf[o2:o3].view(bs, b))
+            host = split(self.res_host)
+            v = (self.res_dev[:o3], self.res_host[:o3]) + split(self.res_dev) + (host[0], host[1].numpy(), host[2].numpy())
+            self._res_views[bs] = v
+        return v
+
+    def prepare_decode(self, seqs: list[Sequence], copy: bool = True):
+        """Fills the packed pinned buffer and (``copy``) starts its copy; returns the longest context.
+        While the same requests stay on the same blocks (one denoising step after another) only the
+        token ids and the step counter change, so everything else is left as the last step wrote it."""
         b, bs = self.block_size, len(seqs)
-        inp = build_decode_inputs(seqs, b)
-        width = inp["block_tables"].shape[1]
-        if width > self.max_pages:
-            raise AssertionError("page table wider than max_model_len allows")
         hn = self.hn
-        hn["slots"].fill(-1)
-        hn["ctx"].fill(0)
-        hn["ids"][:bs] = inp["input_ids"]
-        hn["pos"][:bs] = inp["positions"]
-        hn["slots"][:bs] = inp["slot_mapping"]
-        hn["ctx"][:bs] = inp["context_lens"]
-        hn["tab"][:bs, :width] = inp["block_tables"]
-        for i, seq in enumerate(seqs):
-            hn["temp"][i] = seq.temperature
+        key = (tuple(map(id, seqs)), tuple(map(len, seqs)), tuple(len(seq.block_table) for seq in seqs))
+        if key == self._decode_key:
+            if bs == 1:
+                hn["ids"][0] = seqs[0].current_denoising_block.numpy()
+            else:
+                np.stack([seq.current_denoising_block.numpy() for seq in seqs], out=hn["ids"][:bs])
+        else:
+            inp = build_decode_inputs(seqs, b)
+            width = inp["block_tables"].shape[1]
+            if width > self.max_pages:
+                raise AssertionError("page table wider than max_model_len allows")
+            hn["slots"].fill(-1)
+            hn["ctx"].fill(0)
+            hn["ids"][:bs] = inp["input_ids"]
+            hn["pos"][:bs] = inp["positions"]
+            hn["slots"][:bs] = inp["slot_mapping"]
+            hn["ctx"][:bs] = inp["context_lens"]
+            hn["tab"][:bs, :width] = inp["block_tables"]
+            for i, seq in enumerate(seqs):
+                hn["temp"][i] = seq.temperature
+            self._decode_key = key
+            self._decode_max_ctx = int(inp["context_lens"].max())
         hn["step"][0] = self.step_index
         hn["step"][1] = self.step_index + 1
-        self.inputs.dev.copy_(self.inputs.host, non_blocking=True)
-        return int(inp["context_lens"].max())
+        if copy:
+            self.inputs.dev.copy_(self.inputs.host, non_blocking=True)
+        return self._decode_max_ctx
 
     def prepare_sample(self, seqs: list[Sequence]) -> torch.Tensor:
         t = torch.tensor([seq.temperature for seq in seqs], dtype=torch.float32, pin_memory=True)
@@ -261,10 +287,10 @@ class ModelRunner:
     @torch.inference_mode()
     def run_model_decode(self, seqs: list[Sequence]):
         bs = len(seqs)
-        max_ctx = self.prepare_decode(seqs)
-        if self.step_events is not None:
-            self.step_events[0].record()      # inputs are resident from here on
         use_graph = (not self.enforce_eager) and self.noise != "explicit" and bs <= self.max_bs and self.graph_bs
+        max_ctx = self.prepare_decode(seqs, copy=not use_graph)   # a graph starts with the copy of the packed inputs
+        if self.step_events is not None:
+            self.step_events[0].record()
         if use_graph:
             gbs = next(x for x in self.graph_bs if x >= bs)
             graph, _ = self.graphs[gbs]
@@ -276,6 +302,7 @@ class ModelRunner:
     def run_model_prefill(self, seqs: list[Sequence]):
         b = self.block_size
         input_ids, positions, ctx, cu = self.prepare_prefill(seqs)
+        self._decode_key = None            # pages may have been handed out anew
         m = input_ids.numel()
         eng = self.engine
         if m > eng.max_tokens:
@@ -310,8 +337,13 @@ class ModelRunner:
             hidden = self.engine.final[:bs * b]     # final-norm rows of the step (graph replays write here too)
         with torch.inference_mode():
             # sampler state: the host copy of each block is the source of truth, as in the reference
-            torch.stack([seq.current_denoising_block for seq in seqs], out=self.h_block_ids[:bs])
-            self.block_ids[:bs].copy_(self.h_block_ids[:bs], non_blocking=True)
+            # (a decode step has just sent those ids down as its input)
+            d_all, h_all, d_ids, d_counts, d_transfer, h_ids, h_counts, h_transfer = self._result_views(bs)
+            if is_prefill:
+                torch.stack([seq.current_denoising_block for seq in seqs], out=h_ids)
+                d_ids.copy_(h_ids, non_blocking=True)
+            else:
+                d_ids.copy_(self.dv["ids"][:bs], non_blocking=True)
             sp = seqs[0].sampling_params
             if sp.denoising_strategy != "low_confidence_dynamic":
                 raise NotImplementedError(f"Denoising strategy {sp.denoising_strategy} not implemented")
@@ -319,26 +351,24 @@ class ModelRunner:
             if sp.denoising_steps:
                 quota = max(1, b // sp.denoising_steps)
             m = bs * b
-            ops.unmask_decide(self.block_ids[:bs], self.engine.x0[:m], self.engine.conf[:m], seqs[0].mask_token_id,
-                              sp.dynamic_threshold, quota, transfer=self.transfer[:bs], counts=self.counts[:bs])
+            ops.unmask_decide(d_ids, self.engine.x0[:m], self.engine.conf[:m], seqs[0].mask_token_id,
+                              sp.dynamic_threshold, quota, transfer=d_transfer, counts=d_counts)
             if self.step_events is not None and not is_prefill:
                 self.step_events[1].record()
-            self.h_block_ids[:bs].copy_(self.block_ids[:bs], non_blocking=True)
-            self.h_transfer[:bs].copy_(self.transfer[:bs], non_blocking=True)
-            self.h_counts[:bs].copy_(self.counts[:bs], non_blocking=True)
+            h_all.copy_(d_all, non_blocking=True)
             if self.keep_last:
                 self.last = dict(x0=self.engine.x0[:m].clone(), conf=self.engine.conf[:m].clone(),
                                  hidden=None if hidden is None else hidden.clone())
             torch.cuda.current_stream().synchronize()
         # one copy of the results for the whole batch; every request keeps a row of it
-        blocks = self.h_block_ids[:bs].clone()
-        moved = self.h_transfer[:bs].bool()
+        blocks = h_ids.clone().unbind(0)
+        moved = h_transfer != 0
         for i, seq in enumerate(seqs):
             seq.current_denoising_block = blocks[i]
-            seq.current_step_map[moved[i]] = seq.current_denoise_step
+            seq.current_step_map.numpy()[moved[i]] = seq.current_denoise_step
             seq.current_denoise_step += 1
         self.step_index += 1
-        return int(self.h_counts[:bs].sum())
+        return int(h_counts.sum())
 
     def launches_per_decode_step(self, bs: int = 1) -> int:
         """Kernels of libmdb200 launched by one decode-form step: row gather,
@@ -363,11 +393,13 @@ class ModelRunner:
     # ------------------------------------------------------------------ CUDA graphs
     @torch.inference_mode()
     def capture_cudagraph(self):
-        """One graph per batch-size bucket covering embedding gather, all
-        layers, the LM head and the sampler statistics.  Padded rows carry
+        """One graph per batch-size bucket covering the copy of the packed
+        step inputs from pinned memory, embedding gather, all layers, the LM
+        head and the sampler statistics.  Padded rows carry
         slot -1 and context length 0, which every kernel treats as a no-op."""
         if self.noise == "explicit":
             return
+        self._decode_key = None            # the pinned input buffer is rewritten below
         max_bs = self.max_bs
         self.graph_bs = [x for x in (1, 2, 4, 8) if x <= max_bs] + list(range(16, max_bs + 1, 16))
         hv = self.hv
@@ -381,6 +413,7 @@ class ModelRunner:
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, pool):
+                self.inputs.dev.copy_(self.inputs.host, non_blocking=True)   # pinned buffer, read at replay time
                 self._decode_body(bs, nsplit)
             if pool is None:
                 pool = graph.pool()

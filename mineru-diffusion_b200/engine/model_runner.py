@@ -145,6 +145,7 @@ class ModelRunner:
         self.res_host = torch.zeros(self.max_bs * (9 * b + 4), dtype=torch.uint8, pin_memory=True)
         self._res_views: dict[int, tuple] = {}
         self._decode_key = None       # requests and lengths the pinned step inputs were last built for
+        self._last_rows, self._last_blocks = None, None   # blocks handed to the requests after the last step
         self._decode_max_ctx = 0
         self.graphs: dict[int, tuple[torch.cuda.CUDAGraph, int]] = {}
         self.graph_bs: list[int] = []
@@ -219,10 +220,17 @@ class ModelRunner:
         hn = self.hn
         key = (tuple(map(id, seqs)), tuple(map(len, seqs)), tuple(len(seq.block_table) for seq in seqs))
         if key == self._decode_key:
-            if bs == 1:
-                hn["ids"][0] = seqs[0].current_denoising_block.numpy()
+            ids, rows = hn["ids"], self._last_rows
+            if rows is not None and len(rows) == bs:
+                # the blocks handed out after the last step, in one copy; a request that has started a new
+                # block since holds another tensor
+                ids[:bs] = self._last_blocks
+                for i, seq in enumerate(seqs):
+                    if seq.current_denoising_block is not rows[i]:
+                        ids[i] = seq.current_denoising_block.numpy()
             else:
-                np.stack([seq.current_denoising_block.numpy() for seq in seqs], out=hn["ids"][:bs])
+                for i, seq in enumerate(seqs):
+                    ids[i] = seq.current_denoising_block.numpy()
         else:
             inp = build_decode_inputs(seqs, b)
             width = inp["block_tables"].shape[1]
@@ -361,12 +369,16 @@ class ModelRunner:
                                  hidden=None if hidden is None else hidden.clone())
             torch.cuda.current_stream().synchronize()
         # one copy of the results for the whole batch; every request keeps a row of it
-        blocks = h_ids.clone().unbind(0)
+        blocks = h_ids.clone()
+        rows = blocks.unbind(0)
         moved = h_transfer != 0
+        moved_any = moved.any(axis=1)
         for i, seq in enumerate(seqs):
-            seq.current_denoising_block = blocks[i]
-            seq.current_step_map.numpy()[moved[i]] = seq.current_denoise_step
+            seq.current_denoising_block = rows[i]
+            if moved_any[i]:
+                seq.current_step_map.numpy()[moved[i]] = seq.current_denoise_step
             seq.current_denoise_step += 1
+        self._last_rows, self._last_blocks = rows, blocks.numpy()   # shares memory with the rows
         self.step_index += 1
         return int(h_counts.sum())
 

@@ -11,6 +11,9 @@ from __future__ import annotations
 
 from collections import deque
 
+import numpy as np
+import torch
+
 from .block_manager import BlockManager
 from .sequence import Sequence, SequenceStatus
 
@@ -70,11 +73,20 @@ class Scheduler:
         self.waiting.appendleft(seq)
 
     def postprocess(self, seqs: list[Sequence]):
-        for seq in seqs:
-            if not seq.is_caching:
+        caching = [seq for seq in seqs if seq.is_caching]
+        denoising = [seq for seq in seqs if not seq.is_caching]
+        if len(denoising) > 4:
+            # one comparison for the whole batch: a block with no masked position left goes to its caching pass
+            ids = torch.stack([seq.current_denoising_block for seq in denoising]).numpy()
+            mask_ids = np.fromiter((seq.mask_token_id for seq in denoising), dtype=np.int64, count=len(denoising))
+            masked_left = (ids == mask_ids[:, None]).any(axis=1)
+            for i in np.flatnonzero(~masked_left):
+                denoising[i].status = SequenceStatus.CACHING
+        else:
+            for seq in denoising:
                 if not bool((seq.current_denoising_block.numpy() == seq.mask_token_id).any()):   # numpy view: no dispatch cost
                     seq.status = SequenceStatus.CACHING
-                continue
+        for seq in caching:
             block_np = seq.current_denoising_block.numpy()
             hit_stop = any(bool((block_np == t).any()) for t in seq.sampling_params.stop_token_ids)
             seq.append_block()

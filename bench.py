@@ -301,8 +301,8 @@ def run_cpu_sample(steps: int, warmup: int, threads: int | None = None):
     the context length reached half way through generation, KV cache filled
     with seeded noise instead of a CPU prefill."""
     from oracle import nano_oracle as orc
-    if threads:
-        torch.set_num_threads(threads)
+    # every core this process may run on (a torchrun launch sets OMP_NUM_THREADS=1, which would leave 1 thread)
+    torch.set_num_threads(threads or len(os.sched_getaffinity(0)))
     orc.use_native_linear(True)
     cfg = orc.DecoderConfig()
     g = torch.Generator().manual_seed(WEIGHT_SEED)

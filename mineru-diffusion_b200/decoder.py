@@ -338,7 +338,11 @@ class DecoderEngine:
                                       step=step, step_dev=step_dev, workspace=self.lm_ws, x0=self.x0[:m],
                                       conf=self.conf[:m])
         if m > SKINNY_MAX_ROWS:
-            raise NotImplementedError("the tensor-parallel LM head takes at most 64 rows per step")
+            # Many-row steps: both ranks hold the whole LM head and bit-identical hidden rows, so each scans the
+            # full vocabulary itself and reaches the same decisions with nothing exchanged.
+            return ops.lm_head_sample(rows, self.w.lm_head, temperatures, self.block_size, noise=noise, seed=seed,
+                                      step=step, step_dev=step_dev, workspace=self.lm_ws, x0=self.x0[:m],
+                                      conf=self.conf[:m])
         # vocabulary tiles (128 rows) split between the two ranks; records are exchanged, never logits
         tiles = self.cfg.vocab_size // 128
         first = (tiles + 1) // 2

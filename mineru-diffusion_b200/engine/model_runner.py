@@ -414,6 +414,8 @@ class ModelRunner:
         self._decode_key = None            # the pinned input buffer is rewritten below
         max_bs = self.max_bs
         self.graph_bs = [x for x in (1, 2, 4, 8) if x <= max_bs] + list(range(16, max_bs + 1, 16))
+        if self.graph_bs[-1] != max_bs:      # a batch limit between two buckets gets a bucket of its own
+            self.graph_bs.append(max_bs)
         hv = self.hv
         hv["ids"].zero_(); hv["pos"].zero_(); hv["slots"].fill_(-1); hv["ctx"].zero_(); hv["tab"].fill_(-1)
         hv["temp"].fill_(1.0)

@@ -15,7 +15,7 @@ from conftest import ROOT
 pytestmark = pytest.mark.gpu
 
 
-def _child(rank, port, out_dir, eager):
+def _child(rank, port, out_dir, eager, nreq=2):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import torch.distributed as dist
@@ -32,7 +32,7 @@ def _child(rank, port, out_dir, eager):
     weights = orc.make_weights(ocfg, seed=31)
 
     def runner(tp):
-        cfg = mdb.Config(max_num_batched_tokens=2048, max_num_seqs=2, max_model_len=1024, enforce_eager=eager,
+        cfg = mdb.Config(max_num_batched_tokens=2048, max_num_seqs=nreq, max_model_len=1024, enforce_eager=eager,
                          num_kvcache_blocks=6, decoder_config=dcfg, mask_token_id=1000, tensor_parallel_size=tp)
         r = mdb.ModelRunner(cfg, rank=rank if tp == 2 else 0, device=dev,
                             weights=mdb.DecoderWeights.from_reference_layout(weights, dev),
@@ -43,7 +43,7 @@ def _child(rank, port, out_dir, eager):
     cfg2, r2 = runner(2)
     cfg1, r1 = runner(1)
     gen = torch.Generator().manual_seed(9)
-    prompts = [torch.randint(0, 990, (n,), generator=gen).tolist() for n in (200, 40)]
+    prompts = [torch.randint(0, 990, (n,), generator=gen).tolist() for n in (200, 40, 90)[:nreq]]
     noise = {}
 
     def noise_fn(step, m, v):
@@ -59,7 +59,7 @@ def _child(rank, port, out_dir, eager):
         for i, p in enumerate(prompts):
             sp = mdb.SamplingParams(temperature=1.0, max_new_tokens=64, ignore_eos=True)
             s = mdb.Sequence(p, sp, denoising_block_size=32, mask_token_id=1000)
-            s.block_table = [[4, 1], [2]][i]
+            s.block_table = [[4, 1], [2], [3]][i]
             out.append(s)
         return out
 
@@ -106,4 +106,25 @@ def test_tp2_matches_tp1_and_ranks_agree(tmp_path, eager):
         agree += int(same.sum())
         total += same.numel()
     print(f"TP=2 vs TP=1 sampled-token agreement {agree}/{total}, hidden max-abs {max(r0['hidden_err']):.4f}")
+    assert agree / total >= 0.9
+
+
+@pytest.mark.parametrize("eager", [True, False])
+def test_tp2_many_row_steps(tmp_path, eager):
+    """Three requests = 96 rows per step: the row-parallel projections go through the many-row GEMM + the
+    reference's collective, the LM head is scanned whole on both ranks."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    port = 29300 + os.getpid() % 200 + (0 if eager else 1)
+    mp.start_processes(_child, args=(port, str(tmp_path), eager, 3), nprocs=2, join=True, start_method="spawn")
+    r0, r1 = torch.load(tmp_path / "rank0.pt"), torch.load(tmp_path / "rank1.pt")
+    assert r0["status"] == 0 and r1["status"] == 0
+    agree = total = 0
+    for step in range(6):
+        assert torch.equal(r0["x0_tp"][step], r1["x0_tp"][step])
+        assert torch.equal(r0["conf_tp"][step], r1["conf_tp"][step])
+        assert r0["hidden_err"][step] <= 0.08, r0["hidden_err"]
+        same = r0["x0_tp"][step] == r0["x0_one"][step]
+        agree += int(same.sum())
+        total += same.numel()
     assert agree / total >= 0.9

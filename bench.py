@@ -127,7 +127,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     nreq = REQUESTS
     if nreq > 1:
         # config 3: per-request visual rows uniform in [512, 4096]; pages for every request's full length
-        vg = torch.Generator().manual_seed(3 + rank)
+        vg = torch.Generator().manual_seed(3 + (0 if args.tp == 2 else rank))   # a TP pair serves the same requests
         visual_rows = torch.randint(512, VISUAL_MAX + 1, (nreq,), generator=vg).tolist()
         pages = sum((v + TEXT_IDS + NEW_TOKENS + BLOCK + 255) // 256 for v in visual_rows) + 2
         max_len = (VISUAL_MAX + TEXT_IDS + NEW_TOKENS + BLOCK + 255) // 256 * 256

@@ -333,6 +333,23 @@ int mdb_add_rmsnorm_tp(const void* x, const float* partials, int nparts, const v
                        float eps, void* y_out, void* residual_out, int m, int h, const uint32_t* wait_flags,
                        int wait_count, uint32_t tag, const uint32_t* epoch, mdb_stream_t stream);
 
+/* The same exchange for steps of more than 64 rows (RowParallelLinear.forward +
+ * dist.all_reduce, NV/layers/linear.py:153-157, on the tcgen05 tile GEMM):
+ * mdb_gemm_bf16_tp stores every bf16 output tile into y and, with plain stores
+ * over NVLink, into y_peer (the landing buffer in the peer's mdb_tp_alloc
+ * memory, same leading dimension); each CTA then raises peer_flags[cta].
+ * *grid_out = number of CTAs launched = flag slots the consumer has to wait
+ * for (both ranks launch the same shape).  MDB_ERR_UNSUPPORTED unless m > 64
+ * and the shape suits the tile kernel (k % 64 == 0, n % 8 == 0, ldy % 8 == 0).
+ * mdb_add_rmsnorm_tp_rows waits for those slots and takes bf16(x + x_peer) as
+ * its input row (x: this rank's output, x_peer: the local landing buffer the
+ * peer wrote), which is what the all-reduce of two bf16 tensors yields. */
+int mdb_gemm_bf16_tp(const void* x, int64_t ldx, const void* w, void* y, void* y_peer, int64_t ldy, int m, int n, int k,
+                     uint32_t* peer_flags, uint32_t tag, const uint32_t* epoch, int* grid_out, mdb_stream_t stream);
+int mdb_add_rmsnorm_tp_rows(const void* x, const void* x_peer, const void* residual_in, const void* weight, float eps,
+                            void* y_out, void* residual_out, int m, int h, const uint32_t* wait_flags, int wait_count,
+                            uint32_t tag, const uint32_t* epoch, mdb_stream_t stream);
+
 /* mdb_lmhead_sample over the vocabulary tiles [tile_begin, tile_begin + tile_count)
  * (128 rows each) of the full weight; the per-tile records (20 bytes per step
  * row) are mirrored into the peer's workspace instead of gathering logits, and

@@ -188,6 +188,27 @@ int mdb_gemm_bf16(const void* x, int64_t ldx, const void* w, void* y, int64_t ld
                            m, n, k, st);
 }
 
+int mdb_gemm_bf16_tp(const void* x, int64_t ldx, const void* w, void* y, void* y_peer, int64_t ldy, int m, int n, int k,
+                     uint32_t* peer_flags, uint32_t tag, const uint32_t* epoch, int* grid_out, mdb_stream_t stream) {
+  MDB_REQUIRE(m > 64 && n > 0 && k > 0, MDB_ERR_UNSUPPORTED);
+  MDB_REQUIRE(x && w && y && y_peer && peer_flags && epoch && grid_out && ldx >= k && ldy >= n, MDB_ERR_ARG);
+  MDB_REQUIRE(tag >= 1 && tag <= 255, MDB_ERR_ARG);
+  MDB_REQUIRE(ldx % 8 == 0 && ldy % 8 == 0 && mdb_aligned16(x) && mdb_aligned16(w) && mdb_aligned16(y) &&
+                  mdb_aligned16(y_peer),
+              MDB_ERR_ALIGN);
+  MDB_REQUIRE(g_opt_stream_kernel == 0 && tc_supported(kTcBf16, m, n, k, ldx, ldy), MDB_ERR_UNSUPPORTED);
+  TcArgs a = {};
+  a.m = m; a.n = n; a.k = k;
+  a.y = static_cast<bf16*>(y);
+  a.y_peer = static_cast<bf16*>(y_peer);
+  a.ldy = ldy;
+  a.tp = {peer_flags, nullptr, 0, tag, epoch};
+  const int rc = launch_tc<kTcBf16>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), n, a,
+                                    static_cast<cudaStream_t>(stream));
+  *grid_out = a.grid;
+  return rc;
+}
+
 int mdb_gemm_qkv_rope_commit(const void* x, int64_t ldx, const void* w_qkv, int m, int k, const int64_t* positions,
                              const float* rope_table, int max_pos, const void* q_norm_w, const void* k_norm_w,
                              float eps, const int32_t* slot_mapping, void* q_out, void* k_out, void* v_out,

@@ -41,7 +41,7 @@ constexpr int kNormMaxChunks = 4;  // h <= 256 * 4 * 8 = 8192
 // PARTIALS: the input row is the sum of fp32 slices (short steps; latency-bound, loads batched) or a bf16 row.
 template <bool PARTIALS>
 __global__ void __launch_bounds__(kNormThreads)
-add_rmsnorm_kernel(const bf16* __restrict__ x, const float* __restrict__ partials, int nparts,
+add_rmsnorm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ x2, const float* __restrict__ partials, int nparts,
                    const bf16* __restrict__ residual_in, const bf16* __restrict__ weight, float eps,
                    bf16* __restrict__ y_out, bf16* __restrict__ residual_out, int m, int h, const TpSignal tp) {
   if (threadIdx.x == 0) trace_event(10, 0);
@@ -93,6 +93,15 @@ add_rmsnorm_kernel(const bf16* __restrict__ x, const float* __restrict__ partial
         f = unpack_bf16x2(u.y); a[2] = f.x; a[3] = f.y;
         f = unpack_bf16x2(u.z); a[4] = f.x; a[5] = f.y;
         f = unpack_bf16x2(u.w); a[6] = f.x; a[7] = f.y;
+        if (x2 != nullptr) {
+          // tensor-parallel pair: the other rank's partial output; the sum is rounded to bf16 as the
+          // all-reduce of two bf16 tensors rounds it (a + b is the same on both ranks)
+          const uint4 w2 = *reinterpret_cast<const uint4*>(x2 + row_off + c * 8);
+          f = unpack_bf16x2(w2.x); a[0] = bf16_round(a[0] + f.x); a[1] = bf16_round(a[1] + f.y);
+          f = unpack_bf16x2(w2.y); a[2] = bf16_round(a[2] + f.x); a[3] = bf16_round(a[3] + f.y);
+          f = unpack_bf16x2(w2.z); a[4] = bf16_round(a[4] + f.x); a[5] = bf16_round(a[5] + f.y);
+          f = unpack_bf16x2(w2.w); a[6] = bf16_round(a[6] + f.x); a[7] = bf16_round(a[7] + f.y);
+        }
       }
       if (residual_in != nullptr) {
         const uint4 u = *reinterpret_cast<const uint4*>(residual_in + row_off + c * 8);
@@ -408,7 +417,7 @@ int mdb_kv_commit(const void* key, int64_t key_stride, const void* value, int64_
                     static_cast<bf16*>(k_cache), static_cast<bf16*>(v_cache), slot_mapping, row_elems, num_slots);
 }
 
-static int add_rmsnorm_impl(const void* x, const float* partials, int nparts, const void* residual_in,
+static int add_rmsnorm_impl(const void* x, const void* x2, const float* partials, int nparts, const void* residual_in,
                             const void* weight, float eps, void* y_out, void* residual_out, int m, int h,
                             const TpSignal& tp, mdb_stream_t stream) {
   MDB_REQUIRE(m >= 0 && h > 0, MDB_ERR_ARG);
@@ -422,19 +431,19 @@ static int add_rmsnorm_impl(const void* x, const float* partials, int nparts, co
               MDB_ERR_ALIGN);
   if (partials != nullptr)
     return mdb_launch(add_rmsnorm_kernel<true>, dim3(m), dim3(kNormThreads), 0, static_cast<cudaStream_t>(stream),
-                      static_cast<const bf16*>(x), partials, nparts, static_cast<const bf16*>(residual_in),
-                      static_cast<const bf16*>(weight), eps, static_cast<bf16*>(y_out),
-                      static_cast<bf16*>(residual_out), m, h, tp);
+                      static_cast<const bf16*>(x), static_cast<const bf16*>(x2), partials, nparts,
+                      static_cast<const bf16*>(residual_in), static_cast<const bf16*>(weight), eps,
+                      static_cast<bf16*>(y_out), static_cast<bf16*>(residual_out), m, h, tp);
   return mdb_launch(add_rmsnorm_kernel<false>, dim3(m), dim3(kNormThreads), 0, static_cast<cudaStream_t>(stream),
-                    static_cast<const bf16*>(x), partials, nparts, static_cast<const bf16*>(residual_in),
-                    static_cast<const bf16*>(weight), eps, static_cast<bf16*>(y_out),
-                    static_cast<bf16*>(residual_out), m, h, tp);
+                    static_cast<const bf16*>(x), static_cast<const bf16*>(x2), partials, nparts,
+                    static_cast<const bf16*>(residual_in), static_cast<const bf16*>(weight), eps,
+                    static_cast<bf16*>(y_out), static_cast<bf16*>(residual_out), m, h, tp);
 }
 
 int mdb_add_rmsnorm(const void* x, const float* partials, int nparts, const void* residual_in, const void* weight,
                     float eps, void* y_out, void* residual_out, int m, int h, mdb_stream_t stream) {
   const TpSignal none = {nullptr, nullptr, 0, 0, nullptr};
-  return add_rmsnorm_impl(x, partials, nparts, residual_in, weight, eps, y_out, residual_out, m, h, none, stream);
+  return add_rmsnorm_impl(x, nullptr, partials, nparts, residual_in, weight, eps, y_out, residual_out, m, h, none, stream);
 }
 
 int mdb_add_rmsnorm_tp(const void* x, const float* partials, int nparts, const void* residual_in, const void* weight,
@@ -442,7 +451,16 @@ int mdb_add_rmsnorm_tp(const void* x, const float* partials, int nparts, const v
                        int wait_count, uint32_t tag, const uint32_t* epoch, mdb_stream_t stream) {
   MDB_REQUIRE(wait_flags && epoch && wait_count > 0 && tag >= 1 && tag <= 255, MDB_ERR_ARG);
   const TpSignal tp = {nullptr, wait_flags, wait_count, tag, epoch};
-  return add_rmsnorm_impl(x, partials, nparts, residual_in, weight, eps, y_out, residual_out, m, h, tp, stream);
+  return add_rmsnorm_impl(x, nullptr, partials, nparts, residual_in, weight, eps, y_out, residual_out, m, h, tp, stream);
+}
+
+int mdb_add_rmsnorm_tp_rows(const void* x, const void* x_peer, const void* residual_in, const void* weight, float eps,
+                            void* y_out, void* residual_out, int m, int h, const uint32_t* wait_flags, int wait_count,
+                            uint32_t tag, const uint32_t* epoch, mdb_stream_t stream) {
+  MDB_REQUIRE(x && x_peer && wait_flags && epoch && wait_count > 0 && tag >= 1 && tag <= 255, MDB_ERR_ARG);
+  MDB_REQUIRE(mdb_aligned16(x_peer), MDB_ERR_ALIGN);
+  const TpSignal tp = {nullptr, wait_flags, wait_count, tag, epoch};
+  return add_rmsnorm_impl(x, x_peer, nullptr, 0, residual_in, weight, eps, y_out, residual_out, m, h, tp, stream);
 }
 
 int mdb_qknorm_rope_commit(const void* qkv, int64_t ld_qkv, const float* partials, int nparts,

@@ -81,6 +81,11 @@ struct TcArgs {
   bf16* k_cache;               // [slots][hkv][128]
   bf16* v_cache;
   int64_t num_slots;
+  // tensor-parallel pair, bf16 epilogue: every output tile is also stored into the peer's memory (same
+  // leading dimension), then the CTA raises its flag slot there (all null / zero on one GPU)
+  bf16* y_peer;
+  TpSignal tp;
+  int grid;                    // CTAs launched (set by the launcher; the peer waits for that many flags)
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -284,6 +289,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       const int row = tm * kRowsPerTile + static_cast<int>(rank) * kTcBM + 32 * quarter + lane;
       if (EPI == kTcBf16) {
         bf16* dst = a.y + static_cast<int64_t>(row) * a.ldy + tn * kTcBN;
+        // Tensor-parallel pair: the copy for the peer is staged in shared memory, 32 rows x 64 columns per warp,
+        // and leaves as 128-byte row segments (four rows per store instruction): over NVLink the 16-byte pieces
+        // a thread holds of its own row would travel one by one.
+        const bool peer_staged = a.y_peer != nullptr && (tn + 1) * kTcBN <= a.n;
+        const uint32_t stage_smem = base + bars_off + 256 + (warp & 3) * 4096;
 #pragma unroll 1
         for (int c = 0; c < kTcBN / 32; ++c) {
           float v0[16], v1[16];
@@ -300,13 +310,51 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
               o[3] = make_uint4(pack_bf16x2(v1[8], v1[9]), pack_bf16x2(v1[10], v1[11]), pack_bf16x2(v1[12], v1[13]), pack_bf16x2(v1[14], v1[15]));
               uint4* d4 = reinterpret_cast<uint4*>(dst + 32 * c);
               d4[0] = o[0]; d4[1] = o[1]; d4[2] = o[2]; d4[3] = o[3];
+              if (a.y_peer != nullptr && !peer_staged) {   // ragged right edge: the same 64 bytes straight to the peer
+                uint4* p4 = reinterpret_cast<uint4*>(a.y_peer + static_cast<int64_t>(row) * a.ldy + tn * kTcBN + 32 * c);
+                p4[0] = o[0]; p4[1] = o[1]; p4[2] = o[2]; p4[3] = o[3];
+              }
+              if (peer_staged) {
+                // 16-byte piece s of a staged row sits at piece s ^ (row & 7): no bank conflicts either way
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const uint32_t piece = static_cast<uint32_t>(4 * (c & 1) + i) ^ static_cast<uint32_t>(lane & 7);
+                  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_smem + lane * 128 + (piece << 4)),
+                               "r"(o[i].x), "r"(o[i].y), "r"(o[i].z), "r"(o[i].w)
+                               : "memory");
+                }
+              }
             } else {
+              bf16* pdst = a.y_peer != nullptr ? a.y_peer + static_cast<int64_t>(row) * a.ldy + tn * kTcBN : nullptr;
 #pragma unroll
               for (int i = 0; i < 16; ++i) {
-                if (col + i < a.n) dst[32 * c + i] = __float2bfloat16_rn(v0[i]);
-                if (col + 16 + i < a.n) dst[32 * c + 16 + i] = __float2bfloat16_rn(v1[i]);
+                if (col + i < a.n) {
+                  dst[32 * c + i] = __float2bfloat16_rn(v0[i]);
+                  if (pdst != nullptr) pdst[32 * c + i] = __float2bfloat16_rn(v0[i]);
+                }
+                if (col + 16 + i < a.n) {
+                  dst[32 * c + 16 + i] = __float2bfloat16_rn(v1[i]);
+                  if (pdst != nullptr) pdst[32 * c + 16 + i] = __float2bfloat16_rn(v1[i]);
+                }
               }
             }
+          }
+          if (peer_staged && (c & 1)) {
+            __syncwarp();
+            const int row0 = tm * kRowsPerTile + static_cast<int>(rank) * kTcBM + 32 * quarter;
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const int r = 4 * it + (lane >> 3);
+              const uint32_t piece = static_cast<uint32_t>(lane & 7) ^ static_cast<uint32_t>(r & 7);
+              uint4 o;
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(o.x), "=r"(o.y), "=r"(o.z), "=r"(o.w)
+                           : "r"(stage_smem + r * 128 + (piece << 4)));
+              if (row0 + r < a.m)
+                *reinterpret_cast<uint4*>(a.y_peer + static_cast<int64_t>(row0 + r) * a.ldy + tn * kTcBN + 32 * (c - 1) +
+                                          8 * (lane & 7)) = o;
+            }
+            __syncwarp();
           }
         }
       } else if (EPI == kTcSwiglu) {
@@ -511,6 +559,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   tc_fence_before();
   if (PAIR) cluster_sync_all();            // neither CTA leaves while the other may still read its shared memory
   else __syncthreads();
+  if (EPI == kTcBf16 && threadIdx.x == 0) tp_signal(a.tp);   // all peer stores of this CTA were issued before the barrier
   if (warp == kMmaWarp) {
     tc_fence_after();
     if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
@@ -555,6 +604,7 @@ static int launch_tc_impl(const bf16* x, int64_t ldx, const bf16* w, int w_rows,
     attr_set = true;
   }
   const int tiles = a.tiles_m * a.tiles_n;
+  a.grid = tiles < sm_count ? tiles : sm_count;
   if (!PAIR)
     return mdb_launch(gemm_tc_kernel<EPI, PAIR>, dim3(tiles < sm_count ? tiles : sm_count), dim3(tc_threads(EPI)), kSmem,
                       st, map_x, map_w, a);
@@ -582,6 +632,7 @@ static int launch_tc_impl(const bf16* x, int64_t ldx, const bf16* w, int w_rows,
   }
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
   cfg.gridDim = dim3(2 * pairs);
+  a.grid = 2 * pairs;
   cfg.numAttrs = g_opt_pdl ? 2 : 1;
   return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<EPI, PAIR>, map_x, map_w, a) == cudaSuccess ? MDB_OK : MDB_ERR_CUDA;
 }

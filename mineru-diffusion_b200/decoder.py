@@ -313,9 +313,19 @@ class DecoderEngine:
             ops.gemm_splitk_partials_tp(x_in, w, ks, mine, theirs, signal_ptr, tag, self.tp_epoch)
             return ("tp", view, wait_ptr, ops.tp_grid_size(m, h, x_in.shape[1], ks), tag)
         ho = self.h_out[:m]
+        k = x_in.shape[1]
+        if (self.tp is not None and m <= self.tp.many_rows and k % 64 == 0 and h % 8 == 0
+                and ops.get_option(ops.OPT_STREAM_KERNEL) == 0):
+            # the all-reduce rides in the GEMM epilogue: every tile goes to the local output and, over NVLink,
+            # to the peer's landing buffer; the following norm adds the two
+            land, peer_ptr = self.tp.landing(which, m)
+            wait_ptr, signal_ptr = self.tp.flags(which)
+            tag = 2 * li + 1 + which
+            slots = ops.linear_tp_rows(x_in, w, ho, peer_ptr, signal_ptr, tag, self.tp_epoch)
+            return ("tp_rows", ho, land, wait_ptr, slots, tag)
         ops.linear(x_in, w, out=ho)
         if self.tp_size > 1:
-            # many-row steps (prefill) keep the reference's collective: bf16 partial outputs summed by NCCL
+            # shapes the tile kernel does not take keep the reference's collective: bf16 partial outputs summed by NCCL
             torch.distributed.all_reduce(ho)
         return ("bf16", ho)
 
@@ -325,6 +335,9 @@ class DecoderEngine:
         elif prev[0] == "tp":
             _, view, wait_ptr, count, tag = prev
             ops.add_rms_norm_tp(view, res, ln, eps, out, res, wait_ptr, count, tag, self.tp_epoch)
+        elif prev[0] == "tp_rows":
+            _, own, land, wait_ptr, count, tag = prev
+            ops.add_rms_norm_tp_rows(own, land, res, ln, eps, out, res, wait_ptr, count, tag, self.tp_epoch)
         else:
             ops.add_rms_norm(prev[1], res, ln, eps, out=out, residual_out=res)
 

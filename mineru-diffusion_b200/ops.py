@@ -448,6 +448,32 @@ def gemm_splitk_partials_tp(x: torch.Tensor, weight: torch.Tensor, ksplit: int, 
                                                       epoch.data_ptr(), _stream()), "mdb_gemm_splitk_partials_tp")
 
 
+def linear_tp_rows(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, peer_ptr: int, peer_flags_ptr: int,
+                   tag: int, epoch: torch.Tensor) -> int:
+    """Many-row x W^T stored into ``out`` and, over NVLink, into the peer's landing buffer at ``peer_ptr``
+    (same leading dimension as ``out``); then the peer's flag slots are raised.  Returns the number of
+    flag slots (= CTAs launched) the consumer has to wait for."""
+    import ctypes as C
+    m, k = x.shape
+    n = weight.shape[0]
+    grid = C.c_int(0)
+    _lib.check(_lib.lib().mdb_gemm_bf16_tp(x.data_ptr(), _rows(x, "x"), weight.data_ptr(), out.data_ptr(), peer_ptr,
+                                           _rows(out, "out"), m, n, k, peer_flags_ptr, tag, epoch.data_ptr(),
+                                           C.byref(grid), _stream()), "mdb_gemm_bf16_tp")
+    return int(grid.value)
+
+
+def add_rms_norm_tp_rows(x: torch.Tensor, x_peer: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float,
+                         out: torch.Tensor, residual_out: torch.Tensor, wait_flags_ptr: int, wait_count: int, tag: int,
+                         epoch: torch.Tensor) -> None:
+    """``add_rms_norm`` of bf16(x + x_peer) after the peer's flag slots show this launch's number."""
+    m, h = x.shape
+    _lib.check(_lib.lib().mdb_add_rmsnorm_tp_rows(x.data_ptr(), x_peer.data_ptr(), residual.data_ptr(),
+                                                  weight.data_ptr(), float(eps), out.data_ptr(), residual_out.data_ptr(),
+                                                  m, h, wait_flags_ptr, wait_count, tag, epoch.data_ptr(), _stream()),
+               "mdb_add_rmsnorm_tp_rows")
+
+
 def tp_grid_size(m: int, n: int, k: int, ksplit: int) -> int:
     return int(_lib.lib().mdb_tp_grid_size(m, n, k, ksplit))
 

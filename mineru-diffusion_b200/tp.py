@@ -73,7 +73,8 @@ def shard_weights(full, cfg: DecoderConfig, rank: int, world: int):
 
 class TensorParallelPair:
 
-    def __init__(self, rank: int, device, hidden: int, ks_o: int, ks_down: int, lm_ws_bytes: int, max_rows: int = 64):
+    def __init__(self, rank: int, device, hidden: int, ks_o: int, ks_down: int, lm_ws_bytes: int, max_rows: int = 64,
+                 many_rows: int = 0):
         if not dist.is_initialized() or dist.get_world_size() != 2:
             raise RuntimeError("TensorParallelPair needs an initialised process group of size 2")
         self.rank, self.peer_rank, self.device = rank, 1 - rank, torch.device(device)
@@ -82,7 +83,11 @@ class TensorParallelPair:
         self.off_o = 0
         self.off_down = _align(self.off_o + 2 * ks_o * max_rows * hidden * 4)
         self.off_lm = _align(self.off_down + 2 * ks_down * max_rows * hidden * 4)
-        self.off_flags = _align(self.off_lm + lm_ws_bytes)
+        # many-row steps: one landing buffer per exchange of a layer (o_proj, down_proj), [many_rows, hidden] bf16,
+        # that only the peer writes
+        self.many_rows = many_rows
+        self.off_land = _align(self.off_lm + lm_ws_bytes)
+        self.off_flags = _align(self.off_land + 2 * many_rows * hidden * 2)
         self.lm_ws_bytes = lm_ws_bytes
         self.nbytes = self.off_flags + 3 * FLAG_SLOTS * 4
         base = C.c_void_p()
@@ -113,6 +118,12 @@ class TensorParallelPair:
 
     def down_slices(self, m: int):
         return self._slices(self.off_down, self.ks_down, m)
+
+    def landing(self, which: int, m: int):
+        """(local [m, H] bf16 view the peer's GEMM stores into, the matching address in the peer's region)."""
+        off = self.off_land + which * self.many_rows * self.hidden * 2
+        view = self.local[off:off + m * self.hidden * 2].view(torch.bfloat16).view(m, self.hidden)
+        return view, self.peer_base + off
 
     def flags(self, which: int) -> tuple[int, int]:
         """(local slots the peer writes, slots in the peer's region this rank writes)."""

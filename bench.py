@@ -48,6 +48,7 @@ TEXT_IDS = 32
 NEW_TOKENS = 1024
 THRESHOLD = 0.9
 REQUESTS = 1
+TEMPERATURE = 1.0
 VISUAL_MAX = 4096      # upper end of the per-request visual row count when several requests run
 WEIGHT_SEED = 20260320
 
@@ -112,7 +113,7 @@ def make_request(pkg, dcfg, seed: int, device, visual_rows: int | None = None):
     visual = torch.randn(rows, dcfg.hidden_size, generator=g).to(torch.bfloat16)
     text = torch.randint(0, 151000, (TEXT_IDS,), generator=g).tolist()
     ids = [0] * rows + text                 # the visual positions' ids are never embedded
-    sp = pkg.SamplingParams(temperature=1.0, max_new_tokens=NEW_TOKENS, ignore_eos=True, dynamic_threshold=THRESHOLD)
+    sp = pkg.SamplingParams(temperature=TEMPERATURE, max_new_tokens=NEW_TOKENS, ignore_eos=True, dynamic_threshold=THRESHOLD)
     return pkg.Sequence(ids, sp, denoising_block_size=BLOCK, mask_token_id=151669,
                         inputs_embeds=visual.pin_memory() if device != "cpu" else visual)
 
@@ -375,10 +376,13 @@ def main():
                          "512 / N share, visual rows uniform in [512, 8192], --block and --threshold set the point)")
     ap.add_argument("--block", type=int, default=32, choices=[8, 16, 32, 64], help="denoising block size")
     ap.add_argument("--threshold", type=float, default=0.9, help="confidence threshold of the unmask rule")
+    ap.add_argument("--temperature", type=float, default=1.0,
+                    help="sampling temperature; with random weights only a low one (0.02) lets confidences pass the "
+                         "threshold, so that steps commit several tokens as they do on a trained model")
     ap.add_argument("--tp", type=int, default=1, choices=[1, 2], help="2: the two ranks form one tensor-parallel pair")
     args = ap.parse_args()
-    global VISUAL_ROWS, NEW_TOKENS, REQUESTS, BLOCK, THRESHOLD, VISUAL_MAX
-    BLOCK, THRESHOLD = args.block, args.threshold
+    global VISUAL_ROWS, NEW_TOKENS, REQUESTS, BLOCK, THRESHOLD, VISUAL_MAX, TEMPERATURE
+    BLOCK, THRESHOLD, TEMPERATURE = args.block, args.threshold, args.temperature
     if args.workload == "config5":
         NEW_TOKENS, REQUESTS, VISUAL_MAX = 2048, 64, 8192
     if args.workload == "config4":
@@ -426,6 +430,8 @@ def main():
     if args.workload == "config4":
         config["workload"] = ("config4: full decoder, 1 request, 4096 synthetic visual rows + 32 text ids, 4096 new "
                               "tokens, block 32, threshold 0.9, temperature 1.0")
+    if TEMPERATURE != 1.0:
+        config["workload"] = config["workload"].replace("temperature 1.0", f"temperature {TEMPERATURE}")
     if world > 1:
         torch.distributed.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
     res = run_ours(args, rank, world, local_rank)

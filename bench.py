@@ -137,7 +137,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         pages = (total_len + 255) // 256 + 1
     cfg = pkg.Config(max_num_batched_tokens=max(max_len, 16384 if nreq > 1 else 0), max_num_seqs=nreq,
                      max_model_len=max_len, enforce_eager=False, num_kvcache_blocks=pages, decoder_config=dcfg,
-                     tensor_parallel_size=args.tp, block_size=BLOCK)
+                     tensor_parallel_size=args.tp, block_size=BLOCK, fuse_commit_pass=getattr(args, "fuse_commit", False))
     # tensor-parallel pair: both ranks serve the same request with the same noise; replicas: one request each
     seed = 2 if args.tp == 2 else 2 + rank
     runner = pkg.ModelRunner(cfg, rank=rank if args.tp == 2 else 0, weight_seed=WEIGHT_SEED, noise="gumbel",
@@ -379,6 +379,9 @@ def main():
     ap.add_argument("--temperature", type=float, default=1.0,
                     help="sampling temperature; with random weights only a low one (0.02) lets confidences pass the "
                          "threshold, so that steps commit several tokens as they do on a trained model")
+    ap.add_argument("--fuse-commit", action="store_true",
+                    help="Config.fuse_commit_pass: a block's commit pass also runs the next block's first denoising "
+                         "pass (not the reference's schedule; off for the headline number)")
     ap.add_argument("--tp", type=int, default=1, choices=[1, 2], help="2: the two ranks form one tensor-parallel pair")
     args = ap.parse_args()
     global VISUAL_ROWS, NEW_TOKENS, REQUESTS, BLOCK, THRESHOLD, VISUAL_MAX, TEMPERATURE
@@ -430,6 +433,8 @@ def main():
     if args.workload == "config4":
         config["workload"] = ("config4: full decoder, 1 request, 4096 synthetic visual rows + 32 text ids, 4096 new "
                               "tokens, block 32, threshold 0.9, temperature 1.0")
+    if args.fuse_commit:
+        config["fuse_commit_pass"] = True
     if TEMPERATURE != 1.0:
         config["workload"] = config["workload"].replace("temperature 1.0", f"temperature {TEMPERATURE}")
     if world > 1:

@@ -57,6 +57,10 @@ class Config:
     mask_token_id: int = 151669
     block_size: int = 32
     decoder_config: DecoderConfig | None = None
+    # Not in the reference: a request whose block is complete runs the pass that writes the block's final K/V
+    # and, in the same step, the first denoising pass of its next block (one pass per block saved; the tokens
+    # are the ones the two separate passes would produce from the same noise).  Off: the reference's schedule.
+    fuse_commit_pass: bool = False
 
     def __post_init__(self):
         if self.kvcache_block_size % 256 != 0:

@@ -72,6 +72,22 @@ class _StepInputs:
         )
 
 
+class _NextBlock:
+    """Stand-in for the block a request opens after the one it is committing: a fresh masked block at the
+    positions behind the committed one, on the same pages (``Config.fuse_commit_pass``).  Quacks like a
+    Sequence for the builders of the step inputs."""
+    __slots__ = ("seq", "current_denoising_block", "block_table", "temperature")
+
+    def __init__(self, seq: Sequence):
+        self.seq = seq
+        self.current_denoising_block = seq._fresh_block()
+        self.block_table = seq.block_table
+        self.temperature = seq.temperature
+
+    def __len__(self):
+        return len(self.seq) + self.seq.denoising_block_size
+
+
 class ModelRunner:
 
     def __init__(self, config: Config, rank: int = 0, event=None, weights: DecoderWeights | None = None,
@@ -120,7 +136,9 @@ class ModelRunner:
         self.step_index = 0
         self.allocate_kv_cache()
         b = self.block_size
-        self.max_bs = min(config.max_num_seqs, 512)
+        self.fuse_commit_pass = bool(getattr(config, "fuse_commit_pass", False))
+        # with fused commit passes a request can stand in a step twice (the block it commits + the one it opens)
+        self.max_bs = min(config.max_num_seqs * (2 if self.fuse_commit_pass else 1), 512)
         max_tokens = max(config.max_num_batched_tokens + config.max_num_seqs * b, self.max_bs * b)
         max_tokens = min(max_tokens, config.max_model_len * config.max_num_seqs + config.max_num_seqs * b)
         self.engine = DecoderEngine(self.dcfg, self.weights, self.kv_cache, max_tokens, self.max_bs, b,
@@ -342,6 +360,12 @@ class ModelRunner:
         if is_prefill:
             hidden = self.run_model_prefill(seqs)
         else:
+            if self.fuse_commit_pass:
+                extra = [_NextBlock(seq) for seq in seqs if seq.is_caching and self._next_block_ready(seq)]
+                extra = extra[:self.max_bs - bs]
+                if extra:
+                    seqs = list(seqs) + extra
+                    bs = len(seqs)
             self.run_model_decode(seqs)
             hidden = self.engine.final[:bs * b]     # final-norm rows of the step (graph replays write here too)
         with torch.inference_mode():
@@ -375,6 +399,9 @@ class ModelRunner:
         moved = h_transfer != 0
         moved_any = moved.any(axis=1)
         for i, seq in enumerate(seqs):
+            if type(seq) is _NextBlock:     # applied by Scheduler.postprocess once the block before it is appended
+                seq.seq.pending_first_step = (rows[i], moved[i].copy() if moved_any[i] else None)
+                continue
             seq.current_denoising_block = rows[i]
             if moved_any[i]:
                 seq.current_step_map.numpy()[moved[i]] = seq.current_denoise_step
@@ -382,6 +409,18 @@ class ModelRunner:
         self._last_rows, self._last_blocks = rows, blocks.numpy()   # shares memory with the rows
         self.step_index += 1
         return int(h_counts.sum())
+
+    def _next_block_ready(self, seq: Sequence) -> bool:
+        """True when the request being committed goes on to another block (the finishing rule of
+        ``Scheduler.postprocess``) and already holds the pages that block needs."""
+        b = self.block_size
+        if seq.num_completion_tokens + b >= seq.max_new_tokens:
+            return False
+        if not seq.ignore_eos:
+            block = seq.current_denoising_block.numpy()
+            if any(bool((block == t).any()) for t in seq.sampling_params.stop_token_ids):
+                return False
+        return seq.num_tokens + 2 * b <= Sequence.kvcache_block_size * len(seq.block_table)
 
     def launches_per_decode_step(self, bs: int = 1) -> int:
         """Kernels of libmdb200 launched by one decode-form step: row gather,

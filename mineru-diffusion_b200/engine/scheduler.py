@@ -96,3 +96,13 @@ class Scheduler:
                 self.running.remove(seq)
             else:
                 seq.status = SequenceStatus.RUNNING
+            pending, seq.pending_first_step = getattr(seq, "pending_first_step", None), None
+            if pending is not None and seq.status is SequenceStatus.RUNNING:
+                # the new block's first denoising pass already ran, together with the commit pass
+                block, moved = pending
+                seq.current_denoising_block = block
+                if moved is not None:
+                    seq.current_step_map.numpy()[moved] = seq.current_denoise_step
+                seq.current_denoise_step += 1
+                if not bool((block.numpy() == seq.mask_token_id).any()):
+                    seq.status = SequenceStatus.CACHING

@@ -55,6 +55,9 @@ class Sequence:
         # never-set entries are meaningless in the reference (torch.empty); zero here
         self.current_step_map = torch.zeros(denoising_block_size, dtype=torch.int32)
         self.current_denoise_step = 0
+        # (block ids, moved positions) of the next block's first denoising pass when it ran together with this
+        # block's commit pass (Config.fuse_commit_pass); applied by Scheduler.postprocess after append_block
+        self.pending_first_step = None
 
     def _fresh_block(self) -> torch.Tensor:
         return torch.full((self.denoising_block_size,), self.mask_token_id, dtype=torch.int64)

@@ -328,3 +328,49 @@ def test_engine_generates_and_frees_pages(mdb):
         assert len(toks) == new and 500 not in toks and len(step_map) == new
     assert len(engine.scheduler.block_manager.free_block_ids) == 10
     assert mdb._lib.device_status(clear=True) == 0
+
+
+@pytest.mark.parametrize("eager", [True, False])
+def test_fused_commit_pass(mdb, eager):
+    """Config.fuse_commit_pass: the pass that writes a finished block's K/V also runs the first denoising pass of
+    the next block.  One request, no sampling noise, low temperature (several tokens per step): the rows of a
+    request do not depend on how many other rows share the step, so the tokens must be the same as with the
+    reference's schedule, in fewer steps.  Several requests: everything completes and pages come back."""
+    dcfg = _tiny_cfg(mdb, vocab=1024, layers=2, hkv=2)
+    weights = orc.make_weights(_oracle_cfg(dcfg), seed=11)
+    gen = torch.Generator().manual_seed(4)
+    prompt = torch.randint(0, 490, (120,), generator=gen).tolist()
+    results = {}
+    for fuse in (False, True):
+        cfg = mdb.Config(max_num_batched_tokens=2048, max_num_seqs=1, max_model_len=1024, enforce_eager=eager,
+                         num_kvcache_blocks=4, decoder_config=dcfg, mask_token_id=500, fuse_commit_pass=fuse)
+        runner = mdb.ModelRunner(cfg, weights=mdb.DecoderWeights.from_reference_layout(weights, DEV), noise="none")
+        engine = mdb.LLMEngine(cfg, runner)
+        sp = mdb.SamplingParams(temperature=0.02, max_new_tokens=256, ignore_eos=True, dynamic_threshold=0.9)
+        seq = mdb.Sequence(list(prompt), sp, denoising_block_size=32, mask_token_id=500)
+        done, _ = engine.generate([seq])
+        results[fuse] = (done[seq.seq_id][0], engine.num_decode_steps)
+        assert len(engine.scheduler.block_manager.free_block_ids) == 4
+        runner.exit()
+    (plain_tokens, plain_steps), (fused_tokens, fused_steps) = results[False], results[True]
+    assert len(plain_tokens) == 256 and 500 not in plain_tokens
+    assert fused_tokens == plain_tokens
+    # 8 blocks; the commit pass of every block but the last and the page-crossing ones rides with the next block
+    assert fused_steps <= plain_steps - 5, (plain_steps, fused_steps)
+    print(f"fused commit pass (eager={eager}): {plain_steps} -> {fused_steps} decode steps for 256 tokens")
+
+    cfg = mdb.Config(max_num_batched_tokens=2048, max_num_seqs=3, max_model_len=1024, enforce_eager=eager,
+                     num_kvcache_blocks=8, decoder_config=dcfg, mask_token_id=500, fuse_commit_pass=True)
+    runner = mdb.ModelRunner(cfg, weights=mdb.DecoderWeights.from_reference_layout(weights, DEV), noise="gumbel")
+    engine = mdb.LLMEngine(cfg, runner)
+    seqs = []
+    for plen, new in [(100, 96), (300, 64), (31, 128), (200, 64)]:
+        sp = mdb.SamplingParams(temperature=0.05, max_new_tokens=new, ignore_eos=True)
+        seqs.append(mdb.Sequence(torch.randint(0, 490, (plen,), generator=gen).tolist(), sp, denoising_block_size=32,
+                                 mask_token_id=500))
+    done, _ = engine.generate(seqs)
+    for seq, new in zip(seqs, (96, 64, 128, 64)):
+        toks, step_map = done[seq.seq_id]
+        assert len(toks) == new and 500 not in toks and len(step_map) == new
+    assert len(engine.scheduler.block_manager.free_block_ids) == 8
+    assert mdb._lib.device_status(clear=True) == 0

@@ -374,3 +374,35 @@ def test_fused_commit_pass(mdb, eager):
         assert len(toks) == new and 500 not in toks and len(step_map) == new
     assert len(engine.scheduler.block_manager.free_block_ids) == 8
     assert mdb._lib.device_status(clear=True) == 0
+
+
+def test_reused_step_inputs_change_nothing(mdb):
+    """While the same requests stay on the same blocks the runner rewrites only the token ids of the pinned step
+    inputs (taken from the previous step's result copy).  Forcing the full rebuild every step must give the same
+    tokens and step maps."""
+    dcfg = _tiny_cfg(mdb, vocab=1024, layers=2, hkv=2)
+    weights = orc.make_weights(_oracle_cfg(dcfg), seed=13)
+    outs = []
+    for force_rebuild in (False, True):
+        cfg, runner = _make_runner(mdb, dcfg, weights, pages=10, eager=False, noise="gumbel", max_seqs=4)
+        if force_rebuild:
+            plain = runner.prepare_decode
+
+            def rebuild(seqs, copy=True, _plain=plain, _runner=runner):
+                _runner._decode_key, _runner._last_rows = None, None
+                return _plain(seqs, copy)
+
+            runner.prepare_decode = rebuild
+        engine = mdb.LLMEngine(cfg, runner)
+        gen = torch.Generator().manual_seed(5)
+        seqs = []
+        for plen, new in [(100, 64), (300, 96), (31, 32), (250, 64), (64, 64)]:
+            sp = mdb.SamplingParams(temperature=0.05, max_new_tokens=new, ignore_eos=True)
+            seqs.append(mdb.Sequence(torch.randint(0, 490, (plen,), generator=gen).tolist(), sp,
+                                     denoising_block_size=32, mask_token_id=500))
+        done, _ = engine.generate(seqs)
+        outs.append([done[s.seq_id] for s in seqs])
+        runner.exit()
+    for (tok_a, map_a), (tok_b, map_b) in zip(*outs):
+        assert tok_a == tok_b and map_a == map_b
+    assert mdb._lib.device_status(clear=True) == 0

@@ -360,6 +360,15 @@ int mdb_lmhead_sample_tp(const void* hidden, int64_t ld_hidden, const void* w, i
                          int64_t workspace_bytes, int tile_begin, int tile_count, uint32_t* peer_flags,
                          const uint32_t* wait_flags, int wait_count, uint32_t tag, const uint32_t* epoch,
                          int32_t* x0_out, float* conf_out, mdb_stream_t stream);
+/* More than 64 rows: the same call runs the tcgen05 tile GEMM over the rank's
+ * columns (tile_begin even; the shard ends on a multiple of 256 columns or at
+ * the end of the vocabulary; no explicit noise tensor), one record per
+ * 256-column tile, mirrored into the peer's workspace.  The workspace needs
+ * mdb_lmhead_tp_workspace_bytes(m, vocab) bytes; the number of flag slots a
+ * shard of `cols` columns raises (the peer's wait_count) is
+ * mdb_lmhead_tp_slots(m, cols). */
+int64_t mdb_lmhead_tp_workspace_bytes(int m, int vocab);
+int mdb_lmhead_tp_slots(int m, int cols);
 
 #ifdef __cplusplus
 }

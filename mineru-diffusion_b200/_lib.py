@@ -79,6 +79,8 @@ SIGNATURES = {
     "mdb_gemm_splitk_partials_tp": (_i, [_p, _i64, _p, _p, _p, _i, _i, _i, _i, _p, _u32, _p, _p]),
     "mdb_tp_grid_size": (_i, [_i, _i, _i, _i]),
     "mdb_add_rmsnorm_tp": (_i, [_p, _p, _i, _p, _p, _f, _p, _p, _i, _i, _p, _i, _u32, _p, _p]),
+    "mdb_lmhead_tp_workspace_bytes": (_i64, [_i, _i]),
+    "mdb_lmhead_tp_slots": (_i, [_i, _i]),
     "mdb_gemm_bf16_tp": (_i, [_p, _i64, _p, _p, _p, _i64, _i, _i, _i, _p, _u32, _p, C.POINTER(C.c_int), _p]),
     "mdb_add_rmsnorm_tp_rows": (_i, [_p, _p, _p, _p, _f, _p, _p, _i, _i, _p, _i, _u32, _p, _p]),
     "mdb_lmhead_sample_tp": (_i, [_p, _i64, _p, _i, _i, _i, _p, _i, _i, _p, _u32, _u32, _p, _p, _p, _i64, _i, _i, _p,

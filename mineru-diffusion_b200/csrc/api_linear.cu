@@ -381,11 +381,48 @@ int mdb_lmhead_sample_tp(const void* hidden, int64_t ld_hidden, const void* w, i
                          int64_t workspace_bytes, int tile_begin, int tile_count, uint32_t* peer_flags,
                          const uint32_t* wait_flags, int wait_count, uint32_t tag, const uint32_t* epoch,
                          int32_t* x0_out, float* conf_out, mdb_stream_t stream) {
-  MDB_REQUIRE(m >= 1 && m <= 64 && vocab > 0 && h > 0 && block > 0, MDB_ERR_ARG);
+  MDB_REQUIRE(m >= 1 && vocab > 0 && h > 0 && block > 0, MDB_ERR_ARG);
   MDB_REQUIRE(hidden && w && temperatures && x0_out && conf_out && workspace && peer_workspace, MDB_ERR_ARG);
   MDB_REQUIRE(peer_flags && wait_flags && epoch && wait_count > 0 && tag >= 1 && tag <= 255, MDB_ERR_ARG);
   MDB_REQUIRE(m % block == 0 && ld_hidden >= h, MDB_ERR_ARG);
   MDB_REQUIRE(noise_mode >= 0 && noise_mode <= 2 && (noise_mode != 1 || noise != nullptr), MDB_ERR_ARG);
+  if (m > 64) {
+    // many rows: the tile GEMM over this rank's columns [128 tile_begin, 128 (tile_begin + tile_count)) of the
+    // vocabulary, one record per 256-column tile; the shard must start on a 256-column boundary and end on one
+    // or at the end of the vocabulary
+    MDB_REQUIRE(noise_mode != 1 && g_opt_stream_kernel == 0 && vocab % 128 == 0, MDB_ERR_UNSUPPORTED);
+    MDB_REQUIRE(tile_begin >= 0 && tile_count >= 1 && tile_begin % 2 == 0, MDB_ERR_ARG);
+    const int64_t col_begin = static_cast<int64_t>(tile_begin) * 128;
+    const int64_t col_end = col_begin + static_cast<int64_t>(tile_count) * 128;
+    MDB_REQUIRE(col_end <= vocab && (col_end == vocab || col_end % kTcBN == 0), MDB_ERR_ARG);
+    const int cols = static_cast<int>(col_end - col_begin);
+    MDB_REQUIRE(tc_supported(kTcLmHead, m, cols, h, ld_hidden, 0), MDB_ERR_UNSUPPORTED);
+    const LmHeadLayout lay = lmhead_layout(m, vocab);
+    MDB_REQUIRE(workspace_bytes >= lay.off_logits, MDB_ERR_WORKSPACE);
+    unsigned char* ws = static_cast<unsigned char*>(workspace);
+    unsigned char* pws = static_cast<unsigned char*>(peer_workspace);
+    const int64_t rec0 = col_begin / kTcBN * m;            // first record of the shard
+    TcArgs a = {};
+    a.m = m; a.n = cols; a.k = h;
+    a.temperatures = temperatures;
+    a.block = block;
+    a.noise_mode = noise_mode;
+    a.seed = seed; a.step = step;
+    a.step_dev = step_dev;
+    a.part_f = reinterpret_cast<float4*>(ws) + rec0;
+    a.part_i = reinterpret_cast<int*>(ws + lay.off_i) + rec0;
+    a.peer_part_f = reinterpret_cast<float4*>(pws) + rec0;
+    a.peer_part_i = reinterpret_cast<int*>(pws + lay.off_i) + rec0;
+    a.col_base = static_cast<int>(col_begin);
+    a.tp = TpSignal{peer_flags, nullptr, 0, tag, epoch};
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bf16* w_shard = static_cast<const bf16*>(w) + col_begin * h;
+    int rc = launch_tc_impl<kTcLmHead, false>(static_cast<const bf16*>(hidden), ld_hidden, w_shard, cols, a, st);
+    if (rc != MDB_OK) return rc;
+    const TpSignal wait = {nullptr, wait_flags, wait_count, tag, epoch};
+    return finalize_sampler(reinterpret_cast<float4*>(ws), reinterpret_cast<int*>(ws + lay.off_i),
+                            static_cast<int>(lay.nparts), m, x0_out, conf_out, st, wait);
+  }
   MDB_REQUIRE(ws_supported(kWsLmHead, m, vocab, h, ld_hidden), MDB_ERR_UNSUPPORTED);
   const int tiles_total = vocab / kWsTileRows;
   MDB_REQUIRE(tile_begin >= 0 && tile_count >= 1 && tile_begin + tile_count <= tiles_total, MDB_ERR_ARG);
@@ -413,6 +450,22 @@ int mdb_lmhead_sample_tp(const void* hidden, int64_t ld_hidden, const void* w, i
   if (rc != MDB_OK) return rc;
   const TpSignal wait = {nullptr, wait_flags, wait_count, tag, epoch};
   return finalize_sampler(a.part_f, a.part_i, tiles_total, m, x0_out, conf_out, st, wait);
+}
+
+int64_t mdb_lmhead_tp_workspace_bytes(int m, int vocab) {
+  if (m <= 0 || vocab <= 0) return 0;
+  const LmHeadLayout lay = lmhead_layout(m, vocab);
+  return m <= 64 ? lay.total : lay.off_logits;     // records only: the pair never materialises logits
+}
+
+int mdb_lmhead_tp_slots(int m, int cols) {
+  if (m <= 64 || cols <= 0) return 0;
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (sms <= 0) sms = 148;
+  const int64_t tiles = static_cast<int64_t>((m + kTcBM - 1) / kTcBM) * ((cols + kTcBN - 1) / kTcBN);
+  return static_cast<int>(tiles < sms ? tiles : sms);
 }
 
 }  // extern "C"

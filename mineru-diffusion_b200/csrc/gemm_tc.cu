@@ -85,6 +85,11 @@ struct TcArgs {
   // leading dimension), then the CTA raises its flag slot there (all null / zero on one GPU)
   bf16* y_peer;
   TpSignal tp;
+  // LM head over a vocabulary shard (the weight pointer and n describe the shard): id of its first column, and
+  // the peer's record arrays, which receive a copy of every record
+  int col_base;
+  float4* peer_part_f;
+  int* peer_part_i;
   int grid;                    // CTAs launched (set by the launcher; the peer waits for that many flags)
 };
 
@@ -515,13 +520,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           if (a.noise_mode == 2) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              const float noisy = v[i] + gumbel_from_key(key, col0 + i);   // -inf stays -inf
-              if (noisy > bv) { bv = noisy; bl = v[i]; bi = col0 + i; }    // ascending columns: first maximum kept
+              const float noisy = v[i] + gumbel_from_key(key, a.col_base + col0 + i);   // -inf stays -inf
+              if (noisy > bv) { bv = noisy; bl = v[i]; bi = a.col_base + col0 + i; }    // ascending columns: first maximum kept
             }
           } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i)
-              if (v[i] > bv) { bv = v[i]; bl = v[i]; bi = col0 + i; }
+              if (v[i] > bv) { bv = v[i]; bl = v[i]; bi = a.col_base + col0 + i; }
           }
         }
         // the four warps of a quarter merge their records through shared memory (two buffers, one barrier per tile)
@@ -543,6 +548,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           if (live) {
             a.part_f[static_cast<int64_t>(tn) * a.m + row] = make_float4(r.mx, r.se, r.bv, r.bl);
             a.part_i[static_cast<int64_t>(tn) * a.m + row] = r.bi;
+            if (a.peer_part_f != nullptr) {      // consecutive rows: 512 bytes per warp over NVLink
+              a.peer_part_f[static_cast<int64_t>(tn) * a.m + row] = make_float4(r.mx, r.se, r.bv, r.bl);
+              a.peer_part_i[static_cast<int64_t>(tn) * a.m + row] = r.bi;
+            }
           }
         }
         ++acc_phase_tile;
@@ -559,7 +568,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   tc_fence_before();
   if (PAIR) cluster_sync_all();            // neither CTA leaves while the other may still read its shared memory
   else __syncthreads();
-  if (EPI == kTcBf16 && threadIdx.x == 0) tp_signal(a.tp);   // all peer stores of this CTA were issued before the barrier
+  if ((EPI == kTcBf16 || EPI == kTcLmHead) && threadIdx.x == 0) tp_signal(a.tp);   // all peer stores of this CTA were issued before the barrier
   if (warp == kMmaWarp) {
     tc_fence_after();
     if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");

@@ -350,12 +350,34 @@ class DecoderEngine:
             return ops.lm_head_sample(rows, self.w.lm_head, temperatures, self.block_size, noise=noise, seed=seed,
                                       step=step, step_dev=step_dev, workspace=self.lm_ws, x0=self.x0[:m],
                                       conf=self.conf[:m])
+        lib = ops._lib.lib()
+        ws, peer_ws = self.tp.lm_workspace()
+        wait_ptr, signal_ptr = self.tp.flags(2)
+        tag = 2 * len(self.w.layers) + 1
         if m > SKINNY_MAX_ROWS:
-            # Many-row steps: both ranks hold the whole LM head and bit-identical hidden rows, so each scans the
-            # full vocabulary itself and reaches the same decisions with nothing exchanged.
-            return ops.lm_head_sample(rows, self.w.lm_head, temperatures, self.block_size, noise=noise, seed=seed,
-                                      step=step, step_dev=step_dev, workspace=self.lm_ws, x0=self.x0[:m],
-                                      conf=self.conf[:m])
+            # Many-row steps: the tile GEMM over half of the 256-column vocabulary tiles per rank, one sampler
+            # record per tile mirrored into the peer's workspace; logits are never gathered.
+            vocab = self.cfg.vocab_size
+            can_split = (noise is None and vocab % 128 == 0 and ops.get_option(ops.OPT_STREAM_KERNEL) == 0
+                         and ws.numel() >= lib.mdb_lmhead_tp_workspace_bytes(m, vocab))
+            if not can_split:
+                # both ranks hold the whole LM head and bit-identical hidden rows: each scans all of it
+                return ops.lm_head_sample(rows, self.w.lm_head, temperatures, self.block_size, noise=noise, seed=seed,
+                                          step=step, step_dev=step_dev, workspace=self.lm_ws, x0=self.x0[:m],
+                                          conf=self.conf[:m])
+            tiles128 = vocab // 128
+            first = 2 * ((-(-vocab // 256) + 1) // 2)            # rank 0's 128-column tiles: whole 256-column tiles
+            first = min(first, tiles128)
+            begin, count = (0, first) if self.tp_rank == 0 else (first, tiles128 - first)
+            peer_cols = (tiles128 - first if self.tp_rank == 0 else first) * 128
+            if count == 0 or peer_cols == 0:
+                return ops.lm_head_sample(rows, self.w.lm_head, temperatures, self.block_size, noise=noise, seed=seed,
+                                          step=step, step_dev=step_dev, workspace=self.lm_ws, x0=self.x0[:m],
+                                          conf=self.conf[:m])
+            return ops.lm_head_sample_tp(rows, self.w.lm_head, temperatures, self.block_size, ws, peer_ws, begin, count,
+                                         signal_ptr, wait_ptr, lib.mdb_lmhead_tp_slots(m, peer_cols), tag,
+                                         self.tp_epoch, self.x0[:m], self.conf[:m], noise=None, seed=seed, step=step,
+                                         step_dev=step_dev)
         # vocabulary tiles (128 rows) split between the two ranks; records are exchanged, never logits
         tiles = self.cfg.vocab_size // 128
         first = (tiles + 1) // 2

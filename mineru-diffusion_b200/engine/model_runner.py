@@ -153,7 +153,9 @@ class ModelRunner:
             from .. import tp as tp_mod
             self.tp_pair = tp_mod.TensorParallelPair(rank, self.device, self.dcfg.hidden_size, self.engine.ks_o,
                                                      self.engine.ks_down,
-                                                     ops.lmhead_workspace_bytes(64, self.dcfg.vocab_size),
+                                                     max(ops.lmhead_workspace_bytes(64, self.dcfg.vocab_size),
+                                                         int(ops._lib.lib().mdb_lmhead_tp_workspace_bytes(
+                                                             self.max_bs * b, self.dcfg.vocab_size))),
                                                      many_rows=max_tokens)
             # word 1 of the step slot is the flag epoch: step index + 1, so that real steps never reuse the
             # sequence numbers of the warm-up launches made while graphs are captured (epoch 0)

@@ -138,3 +138,70 @@ def test_model_runner_needs_cuda(mdb):
         pytest.skip("CUDA present")
     with pytest.raises(RuntimeError):
         mdb.ModelRunner(mdb.Config())
+
+
+def _running_seqs(mdb, n, block=32, mask=1000):
+    from types import SimpleNamespace
+    cfg = SimpleNamespace(max_num_seqs=16, max_num_batched_tokens=8192, eos=-1, num_kvcache_blocks=64,
+                          kvcache_block_size=256)
+    sched = mdb.Scheduler(cfg)
+    gen = torch.Generator().manual_seed(3)
+    for i in range(n):
+        sp = mdb.SamplingParams(temperature=1.0, max_new_tokens=96, ignore_eos=True, stop_token_ids=[])
+        sched.add(mdb.Sequence(torch.randint(0, 100, (20 + i,), generator=gen).tolist(), sp,
+                               denoising_block_size=block, mask_token_id=mask))
+    seqs, is_prefill = sched.schedule()
+    assert is_prefill and len(seqs) == n
+    for s in seqs:                         # what a prefill step leaves behind
+        s.num_cached_tokens = len(s)
+    return sched, seqs
+
+
+def test_postprocess_batch_check_equals_per_request(mdb):
+    """Scheduler.postprocess (NV/engine/scheduler.py:65-82) decides RUNNING -> CACHING per request from "any
+    mask token left"; batches of more than four requests make that decision with one comparison."""
+    for n in (3, 9):
+        sched, seqs = _running_seqs(mdb, n)
+        for i, s in enumerate(seqs):
+            s.current_denoising_block = torch.full((32,), 7, dtype=torch.int64)
+            if i % 3 != 0:
+                s.current_denoising_block[5 + i] = 1000
+        sched.postprocess(seqs)
+        for i, s in enumerate(seqs):
+            assert s.is_caching == (i % 3 == 0), (n, i)
+        # the caching pass of the finished ones: block appended, a fresh masked block opened
+        lens = [len(s) for s in seqs]
+        sched.postprocess(seqs)
+        for i, s in enumerate(seqs):
+            if i % 3 == 0:
+                assert len(s) == lens[i] + 32 and not s.is_caching
+                assert bool((s.current_denoising_block == 1000).all())
+            else:
+                assert len(s) == lens[i]
+
+
+def test_pending_first_step_applied_after_append(mdb):
+    """Config.fuse_commit_pass: the result of the next block's first denoising pass, left on the request by the
+    runner, becomes the state of the block opened by append_block; a block without masks goes straight to
+    its own commit pass."""
+    sched, seqs = _running_seqs(mdb, 2)
+    a, b = seqs
+    for s in seqs:
+        s.current_denoising_block = torch.full((32,), 7, dtype=torch.int64)
+    sched.postprocess(seqs)
+    assert a.is_caching and b.is_caching
+    first = torch.full((32,), 1000, dtype=torch.int64)
+    first[3] = 55
+    moved = np.zeros(32, dtype=bool)
+    moved[3] = True
+    a.pending_first_step = (first, moved)
+    done = torch.arange(32, dtype=torch.int64)
+    b.pending_first_step = (done, np.ones(32, dtype=bool))
+    step_a, step_b = a.current_denoise_step, b.current_denoise_step
+    sched.postprocess(seqs)
+    assert a.pending_first_step is None and b.pending_first_step is None
+    assert torch.equal(a.current_denoising_block, first) and not a.is_caching
+    assert a.current_denoise_step == step_a + 1 and int(a.current_step_map[3]) == step_a
+    assert torch.equal(b.current_denoising_block, done) and b.is_caching
+    assert b.current_denoise_step == step_b + 1
+    assert a.token_ids[-32:] == [7] * 32 and b.token_ids[-32:] == [7] * 32

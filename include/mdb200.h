@@ -90,7 +90,9 @@ int mdb_kv_commit(const void* key, int64_t key_stride, const void* value, int64_
  * caches: [num_pages, 256, hkv, 128] bf16; block_table: [bs, table_stride]
  * int32 (-1 padded); ctx_lens: [bs] int32, 0 makes the request a no-op (its
  * output rows are zeroed).  Every query row sees keys [0, ctx).  The key range
- * of each request is cut into nsplit parts processed by different CTAs;
+ * of each request is cut into at most nsplit parts processed by different
+ * CTAs (equal shares of its context, rounded up to whole key tiles and never
+ * shorter than 256 keys, so a short context uses fewer parts than asked for);
  * nsplit > 1 needs the workspace. */
 int64_t mdb_attn_paged_workspace_bytes(int bs, int block, int hq, int nsplit);
 int mdb_attn_block_paged(const void* q, const void* k_cache, const void* v_cache, void* out,

@@ -165,7 +165,8 @@ class ModelRunner:
         self.res_dev = torch.zeros(self.max_bs * (9 * b + 4), dtype=torch.uint8, device=self.device)
         self.res_host = torch.zeros(self.max_bs * (9 * b + 4), dtype=torch.uint8, pin_memory=True)
         self._res_views: dict[int, tuple] = {}
-        self._decode_key = None       # requests and lengths the pinned step inputs were last built for
+        self._decode_key = None       # lengths and page counts the pinned step inputs were last built for
+        self._decode_seqs: list = []  # ... and the requests themselves
         self._last_rows, self._last_blocks = None, None   # blocks handed to the requests after the last step
         self._decode_max_ctx = 0
         self.graphs: dict[int, tuple[torch.cuda.CUDAGraph, int]] = {}
@@ -239,8 +240,11 @@ class ModelRunner:
         token ids and the step counter change, so everything else is left as the last step wrote it."""
         b, bs = self.block_size, len(seqs)
         hn = self.hn
-        key = (tuple(map(id, seqs)), tuple(map(len, seqs)), tuple(len(seq.block_table) for seq in seqs))
-        if key == self._decode_key:
+        # The cached inputs belong to these very objects (kept referenced, so that their identity cannot pass to
+        # another request), at these lengths, holding this many pages.
+        key = (tuple(map(len, seqs)), tuple(len(seq.block_table) for seq in seqs))
+        held = self._decode_seqs
+        if key == self._decode_key and len(held) == bs and all(a is b for a, b in zip(seqs, held)):
             ids, rows = hn["ids"], self._last_rows
             if rows is not None and len(rows) == bs:
                 # the blocks handed out after the last step, in one copy; a request that has started a new
@@ -266,7 +270,7 @@ class ModelRunner:
             hn["tab"][:bs, :width] = inp["block_tables"]
             for i, seq in enumerate(seqs):
                 hn["temp"][i] = seq.temperature
-            self._decode_key = key
+            self._decode_key, self._decode_seqs = key, list(seqs)
             self._decode_max_ctx = int(inp["context_lens"].max())
         hn["step"][0] = self.step_index
         hn["step"][1] = self.step_index + 1

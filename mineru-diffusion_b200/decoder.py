@@ -365,11 +365,8 @@ class DecoderEngine:
                 return ops.lm_head_sample(rows, self.w.lm_head, temperatures, self.block_size, noise=noise, seed=seed,
                                           step=step, step_dev=step_dev, workspace=self.lm_ws, x0=self.x0[:m],
                                           conf=self.conf[:m])
-            tiles128 = vocab // 128
-            first = 2 * ((-(-vocab // 256) + 1) // 2)            # rank 0's 128-column tiles: whole 256-column tiles
-            first = min(first, tiles128)
-            begin, count = (0, first) if self.tp_rank == 0 else (first, tiles128 - first)
-            peer_cols = (tiles128 - first if self.tp_rank == 0 else first) * 128
+            from .tp import lm_head_split
+            begin, count, peer_cols = lm_head_split(vocab, self.tp_rank, many_rows=True)
             if count == 0 or peer_cols == 0:
                 return ops.lm_head_sample(rows, self.w.lm_head, temperatures, self.block_size, noise=noise, seed=seed,
                                           step=step, step_dev=step_dev, workspace=self.lm_ws, x0=self.x0[:m],

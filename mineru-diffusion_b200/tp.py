@@ -71,6 +71,20 @@ def shard_weights(full, cfg: DecoderConfig, rank: int, world: int):
     return DecoderWeights(full.embed, layers, full.final_ln, full.lm_head)
 
 
+def lm_head_split(vocab: int, rank: int, many_rows: bool) -> tuple[int, int, int]:
+    """Share of the LM head a rank of the pair scans, in 128-column tiles of the vocabulary:
+    (first tile, tiles, columns the peer scans).  Short steps (at most 64 rows) split the tiles evenly; steps of
+    more rows run a kernel whose records cover 256 columns, so rank 0's share ends on a 256-column boundary and
+    rank 1 takes the rest up to the end of the vocabulary.  A share can be empty for a tiny vocabulary."""
+    tiles = vocab // 128
+    if many_rows:
+        first = min(2 * ((-(-vocab // 256) + 1) // 2), tiles)
+    else:
+        first = (tiles + 1) // 2
+    begin, count = (0, first) if rank == 0 else (first, tiles - first)
+    return begin, count, (tiles - count) * 128
+
+
 class TensorParallelPair:
 
     def __init__(self, rank: int, device, hidden: int, ks_o: int, ks_down: int, lm_ws_bytes: int, max_rows: int = 64,

@@ -205,3 +205,20 @@ def test_pending_first_step_applied_after_append(mdb):
     assert torch.equal(b.current_denoising_block, done) and b.is_caching
     assert b.current_denoise_step == step_b + 1
     assert a.token_ids[-32:] == [7] * 32 and b.token_ids[-32:] == [7] * 32
+
+
+def test_lm_head_split_covers_the_vocabulary():
+    """The two ranks of a tensor-parallel pair scan disjoint column ranges that cover the vocabulary
+    (the reference shards it evenly, NV/layers/embed_head.py:19-23); for steps of more than 64 rows rank 0's
+    range ends on a 256-column boundary because a sampler record covers one 256-column tile."""
+    import importlib
+    tp = importlib.import_module("mineru-diffusion_b200.tp")
+    for vocab in (151936, 1024, 32000, 128 * 7, 256, 128):
+        for many in (False, True):
+            b0, c0, p0 = tp.lm_head_split(vocab, 0, many)
+            b1, c1, p1 = tp.lm_head_split(vocab, 1, many)
+            assert b0 == 0 and b1 == c0 and (c0 + c1) * 128 == vocab
+            assert p0 == c1 * 128 and p1 == c0 * 128
+            if many and c1 > 0:
+                assert (c0 * 128) % 256 == 0
+            assert abs(c0 - c1) <= 2

@@ -15,7 +15,7 @@ from conftest import ROOT
 pytestmark = pytest.mark.gpu
 
 
-def _child(rank, port, out_dir, eager, nreq=2):
+def _child(rank, port, out_dir, eager, nreq=2, pair_from_256=False):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import torch.distributed as dist
@@ -23,6 +23,8 @@ def _child(rank, port, out_dir, eager, nreq=2):
     mdb = importlib.import_module("mineru-diffusion_b200")
     dev = f"cuda:{rank}"
     torch.cuda.set_device(dev)
+    if pair_from_256:      # the prefill of these requests (more than 256 rows) then runs on CTA pairs
+        mdb.ops.set_option(mdb.ops.OPT_GEMM_PAIR, 2)
     dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", world_size=2, rank=rank,
                             device_id=torch.device(dev))
     dcfg = mdb.DecoderConfig(vocab_size=1024, hidden_size=256, intermediate_size=512, num_hidden_layers=3,
@@ -109,14 +111,15 @@ def test_tp2_matches_tp1_and_ranks_agree(tmp_path, eager):
     assert agree / total >= 0.9
 
 
-@pytest.mark.parametrize("eager", [True, False])
-def test_tp2_many_row_steps(tmp_path, eager):
-    """Three requests = 96 rows per step: the row-parallel projections go through the many-row GEMM + the
-    reference's collective, the LM head is scanned whole on both ranks."""
+@pytest.mark.parametrize("eager,pair", [(True, False), (False, False), (False, True)])
+def test_tp2_many_row_steps(tmp_path, eager, pair):
+    """Three requests = 96 rows per step, 394 rows in the prefill: the row-parallel projections run on the tile
+    GEMM with the exchange in its epilogue (also on CTA pairs, taken from 256 rows for this test), the LM head is
+    split by vocabulary tiles with records exchanged (whole on both ranks with an explicit noise tensor)."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    port = 29300 + os.getpid() % 200 + (0 if eager else 1)
-    mp.start_processes(_child, args=(port, str(tmp_path), eager, 3), nprocs=2, join=True, start_method="spawn")
+    port = 29300 + os.getpid() % 200 + (0 if eager else 1) + (2 if pair else 0)
+    mp.start_processes(_child, args=(port, str(tmp_path), eager, 3, pair), nprocs=2, join=True, start_method="spawn")
     r0, r1 = torch.load(tmp_path / "rank0.pt"), torch.load(tmp_path / "rank1.pt")
     assert r0["status"] == 0 and r1["status"] == 0
     agree = total = 0

@@ -26,7 +26,7 @@ from ..decoder import DecoderEngine, DecoderWeights
 from .config import Config
 from .context import Context
 from .sequence import Sequence
-from .step_inputs import build_decode_inputs, build_prefill_inputs
+from .step_inputs import build_decode_inputs, build_prefill_inputs, fill_decode_inputs_small
 
 
 def _round_up(v: int, a: int) -> int:
@@ -256,6 +256,14 @@ class ModelRunner:
             else:
                 for i, seq in enumerate(seqs):
                     ids[i] = seq.current_denoising_block.numpy()
+        elif bs <= 4:
+            hn["slots"].fill(-1)
+            hn["ctx"].fill(0)
+            self._decode_max_ctx = fill_decode_inputs_small(seqs, b, hn["ids"], hn["pos"], hn["slots"], hn["ctx"],
+                                                            hn["tab"])
+            for i, seq in enumerate(seqs):
+                hn["temp"][i] = seq.temperature
+            self._decode_key, self._decode_seqs = key, list(seqs)
         else:
             inp = build_decode_inputs(seqs, b)
             width = inp["block_tables"].shape[1]

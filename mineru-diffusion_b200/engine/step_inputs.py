@@ -68,3 +68,45 @@ def build_decode_inputs(seqs: list[Sequence], block_size: int) -> dict:
         slots = np.where(held[:, None] > 0, page_ids * page + pos % page, -1).astype(np.int32)
     ctx = (lens + block_size).astype(np.int32)
     return dict(input_ids=ids, positions=pos, slot_mapping=slots, context_lens=ctx, block_tables=tables)
+
+
+_ARANGE64: dict[int, np.ndarray] = {}
+
+
+def fill_decode_inputs_small(seqs: list[Sequence], block_size: int, ids: np.ndarray, pos: np.ndarray,
+                             slots: np.ndarray, ctx: np.ndarray, tab: np.ndarray) -> int:
+    """``build_decode_inputs`` for a handful of requests, written straight into the rows of the caller's
+    (pinned) arrays: per request a few slice writes instead of a dozen array constructions for the whole batch.
+    Same contract (NV/engine/model_runner.py:169-185, NV/engine/sequence.py:117-141): a block spans at most two
+    pages; -1 slots for a request that holds no page; IndexError if a position lies beyond the page table.
+    Returns the longest context."""
+    ar = _ARANGE64.get(block_size)
+    if ar is None:
+        ar = _ARANGE64[block_size] = np.arange(block_size, dtype=np.int64)
+    page = Sequence.kvcache_block_size
+    longest = 0
+    for i, seq in enumerate(seqs):
+        n = len(seq)
+        table = seq.block_table
+        ids[i] = seq.current_denoising_block.numpy()
+        np.add(ar, n, out=pos[i])
+        ctx[i] = n + block_size
+        longest = max(longest, n + block_size)
+        held = len(table)
+        if held == 0:
+            slots[i] = -1
+            tab[i] = -1
+            continue
+        if held > tab.shape[1]:
+            raise AssertionError("page table wider than max_model_len allows")
+        tab[i, :held] = table
+        tab[i, held:] = -1
+        first, off = divmod(n, page)
+        run = min(block_size, page - off)
+        last = first if run == block_size else first + 1
+        if last >= held:
+            raise IndexError("block position beyond the request's page table")
+        np.add(ar[:run], table[first] * page + off, out=slots[i, :run], casting="unsafe")
+        if run < block_size:
+            np.add(ar[:block_size - run], table[last] * page, out=slots[i, run:], casting="unsafe")
+    return longest

@@ -222,3 +222,41 @@ def test_lm_head_split_covers_the_vocabulary():
             if many and c1 > 0:
                 assert (c0 * 128) % 256 == 0
             assert abs(c0 - c1) <= 2
+
+
+def test_small_batch_fill_matches_vectorised_builder(mdb):
+    """The direct fill used for up to four requests writes what the vectorised builder returns (ids, positions,
+    slots, context lengths, the page-table prefix), including blocks that straddle two pages, page-aligned ends
+    and a request without pages."""
+    import importlib
+    si = importlib.import_module("mineru-diffusion_b200.engine.step_inputs")
+    gen = torch.Generator().manual_seed(1)
+    for block in (8, 32, 64):
+        lens = (1, 255, 256 - block, 257, 511, 700, 1024 - block, 3000, 240)
+        for start in range(0, len(lens), 3):
+            seqs = []
+            for n in lens[start:start + 3]:
+                sp = mdb.SamplingParams(temperature=1.0, max_new_tokens=64, ignore_eos=True)
+                seq = mdb.Sequence(torch.randint(0, 100, (n,), generator=gen).tolist(), sp, denoising_block_size=block,
+                                   mask_token_id=1000)
+                seq.block_table = torch.randperm(64, generator=gen)[:(n + block + 255) // 256].tolist()
+                seq.current_denoising_block[::3] = 5
+                seqs.append(seq)
+            if start == 3:
+                seqs[1].block_table = []
+            want = si.build_decode_inputs(seqs, block)
+            bs = len(seqs)
+            ids = np.zeros((4, block), np.int64); pos = np.zeros((4, block), np.int64)
+            slots = np.full((4, block), -1, np.int32); ctx = np.zeros(4, np.int32); tab = np.full((4, 16), -1, np.int32)
+            longest = si.fill_decode_inputs_small(seqs, block, ids, pos, slots, ctx, tab)
+            assert np.array_equal(ids[:bs], want["input_ids"]) and np.array_equal(pos[:bs], want["positions"])
+            assert np.array_equal(slots[:bs], want["slot_mapping"]) and np.array_equal(ctx[:bs], want["context_lens"])
+            width = want["block_tables"].shape[1]
+            assert np.array_equal(tab[:bs, :width], want["block_tables"])
+            assert longest == int(want["context_lens"].max())
+    sp = mdb.SamplingParams(temperature=1.0, max_new_tokens=64, ignore_eos=True)
+    seq = mdb.Sequence(list(range(250)), sp, denoising_block_size=32, mask_token_id=1000)
+    seq.block_table = [3]                     # the block needs a second page
+    with pytest.raises(IndexError):
+        si.fill_decode_inputs_small([seq], 32, np.zeros((1, 32), np.int64), np.zeros((1, 32), np.int64),
+                                    np.zeros((1, 32), np.int32), np.zeros(1, np.int32), np.full((1, 4), -1, np.int32))

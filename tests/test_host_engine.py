@@ -260,3 +260,43 @@ def test_small_batch_fill_matches_vectorised_builder(mdb):
     with pytest.raises(IndexError):
         si.fill_decode_inputs_small([seq], 32, np.zeros((1, 32), np.int64), np.zeros((1, 32), np.int64),
                                     np.zeros((1, 32), np.int32), np.zeros(1, np.int32), np.full((1, 4), -1, np.int32))
+
+
+def test_tensor_parallel_shards_recompose_the_layer(mdb):
+    """tp.shard_weights cuts q|k|v rows by head, o_proj columns by head, gate|up rows and down_proj columns the
+    way the reference's weight loaders do (NV/layers/linear.py:54-151): the column-parallel outputs of the two
+    ranks are the matching columns of the full output, and the row-parallel outputs add up to it."""
+    import importlib
+    tp = importlib.import_module("mineru-diffusion_b200.tp")
+    dec = importlib.import_module("mineru-diffusion_b200.decoder")
+    cfg = mdb.DecoderConfig(vocab_size=256, hidden_size=64, intermediate_size=96, num_hidden_layers=1,
+                            num_attention_heads=4, num_key_value_heads=2, head_dim=16, max_position_embeddings=64)
+    g = torch.Generator().manual_seed(0)
+    h, d, hq, hkv, inter = 64, 16, 4, 2, 96
+    rnd = lambda *s: torch.randn(*s, generator=g, dtype=torch.float64)
+    layer = dec.LayerWeights(rnd(h), rnd((hq + 2 * hkv) * d, h), rnd(d), rnd(d), rnd(h, hq * d), rnd(h), rnd(2 * inter, h),
+                             rnd(h, inter))
+    full = dec.DecoderWeights(rnd(256, h), [layer], rnd(h), rnd(256, h))
+    local = tp.shard_config(cfg, 2)
+    assert (local.num_attention_heads, local.num_key_value_heads, local.intermediate_size) == (2, 1, 48)
+    x = rnd(5, h)
+    qkv = x @ layer.qkv.T
+    q, k, v = qkv.split([hq * d, hkv * d, hkv * d], dim=1)
+    attn = rnd(5, hq * d)
+    gate, up = (x @ layer.gate_up.T).split([inter, inter], dim=1)
+    act = torch.nn.functional.silu(gate) * up
+    o_sum, down_sum = torch.zeros(5, h, dtype=torch.float64), torch.zeros(5, h, dtype=torch.float64)
+    for rank in range(2):
+        w = tp.shard_weights(full, cfg, rank, 2).layers[0]
+        lq, lk, lv = (x @ w.qkv.T).split([2 * d, d, d], dim=1)
+        assert torch.equal(lq, q[:, rank * 2 * d:(rank + 1) * 2 * d])
+        assert torch.equal(lk, k[:, rank * d:(rank + 1) * d]) and torch.equal(lv, v[:, rank * d:(rank + 1) * d])
+        o_sum += attn[:, rank * 2 * d:(rank + 1) * 2 * d] @ w.o.T
+        lg, lu = (x @ w.gate_up.T).split([48, 48], dim=1)
+        lact = torch.nn.functional.silu(lg) * lu
+        assert torch.equal(lact, act[:, rank * 48:(rank + 1) * 48])
+        down_sum += lact @ w.down.T
+    assert torch.allclose(o_sum, attn @ layer.o.T, rtol=1e-12, atol=1e-12)
+    assert torch.allclose(down_sum, act @ layer.down.T, rtol=1e-12, atol=1e-12)
+    with pytest.raises(ValueError):
+        tp.shard_config(mdb.DecoderConfig(num_attention_heads=3, num_key_value_heads=3), 2)

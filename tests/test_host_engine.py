@@ -300,3 +300,21 @@ def test_tensor_parallel_shards_recompose_the_layer(mdb):
     assert torch.allclose(down_sum, act @ layer.down.T, rtol=1e-12, atol=1e-12)
     with pytest.raises(ValueError):
         tp.shard_config(mdb.DecoderConfig(num_attention_heads=3, num_key_value_heads=3), 2)
+
+
+def test_attention_part_policy(mdb):
+    """ops.default_nsplit: key-range parts fill the 148 SMs once and no more, at most 16, none below 256 keys,
+    and no split from 16 requests on (decoder shapes: 16 query / 8 KV heads, block 32)."""
+    n = lambda bs, ctx, block=32, hq=16, hkv=8: mdb.ops.default_nsplit(bs, block, hq, hkv, ctx)
+    assert n(1, 4096) == 16 and n(1, 1100) == 4 and n(1, 200) == 1
+    assert n(2, 8192) == 9 and n(4, 8192) == 4 and n(8, 8192) == 2
+    assert all(n(bs, 8192) == 1 for bs in (16, 19, 32, 64, 512))
+    for bs in (1, 2, 3, 4, 6, 8, 12):
+        for ctx in (300, 1000, 5000, 16416):
+            parts = n(bs, ctx)
+            assert 1 <= parts <= 16 and parts <= max(1, ctx // 256)
+            assert parts == 1 or bs * 8 * parts <= 148
+    # a block of 64 with two heads per KV head still is one 128-row CTA per (request, KV head)
+    assert n(1, 4096, block=64) == 16
+    # 8 query heads per KV head, block 32: 256 rows = two 128-row CTAs per (request, KV head)
+    assert n(1, 4096, hq=16, hkv=2) == 16 and n(8, 4096, hq=16, hkv=2) == 4

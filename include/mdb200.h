@@ -37,7 +37,8 @@ enum {
 /* bits of the device status word */
 enum {
   MDB_STATUS_BAD_SLOT = 1u,     /* slot_mapping entry outside [0, num_slots) and not -1: row skipped */
-  MDB_STATUS_BAD_PAGE = 2u,     /* page-table entry outside [0, num_pages): keys treated as absent */
+  MDB_STATUS_BAD_PAGE = 2u,     /* page-table entry outside [0, num_pages) (page 0 is read in its place) or a context
+                                   longer than the page-table row can address (cut to the row): output rows invalid */
   MDB_STATUS_BAD_TOKEN = 4u,    /* token id outside the embedding table: row zeroed */
   MDB_STATUS_BAD_POSITION = 8u, /* position outside the rotary table: row left unrotated */
   MDB_STATUS_WAIT_TIMEOUT = 16u /* a bounded wait on a peer flag or barrier expired */
@@ -47,17 +48,14 @@ const char* mdb_strerror(int code);
 int mdb_version(void);
 
 /* Process-wide switches (no counterpart in the reference; for measurement and
- * fault isolation).  MDB_OPT_STREAM_KERNEL: 0 = short steps (m <= 64) use the
- * tcgen05/TMA weight-streaming kernel where the shape allows (default), 1 =
- * always the register-streaming kernel.  MDB_OPT_PDL: 1 = kernels are chained
- * with programmatic dependent launch (default), 0 = plain stream order.
- * MDB_OPT_ATTN_KERNEL: which kernel mdb_attn_block_paged runs: 0 = chosen by
- * the amount of work (default), 1 = the mma.sync kernel, 2 = the tcgen05/TMA
- * kernel whenever the shape allows (at most 128 query heads per KV head).
- * MDB_OPT_GEMM_PAIR: GEMMs of many rows on pairs of CTAs (tcgen05.mma.
- * cta_group::2, tiles of 256 x 256): 1 = from 2048 rows (default), 2 = from 256
- * rows, 0 = never. */
-enum { MDB_OPT_STREAM_KERNEL = 0, MDB_OPT_PDL = 1, MDB_OPT_ATTN_KERNEL = 2, MDB_OPT_GEMM_PAIR = 3 };
+ * fault isolation).  MDB_OPT_PDL: 1 = kernels are chained with programmatic
+ * dependent launch (default), 0 = plain stream order.  MDB_OPT_GEMM_PAIR: GEMMs
+ * of many rows on pairs of CTAs (tcgen05.mma.cta_group::2, tiles of 256 x 256):
+ * 1 = from 2048 rows (default), 2 = from 256 rows, 0 = never.
+ * MDB_OPT_WAIT_LIMIT_US: how long a wait inside a kernel (mbarrier, peer flag)
+ * may last before it gives up and raises MDB_STATUS_WAIT_TIMEOUT, in
+ * microseconds (default 2 000 000); written to the current device, blocking. */
+enum { MDB_OPT_PDL = 1, MDB_OPT_GEMM_PAIR = 3, MDB_OPT_WAIT_LIMIT_US = 4 };
 int mdb_set_option(int option, int value);
 /* Measurement aid: registers a device buffer (uint64 count, then (kernel,
  * event, globaltimer ns) triples) that block 0 of the traced kernels appends
@@ -152,12 +150,12 @@ int mdb_gemm_splitk_partials(const void* x, int64_t ldx, const void* w, float* p
 /* gate_up projection fused with SiLU*mul (NV/models/sdar.py:109-111,
  * NV/layers/activation.py:12-15): w is [2*inter, k] with gate rows first;
  * act[m, inter] = bf16(silu_fp32(bf16(gate))) * bf16(up).  m <= 64 streams the
- * weight once (inter % 16 == 0); larger m runs the tcgen05 tile kernel
- * (inter % 128 == 0, k % 64 == 0). */
+ * weight once (inter % 64 == 0, k % 64 == 0); larger m runs the tcgen05 tile
+ * kernel (inter % 128 == 0, k % 64 == 0). */
 int mdb_gemm_gateup_swiglu(const void* x, int64_t ldx, const void* w_gate_up, void* act, int64_t ld_act, int m,
                            int inter, int k, mdb_stream_t stream);
 
-/* SiLU*mul on a materialised [m, 2*inter] bf16 matrix (large-m path). */
+/* SiLU*mul on a materialised [m, 2*inter] bf16 matrix (SiluAndMul.forward, NV/layers/activation.py:12-15). */
 int mdb_silu_mul(const void* gate_up, int64_t ld_in, void* act, int64_t ld_act, int m, int inter,
                  mdb_stream_t stream);
 
@@ -213,8 +211,9 @@ int mdb_gather_rows(const void* table, int64_t num_rows, const int64_t* ids, voi
  * noise from (seed, step, row, column) -- mdb_gumbel_noise() writes out the
  * same values.  step_dev, if not NULL, points to a uint32 in device memory
  * that is added to `step` when the kernel runs, so a captured graph can be
- * replayed with fresh noise.  m <= 64 streams the weight once; larger m goes
- * through bf16 logits in the workspace. */
+ * replayed with fresh noise.  m <= 64 streams the weight once; larger m runs
+ * the tile GEMM with the sampler reduction in its epilogue (an explicit noise
+ * tensor with many rows goes through bf16 logits in the workspace). */
 int64_t mdb_lmhead_workspace_bytes(int m, int vocab);
 int mdb_lmhead_sample(const void* hidden, int64_t ld_hidden, const void* w, int m, int vocab, int h,
                       const float* temperatures, int block, int noise_mode, const float* noise, uint32_t seed,
@@ -232,72 +231,23 @@ int mdb_gumbel_noise(float* out, int m, int vocab, uint32_t seed, uint32_t step,
 
 /* The unmask rule of Sampler.forward (NV/layers/sampler.py:28-54) on device:
  * per request, masked positions whose confidence is > threshold are replaced
- * by x0; if fewer than `quota` qualify the `quota` most confident masked
- * positions are taken instead (quota = 1 is the nano engine's rule, the HF
- * twin's quota is mineru_diffusion/modeling_mineru_diffusion.py:518-532).
+ * by x0; if fewer than the request's quota qualify, the quota most confident
+ * masked positions are taken instead (all of them when fewer are left; the
+ * lowest index wins a tie).  quota = 1 is the nano engine's rule; the HF twin
+ * takes its quota from a per-block schedule
+ * (mineru_diffusion/modeling_mineru_diffusion.py:518-532,617-623): pass it per
+ * request in quotas [bs] int32 (device; NULL: `quota` for every request).
  * block_ids [bs, block] int64 is updated in place; transfer_out [bs, block]
- * uint8; count_out [bs] int32 = positions unmasked. Requests with no masked
- * position are left untouched. */
+ * uint8; count_out [bs] int32 = positions unmasked.  Requests with no masked
+ * position are left untouched.  A quota of 0 (the schedule's entry when a block
+ * has more steps than tokens) transfers only what passes the threshold.
+ * status_out, if not NULL, is a device word that receives the device status
+ * word as it stands when this kernel runs (the step's kernels before it have
+ * finished), and the status word is cleared: the host reads the step's status
+ * in the same copy as its results instead of synchronising for it. */
 int mdb_unmask_decide(int64_t* block_ids, const int32_t* x0, const float* conf, int bs, int block, int64_t mask_id,
-                      float threshold, int quota, uint8_t* transfer_out, int32_t* count_out, mdb_stream_t stream);
-
-/* ---- whole denoising step as one persistent kernel ----------------------------------- */
-
-/* Replaces, for steps of at most 64 rows, everything ModelRunner.run_model does
- * between the input copies and the sampler (NV/engine/model_runner.py:194-211,
- * NV/models/sdar.py:141-181, NV/layers/embed_head.py:61-72, NV/layers/sampler.py:
- * 11-22): embedding rows, every layer, final norm, LM head and sampler
- * statistics, as ONE cooperative kernel whose TMA producer streams the weights
- * of all projections back to back.  All pointers are device pointers; the
- * arrays of per-layer pointers are host arrays of length `layers`.
- * mdb_fused_step_create encodes the tensor maps and writes the descriptor into
- * caller-owned device memory of mdb_fused_step_desc_bytes() bytes (blocking
- * copy; call at set-up).  mdb_fused_step_launch zeroes the barrier word
- * (grid_bar, the one given at creation) and runs one step; the per-step inputs
- * are read from the buffers named in the descriptor.  noise_mode 0 or 2. */
-typedef struct {
-  int layers, m, bs, block, hidden, inter, hq, hkv, vocab;
-  int ks_qkv, ks_o, ks_down, nsplit;
-  float eps, softmax_scale;
-  const void* const* w_qkv;
-  const void* const* w_o;
-  const void* const* w_gate_up;
-  const void* const* w_down;
-  const void* const* ln1;
-  const void* const* ln2;
-  const void* const* q_norm;
-  const void* const* k_norm;
-  void* const* k_cache;
-  void* const* v_cache;
-  const void* final_ln;
-  const void* embed_table;
-  int64_t embed_rows;
-  const void* lm_head;
-  void *x, *res, *q, *attn, *act, *final_rows;
-  float* parts;       /* max(ks_qkv*nqkv, ks_o*hidden, ks_down*hidden) * m floats */
-  void* attn_ws;      /* mdb_attn_paged_workspace_bytes(bs, block, hq, nsplit) */
-  const float* rope;
-  int max_pos;
-  const int64_t* ids;
-  const int64_t* positions;
-  const int32_t* slots;
-  const int32_t* ctx_lens;
-  const int32_t* block_table;
-  int table_stride, num_pages;
-  int64_t num_slots;
-  const float* temperatures;
-  int noise_mode;
-  uint32_t seed;
-  const uint32_t* step_dev;
-  void* lm_ws;        /* mdb_lmhead_workspace_bytes(m, vocab) */
-  int32_t* x0;
-  float* conf;
-  uint32_t* grid_bar; /* one word: arrival counter of the kernel's grid barrier */
-} mdb_fused_step_params;
-
-int64_t mdb_fused_step_desc_bytes(void);
-int mdb_fused_step_create(const mdb_fused_step_params* params, void* desc_device);
-int mdb_fused_step_launch(const void* desc_device, uint32_t* grid_bar, int m, mdb_stream_t stream);
+                      float threshold, int quota, const int32_t* quotas, uint8_t* transfer_out, int32_t* count_out,
+                      uint32_t* status_out, mdb_stream_t stream);
 
 /* ---- tensor-parallel pair (TP = 2) -------------------------------------------------- */
 

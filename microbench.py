@@ -1,10 +1,10 @@
 """Per-kernel timings of the decode-step operators on the current GPU.
 
-    python mineru-diffusion_b200/microbench.py attn --bs 64 --ctx 1536 5120
-    python mineru-diffusion_b200/microbench.py stair --lens 4096 4096 4096 4096
-    python mineru-diffusion_b200/microbench.py gemm --m 2048
-    python mineru-diffusion_b200/microbench.py lmhead --m 2048
-    python mineru-diffusion_b200/microbench.py elementwise --m 2048
+    python microbench.py attn --bs 64 --ctx 1536 5120
+    python microbench.py stair --lens 4096 4096 4096 4096
+    python microbench.py gemm --m 2048
+    python microbench.py lmhead --m 2048
+    python microbench.py elementwise --m 2048
 
 Each operator is captured ``--reps`` times into one CUDA graph and the graph
 is timed with CUDA events, so host launch cost stays out of the figure; the
@@ -22,7 +22,7 @@ import sys
 
 import torch
 
-sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 pkg = importlib.import_module("mineru-diffusion_b200")
 ops = pkg.ops
 DEV, BF = "cuda", torch.bfloat16
@@ -70,7 +70,7 @@ def _mat(gen, r, c, scale=0.02):
     return (torch.randn(r, c, generator=gen, device=DEV) * scale).to(BF)
 
 
-def attn_case(bs: int, ctx_range, block: int = 32, hq: int = 16, hkv: int = 8, nsplit: int = 0, kernel: int = 0,
+def attn_case(bs: int, ctx_range, block: int = 32, hq: int = 16, hkv: int = 8, nsplit: int = 0,
               reps: int = 10, plain: bool = False, seed: int = 3) -> dict:
     """Block attention over the paged cache for ``bs`` requests with prefix lengths uniform in ``ctx_range``.
     Returns milliseconds per launch, the algorithmic bytes (K and V rows of every context once + q and out)
@@ -94,62 +94,83 @@ def attn_case(bs: int, ctx_range, block: int = 32, hq: int = 16, hkv: int = 8, n
     ctx_d, table_d = ctx.int().to(DEV), table.to(DEV)
     nbytes = int((2 * ctx * hkv * 128 * 2).sum()) + 2 * q.numel() * 2
     flops = int((4 * block * hq * 128 * ctx).sum())
-    ops.set_option(ops.OPT_ATTN_KERNEL, kernel)
     ns = nsplit or ops.default_nsplit(bs, block, hq, hkv, int(ctx.max()))
     ws = torch.empty(max(16, ops.attn_workspace_bytes(bs, block, hq, ns)), dtype=torch.uint8, device=DEV)
-    try:
-        ms = timed(lambda: ops.block_attn_with_kvcache(q, kc, vc, ctx_d, table_d, nsplit=ns, workspace=ws, out=out),
-                   reps, plain)
-    finally:
-        ops.set_option(ops.OPT_ATTN_KERNEL, 0)
+    ms = timed(lambda: ops.block_attn_with_kvcache(q, kc, vc, ctx_d, table_d, nsplit=ns, workspace=ws, out=out),
+               reps, plain)
     return {"ms": ms, "bytes": nbytes, "flops": flops, "nsplit": ns}
 
 
 def bench_attn(a) -> None:
-    for kern in a.kernel:
-        r = attn_case(a.bs, a.ctx, a.block, a.hq, a.hkv, a.nsplit, kern, a.reps, a.plain, a.seed)
-        name = {0: "auto", 1: "mma.sync", 2: "tcgen05"}[kern]
-        line(f"attn[{name}] bs={a.bs} ctx[{a.ctx[0]},{a.ctx[1]}] hkv={a.hkv} ns={r['nsplit']}", r["ms"], r["flops"],
-             r["bytes"])
+    r = attn_case(a.bs, a.ctx, a.block, a.hq, a.hkv, a.nsplit, a.reps, a.plain, a.seed)
+    line(f"attn bs={a.bs} ctx[{a.ctx[0]},{a.ctx[1]}] hkv={a.hkv} ns={r['nsplit']}", r["ms"], r["flops"], r["bytes"])
+
+
+def stair_case(lens, block: int = 32, hq: int = 16, hkv: int = 8, reps: int = 10, plain: bool = False,
+               seed: int = 3) -> dict:
+    """Staircase (prefill) attention over packed sequences of the given lengths: milliseconds per launch,
+    flops over the visible part of the mask (T^2 / 2 + T * block / 2 query-key pairs per head) and the
+    algorithmic bytes (q, k, v in and out once)."""
+    import numpy as np
+    cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32, device=DEV)
+    n = int(cu[-1])
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    q = torch.randn(n, hq, 128, generator=g, device=DEV).to(BF)
+    k = torch.randn(n, hkv, 128, generator=g, device=DEV).to(BF)
+    v = torch.randn(n, hkv, 128, generator=g, device=DEV).to(BF)
+    out = torch.empty_like(q)
+    flops = sum(4.0 * hq * 128 * (t * t / 2 + t * block / 2) for t in lens)
+    nbytes = (2 * n * hq * 128 + 2 * n * hkv * 128) * 2
+    ms = timed(lambda: ops.sparse_attn_varlen(q, k, v, cu, cu, block, max_seqlen=max(lens), out=out), reps, plain)
+    return {"ms": ms, "flops": flops, "bytes": nbytes, "tokens": n}
 
 
 def bench_stair(a) -> None:
-    """Staircase (prefill) attention over packed sequences of the given lengths; flops are counted over the
-    visible part of the mask only (T^2 / 2 + T * block / 2 query-key pairs per head)."""
-    import numpy as np
-    lens = a.lens
-    cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32, device=DEV)
-    n = int(cu[-1])
-    g = torch.Generator(device=DEV).manual_seed(a.seed)
-    q = torch.randn(n, a.hq, 128, generator=g, device=DEV).to(BF)
-    k = torch.randn(n, a.hkv, 128, generator=g, device=DEV).to(BF)
-    v = torch.randn(n, a.hkv, 128, generator=g, device=DEV).to(BF)
-    out = torch.empty_like(q)
-    flops = sum(4.0 * a.hq * 128 * (t * t / 2 + t * a.block / 2) for t in lens)
-    for kern in a.kernel:
-        ops.set_option(ops.OPT_ATTN_KERNEL, kern)
-        ms = timed(lambda: ops.sparse_attn_varlen(q, k, v, cu, cu, a.block, max_seqlen=max(lens), out=out), a.reps, a.plain)
-        name = {0: "auto", 1: "mma.sync", 2: "tcgen05"}[kern]
-        line(f"staircase[{name}] {len(lens)} seqs, {n} tokens", ms, flops)
-    ops.set_option(ops.OPT_ATTN_KERNEL, 0)
+    r = stair_case(a.lens, a.block, a.hq, a.hkv, a.reps, a.plain, a.seed)
+    line(f"staircase {len(a.lens)} seqs, {r['tokens']} tokens", r["ms"], r["flops"], r["bytes"])
 
 
-def bench_gemm(a) -> None:
-    g = torch.Generator(device=DEV).manual_seed(a.seed)
-    m, h, inter = a.m, a.hidden, a.inter
-    qkv_n = (a.hq + 2 * a.hkv) * 128
-    for name, (n, k) in {"qkv": (qkv_n, h), "o_proj": (a.hq * 128, h), "down_proj": (h, inter)}.items():
-        if a.only and name not in a.only:
+def gemm_cases(m: int, hidden: int = 2048, inter: int = 6144, hq: int = 16, hkv: int = 8, reps: int = 10,
+               plain: bool = False, seed: int = 3, only=None) -> list[dict]:
+    """The four projections of a layer at ``m`` step rows: name, shape, milliseconds per launch, flops and
+    weight bytes.  qkv is the plain projection (its fused norm / rotary / KV-store form is `qkv+rope+store`)."""
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    h = hidden
+    qkv_n = (hq + 2 * hkv) * 128
+    out = []
+    for name, (n, k) in {"qkv": (qkv_n, h), "o_proj": (h, hq * 128), "down_proj": (h, inter)}.items():
+        if only and name not in only:
             continue
         x, w = _mat(g, m, k, 1.0), _mat(g, n, k)
         y = torch.empty(m, n, dtype=BF, device=DEV)
-        line(f"{name} m={m} n={n} k={k}", timed(lambda: ops.linear(x, w, out=y), a.reps, a.plain), 2.0 * m * n * k,
-             2.0 * n * k)
-    if not a.only or "gate_up" in a.only:
+        out.append(dict(op=name, m=m, n=n, k=k, ms=timed(lambda: ops.linear(x, w, out=y), reps, plain),
+                        flops=2.0 * m * n * k, bytes=2.0 * n * k))
+    if (not only or "qkv+rope+store" in only) and ops.qkv_rope_commit_supported(m, h):
+        x, w = _mat(g, m, h, 1.0), _mat(g, qkv_n, h)
+        pos = torch.arange(m, device=DEV) % 4096
+        table = pkg.decoder.rope_table(4096, 128, 1e6, DEV)
+        ones = torch.ones(128, dtype=BF, device=DEV)
+        pages = (m + 255) // 256
+        kc = torch.zeros(pages, 256, hkv, 128, dtype=BF, device=DEV)
+        vc = torch.zeros_like(kc)
+        slots = torch.arange(m, dtype=torch.int32, device=DEV)
+        q = torch.empty(m, hq, 128, dtype=BF, device=DEV)
+        out.append(dict(op="qkv+rope+store", m=m, n=qkv_n, k=h,
+                        ms=timed(lambda: ops.qkv_proj_rope_commit(x, w, pos, table, ones, ones, 1e-6, hq, hkv, slots, kc,
+                                                                  vc, q_out=q), reps, plain),
+                        flops=2.0 * m * qkv_n * h, bytes=2.0 * qkv_n * h))
+    if not only or "gate_up" in only:
         x, w = _mat(g, m, h, 1.0), _mat(g, 2 * inter, h)
         act = torch.empty(m, inter, dtype=BF, device=DEV)
-        line(f"gate_up+SiLU*mul m={m} n={2 * inter} k={h}", timed(lambda: ops.gateup_swiglu(x, w, out=act), a.reps, a.plain),
-             4.0 * m * inter * h, 4.0 * inter * h)
+        out.append(dict(op="gate_up+SiLU*mul", m=m, n=2 * inter, k=h,
+                        ms=timed(lambda: ops.gateup_swiglu(x, w, out=act), reps, plain),
+                        flops=4.0 * m * inter * h, bytes=4.0 * inter * h))
+    return out
+
+
+def bench_gemm(a) -> None:
+    for c in gemm_cases(a.m, a.hidden, a.inter, a.hq, a.hkv, a.reps, a.plain, a.seed, a.only):
+        line(f"{c['op']} m={c['m']} n={c['n']} k={c['k']}", c["ms"], c["flops"], c["bytes"])
 
 
 def bench_lmhead(a) -> None:
@@ -196,9 +217,8 @@ def main() -> None:
     ap.add_argument("--inter", type=int, default=6144)
     ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--nsplit", type=int, default=0, help="key-range parts per request (0: the library's choice)")
-    ap.add_argument("--kernel", type=int, nargs="+", default=[1, 2], help="attention kernels: 1 mma.sync, 2 tcgen05")
     ap.add_argument("--lens", type=int, nargs="+", default=[4096] * 4, help="stair: sequence lengths of the packed batch")
-    ap.add_argument("--only", nargs="*", default=None, help="gemm: subset of qkv o_proj down_proj gate_up")
+    ap.add_argument("--only", nargs="*", default=None, help="gemm: subset of qkv qkv+rope+store o_proj down_proj gate_up")
     a = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("needs a GPU")

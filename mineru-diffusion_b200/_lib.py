@@ -16,27 +16,6 @@ _i64 = C.c_int64
 _u32 = C.c_uint32
 _f = C.c_float
 
-class FusedStepParams(C.Structure):
-    """mdb_fused_step_params of include/mdb200.h."""
-    _PP = C.POINTER(C.c_void_p)
-    _fields_ = [
-        ("layers", C.c_int), ("m", C.c_int), ("bs", C.c_int), ("block", C.c_int), ("hidden", C.c_int),
-        ("inter", C.c_int), ("hq", C.c_int), ("hkv", C.c_int), ("vocab", C.c_int),
-        ("ks_qkv", C.c_int), ("ks_o", C.c_int), ("ks_down", C.c_int), ("nsplit", C.c_int),
-        ("eps", C.c_float), ("softmax_scale", C.c_float),
-        ("w_qkv", _PP), ("w_o", _PP), ("w_gate_up", _PP), ("w_down", _PP), ("ln1", _PP), ("ln2", _PP),
-        ("q_norm", _PP), ("k_norm", _PP), ("k_cache", _PP), ("v_cache", _PP),
-        ("final_ln", C.c_void_p), ("embed_table", C.c_void_p), ("embed_rows", C.c_int64), ("lm_head", C.c_void_p),
-        ("x", C.c_void_p), ("res", C.c_void_p), ("q", C.c_void_p), ("attn", C.c_void_p), ("act", C.c_void_p),
-        ("final_rows", C.c_void_p), ("parts", C.c_void_p), ("attn_ws", C.c_void_p),
-        ("rope", C.c_void_p), ("max_pos", C.c_int),
-        ("ids", C.c_void_p), ("positions", C.c_void_p), ("slots", C.c_void_p), ("ctx_lens", C.c_void_p),
-        ("block_table", C.c_void_p), ("table_stride", C.c_int), ("num_pages", C.c_int), ("num_slots", C.c_int64),
-        ("temperatures", C.c_void_p), ("noise_mode", C.c_int), ("seed", C.c_uint32), ("step_dev", C.c_void_p),
-        ("lm_ws", C.c_void_p), ("x0", C.c_void_p), ("conf", C.c_void_p), ("grid_bar", C.c_void_p),
-    ]
-
-
 # name -> (restype, argtypes); mirrors include/mdb200.h one to one
 SIGNATURES = {
     "mdb_strerror": (C.c_char_p, [_i]),
@@ -67,10 +46,7 @@ SIGNATURES = {
     "mdb_lmhead_sample": (_i, [_p, _i64, _p, _i, _i, _i, _p, _i, _i, _p, _u32, _u32, _p, _p, _i64, _p, _p, _p]),
     "mdb_logits_sample": (_i, [_p, _i64, _i, _i, _p, _i, _i, _p, _u32, _u32, _p, _p, _i64, _p, _p, _p]),
     "mdb_gumbel_noise": (_i, [_p, _i, _i, _u32, _u32, _p]),
-    "mdb_unmask_decide": (_i, [_p, _p, _p, _i, _i, _i64, _f, _i, _p, _p, _p]),
-    "mdb_fused_step_desc_bytes": (_i64, []),
-    "mdb_fused_step_create": (_i, [C.POINTER(FusedStepParams), _p]),
-    "mdb_fused_step_launch": (_i, [_p, _p, _i, _p]),
+    "mdb_unmask_decide": (_i, [_p, _p, _p, _i, _i, _i64, _f, _i, _p, _p, _p, _p, _p]),
     "mdb_tp_alloc": (_i, [_i64, C.POINTER(C.c_void_p)]),
     "mdb_tp_free": (_i, [_p]),
     "mdb_tp_export": (_i, [_p, _p]),

@@ -1,5 +1,5 @@
-// C entry points of the linear layers and the LM-head sampler; picks the
-// weight-streaming kernel for short steps and the tiled kernel otherwise.
+// C entry points of the linear layers and the LM-head sampler: the weight-streaming
+// kernel for steps of at most 64 rows, the tile GEMM for everything else.
 #include "mdb_common.cuh"
 
 using namespace mdb;
@@ -14,8 +14,8 @@ struct LmHeadLayout {
 
 LmHeadLayout lmhead_layout(int m, int vocab) {
   LmHeadLayout l;
-  const bool streaming = m <= 64;
-  l.nparts = streaming ? (vocab + 31) / 32 : (vocab + kTcBN - 1) / kTcBN;   // many rows: one record per 256-column tile
+  const bool streaming = m <= 64 && vocab % kWsTileRows == 0;   // weight-streaming kernel: one record per 128-column tile
+  l.nparts = streaming ? vocab / kWsTileRows : (vocab + kTcBN - 1) / kTcBN;   // tile GEMM: one record per 256-column tile
   l.off_i = align256(l.nparts * m * 16);
   l.off_logits = l.off_i + align256(l.nparts * m * 4);
   l.total = l.off_logits + (streaming ? 0 : align256(static_cast<int64_t>(m) * vocab * 2));
@@ -41,10 +41,6 @@ int scan_logits(const bf16* logits, int64_t ld, int m, int vocab, const float* t
   return finalize_sampler(part_f, part_i, nparts, m, x0_out, conf_out, st);
 }
 
-bool use_ws(int epi, int m, int n, int k, int64_t ldx) {
-  return g_opt_stream_kernel == 0 && ws_supported(epi, m, n, k, ldx);
-}
-
 // k slices of the tensor-core streaming kernel: about one task per SM, at least four 64-wide chunks per slice
 int ws_pick_ksplit(int n, int k) {
   const int tiles = n / kWsTileRows;
@@ -58,15 +54,13 @@ int ws_pick_ksplit(int n, int k) {
   return s;
 }
 
-int skinny_pick_ksplit(int m, int n, int k) {
-  const int cols_per_cta = m <= 32 ? 32 : 16;
-  const int ctas = n / cols_per_cta > 0 ? n / cols_per_cta : 1;
-  int s = (256 + ctas - 1) / ctas;
-  if (s > k / 256) s = k / 256;
-  if (s > 16) s = 16;
-  if (s < 1) s = 1;
-  while (s > 1 && static_cast<int64_t>(skinny_k_per_cta(k, s)) * (s - 1) >= k) --s;
-  return s;
+// Common argument checks of the short-step (m <= 64) entry points.
+int check_short_step(const void* x, int64_t ldx, const void* w, int m, int n, int k) {
+  MDB_REQUIRE(x && w, MDB_ERR_ARG);
+  MDB_REQUIRE(m >= 1 && m <= 64, MDB_ERR_UNSUPPORTED);
+  MDB_REQUIRE(n > 0 && k > 0 && ldx >= k, MDB_ERR_ARG);
+  MDB_REQUIRE(ldx % 8 == 0 && mdb_aligned16(x) && mdb_aligned16(w), MDB_ERR_ALIGN);
+  return MDB_OK;
 }
 
 }  // namespace
@@ -74,9 +68,8 @@ int skinny_pick_ksplit(int m, int n, int k) {
 extern "C" {
 
 int mdb_gemm_pick_ksplit(int m, int n, int k) {
-  if (m < 1 || n < 1 || k < 1) return 1;
-  if (use_ws(kWsPartial, m, n, k, k)) return ws_pick_ksplit(n, k);
-  return skinny_pick_ksplit(m, n, k);
+  if (m < 1 || n < 1 || k < 1 || !ws_supported(kWsPartial, m, n, k, k)) return 1;
+  return ws_pick_ksplit(n, k);
 }
 
 int64_t mdb_gemm_splitk_workspace_bytes(int m, int n, int ksplit) {
@@ -87,52 +80,30 @@ int64_t mdb_gemm_splitk_workspace_bytes(int m, int n, int ksplit) {
 int mdb_gemm_splitk_partials(const void* x, int64_t ldx, const void* w, float* partials, int m, int n, int k,
                              int ksplit, mdb_stream_t stream) {
   if (m == 0) return MDB_OK;
-  int rc = check_skinny_common(x, ldx, w, m, n, k);
+  int rc = check_short_step(x, ldx, w, m, n, k);
   if (rc != MDB_OK) return rc;
   MDB_REQUIRE(partials != nullptr && ksplit >= 1 && ksplit <= 64, MDB_ERR_ARG);
   MDB_REQUIRE(mdb_aligned16(partials), MDB_ERR_ALIGN);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (use_ws(kWsPartial, m, n, k, ldx)) {
-    const int chunks = k / kWsBK;
-    const int per = (chunks + ksplit - 1) / ksplit;
-    MDB_REQUIRE(per * (ksplit - 1) < chunks, MDB_ERR_ARG);   // no empty slice: every partial row is written
-    WsArgs a = {};
-    a.m = m; a.n = n; a.k = k; a.ksplit = ksplit;
-    a.partials = partials;
-    return launch_ws<kWsPartial>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), a, st);
-  }
-  MDB_REQUIRE(static_cast<int64_t>(skinny_k_per_cta(k, ksplit)) * (ksplit - 1) < k, MDB_ERR_ARG);
-  SkinnyArgs a = {};
-  a.x = static_cast<const bf16*>(x);
-  a.w = static_cast<const bf16*>(w);
-  a.ldx = ldx;
-  a.m = m; a.n = n; a.k = k;
+  MDB_REQUIRE(ws_supported(kWsPartial, m, n, k, ldx), MDB_ERR_UNSUPPORTED);
+  const int chunks = k / kWsBK;
+  const int per = (chunks + ksplit - 1) / ksplit;
+  MDB_REQUIRE(per * (ksplit - 1) < chunks, MDB_ERR_ARG);   // no empty slice: every partial row is written
+  WsArgs a = {};
+  a.m = m; a.n = n; a.k = k; a.ksplit = ksplit;
   a.partials = partials;
-  return launch_skinny<kEpiPartial>(a, ksplit, st);
+  return launch_ws<kWsPartial>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), a,
+                               static_cast<cudaStream_t>(stream));
 }
 
 int mdb_gemm_gateup_swiglu(const void* x, int64_t ldx, const void* w_gate_up, void* act, int64_t ld_act, int m,
                            int inter, int k, mdb_stream_t stream) {
   if (m == 0) return MDB_OK;
-  if (m > 64) {
-    // many rows: tile GEMM on tcgen05 whose weight tile pairs 128 gate rows with their 128 up rows
-    MDB_REQUIRE(x && w_gate_up && act && inter > 0 && k > 0 && ldx >= k && ld_act >= inter, MDB_ERR_ARG);
-    MDB_REQUIRE(mdb_aligned16(x) && mdb_aligned16(w_gate_up) && mdb_aligned16(act), MDB_ERR_ALIGN);
-    MDB_REQUIRE(g_opt_stream_kernel == 0 && tc_supported(kTcSwiglu, m, inter, k, ldx, ld_act), MDB_ERR_UNSUPPORTED);
-    TcArgs a = {};
-    a.m = m; a.n = inter; a.k = k; a.inter = inter;
-    a.y = static_cast<bf16*>(act);
-    a.ldy = ld_act;
-    return launch_tc<kTcSwiglu>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w_gate_up), 2 * inter, a,
-                                static_cast<cudaStream_t>(stream));
-  }
-  int rc = check_skinny_common(x, ldx, w_gate_up, m, 2 * inter, k);
-  if (rc != MDB_OK) return rc;
-  MDB_REQUIRE(act != nullptr && ld_act >= inter, MDB_ERR_ARG);
-  MDB_REQUIRE(inter % 16 == 0, MDB_ERR_UNSUPPORTED);
-  MDB_REQUIRE(ld_act % 2 == 0 && mdb_aligned16(act), MDB_ERR_ALIGN);
+  MDB_REQUIRE(x && w_gate_up && act && m > 0 && inter > 0 && k > 0 && ldx >= k && ld_act >= inter, MDB_ERR_ARG);
+  MDB_REQUIRE(ldx % 8 == 0 && ld_act % 2 == 0 && mdb_aligned16(x) && mdb_aligned16(w_gate_up) && mdb_aligned16(act),
+              MDB_ERR_ALIGN);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (use_ws(kWsSwiglu, m, 2 * inter, k, ldx)) {
+  if (ws_supported(kWsSwiglu, m, 2 * inter, k, ldx)) {
+    // short step: the weight is streamed once, tiles of 64 gate rows + their 64 up rows
     WsArgs a = {};
     a.m = m; a.n = 2 * inter; a.k = k; a.ksplit = 1;
     a.inter = inter;
@@ -140,15 +111,13 @@ int mdb_gemm_gateup_swiglu(const void* x, int64_t ldx, const void* w_gate_up, vo
     a.ldy = ld_act;
     return launch_ws<kWsSwiglu>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w_gate_up), a, st);
   }
-  SkinnyArgs a = {};
-  a.x = static_cast<const bf16*>(x);
-  a.w = static_cast<const bf16*>(w_gate_up);
-  a.ldx = ldx;
-  a.m = m; a.n = 2 * inter; a.k = k;
+  // many rows: tile GEMM whose weight tile pairs 128 gate rows with their 128 up rows
+  MDB_REQUIRE(tc_supported(kTcSwiglu, m, inter, k, ldx, ld_act), MDB_ERR_UNSUPPORTED);
+  TcArgs a = {};
+  a.m = m; a.n = inter; a.k = k; a.inter = inter;
   a.y = static_cast<bf16*>(act);
   a.ldy = ld_act;
-  a.inter = inter;
-  return launch_skinny<kEpiSwiglu>(a, 1, st);
+  return launch_tc<kTcSwiglu>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w_gate_up), 2 * inter, a, st);
 }
 
 int mdb_gemm_bf16(const void* x, int64_t ldx, const void* w, void* y, int64_t ldy, int m, int n, int k,
@@ -159,33 +128,19 @@ int mdb_gemm_bf16(const void* x, int64_t ldx, const void* w, void* y, int64_t ld
   MDB_REQUIRE(ldx % 8 == 0 && ldy % 2 == 0 && mdb_aligned16(x) && mdb_aligned16(w) && mdb_aligned16(y),
               MDB_ERR_ALIGN);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (use_ws(kWsBf16, m, n, k, ldx)) {
+  if (ws_supported(kWsBf16, m, n, k, ldx)) {
     WsArgs a = {};
     a.m = m; a.n = n; a.k = k; a.ksplit = 1;
     a.y = static_cast<bf16*>(y);
     a.ldy = ldy;
     return launch_ws<kWsBf16>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), a, st);
   }
-  if (m <= 64 && n % 32 == 0 && k % 32 == 0) {
-    SkinnyArgs a = {};
-    a.x = static_cast<const bf16*>(x);
-    a.w = static_cast<const bf16*>(w);
-    a.ldx = ldx;
-    a.m = m; a.n = n; a.k = k;
-    a.y = static_cast<bf16*>(y);
-    a.ldy = ldy;
-    return launch_skinny<kEpiBf16>(a, 1, st);
-  }
-  if (g_opt_stream_kernel == 0 && m > 64 && tc_supported(kTcBf16, m, n, k, ldx, ldy)) {
-    TcArgs a = {};
-    a.m = m; a.n = n; a.k = k;
-    a.y = static_cast<bf16*>(y);
-    a.ldy = ldy;
-    return launch_tc<kTcBf16>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), n, a, st);
-  }
-  MDB_REQUIRE(k % kGemmBK == 0 && n % 2 == 0, MDB_ERR_UNSUPPORTED);
-  return launch_gemm_tiled(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), static_cast<bf16*>(y), ldy,
-                           m, n, k, st);
+  MDB_REQUIRE(tc_supported(kTcBf16, m, n, k, ldx, ldy), MDB_ERR_UNSUPPORTED);
+  TcArgs a = {};
+  a.m = m; a.n = n; a.k = k;
+  a.y = static_cast<bf16*>(y);
+  a.ldy = ldy;
+  return launch_tc<kTcBf16>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), n, a, st);
 }
 
 int mdb_gemm_bf16_tp(const void* x, int64_t ldx, const void* w, void* y, void* y_peer, int64_t ldy, int m, int n, int k,
@@ -196,7 +151,7 @@ int mdb_gemm_bf16_tp(const void* x, int64_t ldx, const void* w, void* y, void* y
   MDB_REQUIRE(ldx % 8 == 0 && ldy % 8 == 0 && mdb_aligned16(x) && mdb_aligned16(w) && mdb_aligned16(y) &&
                   mdb_aligned16(y_peer),
               MDB_ERR_ALIGN);
-  MDB_REQUIRE(g_opt_stream_kernel == 0 && tc_supported(kTcBf16, m, n, k, ldx, ldy), MDB_ERR_UNSUPPORTED);
+  MDB_REQUIRE(tc_supported(kTcBf16, m, n, k, ldx, ldy), MDB_ERR_UNSUPPORTED);
   TcArgs a = {};
   a.m = m; a.n = n; a.k = k;
   a.y = static_cast<bf16*>(y);
@@ -222,7 +177,7 @@ int mdb_gemm_qkv_rope_commit(const void* x, int64_t ldx, const void* w_qkv, int 
                   mdb_aligned16(q_norm_w) && mdb_aligned16(k_norm_w),
               MDB_ERR_ALIGN);
   const int n = (hq + 2 * hkv) * kHeadDim;
-  MDB_REQUIRE(g_opt_stream_kernel == 0 && tc_supported(kTcQkvRope, m, n, k, ldx, 0), MDB_ERR_UNSUPPORTED);
+  MDB_REQUIRE(tc_supported(kTcQkvRope, m, n, k, ldx, 0), MDB_ERR_UNSUPPORTED);
   TcArgs a = {};
   a.m = m; a.n = n; a.k = k;
   a.hq = hq; a.hkv = hkv; a.max_pos = max_pos;
@@ -262,7 +217,7 @@ int mdb_lmhead_sample(const void* hidden, int64_t ld_hidden, const void* w, int 
   MDB_REQUIRE(workspace_bytes >= lay.total, MDB_ERR_WORKSPACE);
   unsigned char* ws = static_cast<unsigned char*>(workspace);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (use_ws(kWsLmHead, m, vocab, h, ld_hidden)) {
+  if (ws_supported(kWsLmHead, m, vocab, h, ld_hidden)) {
     WsArgs a = {};
     a.m = m; a.n = vocab; a.k = h; a.ksplit = 1;
     a.temperatures = temperatures;
@@ -277,27 +232,8 @@ int mdb_lmhead_sample(const void* hidden, int64_t ld_hidden, const void* w, int 
     if (rc != MDB_OK) return rc;
     return finalize_sampler(a.part_f, a.part_i, vocab / kWsTileRows, m, x0_out, conf_out, st);
   }
-  if (m <= 64) {
-    MDB_REQUIRE(vocab % 32 == 0 && h % 32 == 0, MDB_ERR_UNSUPPORTED);
-    SkinnyArgs a = {};
-    a.x = static_cast<const bf16*>(hidden);
-    a.w = static_cast<const bf16*>(w);
-    a.ldx = ld_hidden;
-    a.m = m; a.n = vocab; a.k = h;
-    a.temperatures = temperatures;
-    a.block = block;
-    a.noise_mode = noise_mode;
-    a.noise = noise;
-    a.seed = seed; a.step = step;
-    a.step_dev = step_dev;
-    a.part_f = reinterpret_cast<float4*>(ws);
-    a.part_i = reinterpret_cast<int*>(ws + lay.off_i);
-    int rc = launch_skinny<kEpiLmHead>(a, 1, st);
-    if (rc != MDB_OK) return rc;
-    return finalize_sampler(a.part_f, a.part_i, vocab / 32, m, x0_out, conf_out, st);
-  }
-  if (g_opt_stream_kernel == 0 && noise_mode != 1 && tc_supported(kTcLmHead, m, vocab, h, ld_hidden, 0)) {
-    // many rows: tcgen05 tile GEMM whose epilogue reduces each 256-column tile to a sampler record
+  if (noise_mode != 1 && tc_supported(kTcLmHead, m, vocab, h, ld_hidden, 0)) {
+    // tile GEMM whose epilogue reduces each 256-column tile to a sampler record
     TcArgs a = {};
     a.m = m; a.n = vocab; a.k = h;
     a.temperatures = temperatures;
@@ -311,19 +247,14 @@ int mdb_lmhead_sample(const void* hidden, int64_t ld_hidden, const void* w, int 
     if (rc != MDB_OK) return rc;
     return finalize_sampler(a.part_f, a.part_i, a.tiles_n, m, x0_out, conf_out, st);
   }
-  MDB_REQUIRE(h % kGemmBK == 0 && vocab % 2 == 0, MDB_ERR_UNSUPPORTED);
+  // an explicit noise tensor with many rows: bf16 logits in the workspace, then the scan
+  MDB_REQUIRE(tc_supported(kTcBf16, m, vocab, h, ld_hidden, vocab), MDB_ERR_UNSUPPORTED);
   bf16* logits = reinterpret_cast<bf16*>(ws + lay.off_logits);
-  int rc;
-  if (g_opt_stream_kernel == 0 && tc_supported(kTcBf16, m, vocab, h, ld_hidden, vocab)) {
-    TcArgs a = {};
-    a.m = m; a.n = vocab; a.k = h;
-    a.y = logits;
-    a.ldy = vocab;
-    rc = launch_tc<kTcBf16>(static_cast<const bf16*>(hidden), ld_hidden, static_cast<const bf16*>(w), vocab, a, st);
-  } else {
-    rc = launch_gemm_tiled(static_cast<const bf16*>(hidden), ld_hidden, static_cast<const bf16*>(w), logits, vocab, m,
-                           vocab, h, st);
-  }
+  TcArgs a = {};
+  a.m = m; a.n = vocab; a.k = h;
+  a.y = logits;
+  a.ldy = vocab;
+  int rc = launch_tc<kTcBf16>(static_cast<const bf16*>(hidden), ld_hidden, static_cast<const bf16*>(w), vocab, a, st);
   if (rc != MDB_OK) return rc;
   return scan_logits(logits, vocab, m, vocab, temperatures, block, noise_mode, noise, seed, step, step_dev, ws, x0_out,
                      conf_out, st);
@@ -351,7 +282,7 @@ int mdb_gemm_splitk_partials_tp(const void* x, int64_t ldx, const void* w, float
                                 int m, int n, int k, int ksplit, uint32_t* peer_flags, uint32_t tag,
                                 const uint32_t* epoch, mdb_stream_t stream) {
   if (m == 0) return MDB_OK;
-  int rc = check_skinny_common(x, ldx, w, m, n, k);
+  int rc = check_short_step(x, ldx, w, m, n, k);
   if (rc != MDB_OK) return rc;
   MDB_REQUIRE(partials && peer_partials && peer_flags && epoch && ksplit >= 1 && ksplit <= 64, MDB_ERR_ARG);
   MDB_REQUIRE(tag >= 1 && tag <= 255, MDB_ERR_ARG);
@@ -390,7 +321,7 @@ int mdb_lmhead_sample_tp(const void* hidden, int64_t ld_hidden, const void* w, i
     // many rows: the tile GEMM over this rank's columns [128 tile_begin, 128 (tile_begin + tile_count)) of the
     // vocabulary, one record per 256-column tile; the shard must start on a 256-column boundary and end on one
     // or at the end of the vocabulary
-    MDB_REQUIRE(noise_mode != 1 && g_opt_stream_kernel == 0 && vocab % 128 == 0, MDB_ERR_UNSUPPORTED);
+    MDB_REQUIRE(noise_mode != 1 && vocab % 128 == 0, MDB_ERR_UNSUPPORTED);
     MDB_REQUIRE(tile_begin >= 0 && tile_count >= 1 && tile_begin % 2 == 0, MDB_ERR_ARG);
     const int64_t col_begin = static_cast<int64_t>(tile_begin) * 128;
     const int64_t col_end = col_begin + static_cast<int64_t>(tile_count) * 128;

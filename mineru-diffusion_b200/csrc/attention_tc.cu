@@ -5,7 +5,7 @@
 //     flash_attn_with_kvcache as nanovllm/layers/sdar_attention.py:50-55 calls it);
 //   * staircase attention over packed sequences (prefill: a query row sees the
 //     keys up to the right edge of its right-aligned block;
-//     nanovllm/layers/block_prefill_attention_v2.py:17-166).
+//     nanovllm/kernels/triton/attention/block_prefill_attention_v2.py:17-166).
 //
 // One work unit = the query rows of `tokens x group` (tokens of one request or
 // sequence times the query heads that share a KV head; row = token * group +
@@ -153,6 +153,7 @@ struct AtUnit {
   int kvh;
   int q_tok0;       // row of the unit's first token in the q tensor
   int req, split, tok0;        // paged: request, key-range part, first token of the block covered
+  bool ctx_clamped;            // paged: the context length exceeded what the page table can address
   int seq_start, m0, T;        // staircase: first packed row of the sequence, first token of the unit, length
 };
 
@@ -192,7 +193,11 @@ __device__ __forceinline__ AtUnit at_unit(const AtArgs& a, const uint16_t* order
   w.tok0 = (rem / a.nsplit) % a.row_blocks * a.tokens_per_unit;
   w.split = rem % a.nsplit;
   w.q_tok0 = w.req * a.block + w.tok0;
-  const int ctx = a.ctx_lens[w.req];
+  int ctx = a.ctx_lens[w.req];
+  // A context longer than the page table's row can address is cut to the row (the producer warp raises
+  // MDB_STATUS_BAD_PAGE for it): no role ever reads the table past the request's row.
+  const int ctx_cap = a.table_stride * kPage;
+  if (ctx > ctx_cap) { ctx = ctx_cap; w.ctx_clamped = true; }
   const int chunk = attn_part_keys(ctx, a.nsplit, kAtKeys);
   w.kbeg = w.split * chunk;
   w.kend = min(ctx, w.kbeg + chunk);
@@ -286,6 +291,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       };
       for (int wave = 0; wave < waves && ok; ++wave) {
         const AtUnit w = at_unit<STAIR>(a, order, units, wave);
+        if (w.ctx_clamped) report_status(MDB_STATUS_BAD_PAGE);
         if (w.ntiles == 0) continue;
         if (!mbar_wait(bar(kAtBarQEmpty + qr.stage), qr.phase ^ 1)) { ok = false; break; }
         {

@@ -365,26 +365,27 @@ int mdb_set_trace(void* buffer, int64_t bytes) {
 
 int mdb_set_option(int option, int value) {
   switch (option) {
-    case MDB_OPT_STREAM_KERNEL: g_opt_stream_kernel = value ? 1 : 0; return MDB_OK;
     case MDB_OPT_PDL: g_opt_pdl = value ? 1 : 0; return MDB_OK;
     case MDB_OPT_GEMM_PAIR:
       if (value < 0 || value > 2) return MDB_ERR_ARG;
       g_opt_gemm_pair = value;
       return MDB_OK;
-    case MDB_OPT_ATTN_KERNEL:
-      if (value < 0 || value > 2) return MDB_ERR_ARG;
-      g_opt_attn_kernel = value;
+    case MDB_OPT_WAIT_LIMIT_US: {
+      if (value < 1) return MDB_ERR_ARG;
+      const unsigned long long ns = static_cast<unsigned long long>(value) * 1000ull;
+      if (cudaMemcpyToSymbol(g_wait_limit_ns, &ns, sizeof(ns)) != cudaSuccess) return MDB_ERR_CUDA;   // current device
+      g_opt_wait_limit_us = value;
       return MDB_OK;
+    }
     default: return MDB_ERR_ARG;
   }
 }
 
 int mdb_get_option(int option) {
   switch (option) {
-    case MDB_OPT_STREAM_KERNEL: return g_opt_stream_kernel;
     case MDB_OPT_PDL: return g_opt_pdl;
-    case MDB_OPT_ATTN_KERNEL: return g_opt_attn_kernel;
     case MDB_OPT_GEMM_PAIR: return g_opt_gemm_pair;
+    case MDB_OPT_WAIT_LIMIT_US: return g_opt_wait_limit_us;
     default: return MDB_ERR_ARG;
   }
 }

@@ -40,7 +40,6 @@ constexpr int kWsBK = 64;                 // k per stage: one 128-byte swizzle a
 constexpr int kWsWTileBytes = kWsTileRows * kWsBK * 2;   // 16 KB
 constexpr int kWsThreads = 192;           // warps 0-3 epilogue, 4 producer, 5 MMA
 constexpr int kWsEpiFloats = kWsTileRows * 33;           // staging tile [128][33] fp32
-constexpr unsigned long long kWsWaitLimitNs = 2000000000ull;   // 2 s: far beyond any legitimate wait of a decode step
 
 struct WsArgs {
   int m, n, k;
@@ -86,7 +85,8 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait for the phase with the given parity; false once kWsWaitLimitNs have passed.
+// Bounded wait for the phase with the given parity; false once the wait limit (2 s by default: far beyond any
+// legitimate wait of a decode step) has passed.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   unsigned long long deadline = 0;
   for (uint32_t it = 0;; ++it) {
@@ -101,7 +101,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     if (done) return true;
     if ((it & 1023u) == 1023u) {
       const unsigned long long now = global_timer_ns();
-      if (deadline == 0) deadline = now + kWsWaitLimitNs;
+      if (deadline == 0) deadline = now + g_wait_limit_ns;
       else if (now > deadline) return false;
     }
   }

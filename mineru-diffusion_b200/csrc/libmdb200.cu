@@ -3,11 +3,9 @@
 // rather than linked as relocatable device code.
 #include "elementwise.cu"
 #include "attention.cu"
-#include "gemm_skinny.cu"
+#include "sampler.cu"
 #include "gemm_ws.cu"
 #include "gemm_tc.cu"
 #include "attention_tc.cu"
-#include "gemm_tiled.cu"
-#include "fused_step.cu"
 #include "api_linear.cu"
 #include "tp_p2p.cu"

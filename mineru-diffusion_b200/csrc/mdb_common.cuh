@@ -24,6 +24,10 @@ __device__ unsigned int g_device_status = 0;  // one definition: the library is 
 
 __device__ __forceinline__ void report_status(unsigned int bit) { atomicOr(&g_device_status, bit); }
 
+// Longest time any wait inside a kernel (mbarrier, peer flag) may last before it gives up with
+// MDB_STATUS_WAIT_TIMEOUT; 2 s unless MDB_OPT_WAIT_LIMIT_US says otherwise.  Read only on the slow path of a wait.
+__device__ unsigned long long g_wait_limit_ns = 2000000000ull;
+
 // ---- programmatic dependent launch ---------------------------------------------
 // Every kernel of the library opens with pdl_launch_dependents() (the next
 // kernel in the stream may be scheduled early, e.g. to prefetch weights) and
@@ -85,7 +89,7 @@ __device__ __forceinline__ void tp_signal(const TpSignal& s) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(s.peer_flags + blockIdx.x), "r"(tp_seq(s)) : "memory");
 }
 
-// Called by every thread of a CTA; returns after all slots show the sequence number or 2 s have passed
+// Called by every thread of a CTA; returns after all slots show the sequence number or the wait limit has passed
 // (then MDB_STATUS_WAIT_TIMEOUT is raised and the kernel carries on with whatever the buffer holds).
 __device__ __forceinline__ void tp_wait(const TpSignal& s) {
   if (s.wait_flags == nullptr) return;
@@ -99,7 +103,7 @@ __device__ __forceinline__ void tp_wait(const TpSignal& s) {
       if ((it & 255u) == 255u) {
         unsigned long long now;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-        if (deadline == 0) deadline = now + 2000000000ull;
+        if (deadline == 0) deadline = now + g_wait_limit_ns;
         else if (now > deadline) { report_status(MDB_STATUS_WAIT_TIMEOUT); break; }
       }
     }
@@ -132,60 +136,9 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
-// ---- memory access helpers -------------------------------------------------
-// 16-byte streaming load that bypasses L1 allocation (weights are read once).
-__device__ __forceinline__ uint4 ldg_stream16(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
-
-// 16-byte read-only load that may stay in L1 (activations re-read by many warps).
-__device__ __forceinline__ uint4 ldg_cached16(const void* p) {
-  return __ldg(reinterpret_cast<const uint4*>(p));
-}
-
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
-
-// cp.async 16 bytes; src_bytes < 16 zero-fills the rest (0 = pure zero fill).
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N));
-}
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-               : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3,
-                                                  uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-               : "r"(addr));
-}
-
-// D(16x8, fp32) += A(16x16, bf16 row) * B(16x8, bf16 col)
-__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                               uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// Tile rows of 128 bytes (64 bf16) or 256 bytes (128 bf16) are stored with
-// their 16-byte chunks XOR-ed by the row index so that the 8 row addresses of
-// one ldmatrix phase fall in 8 distinct bank groups.
-__device__ __forceinline__ int swz_chunk(int row, int chunk) { return chunk ^ (row & 7); }
 
 __device__ __forceinline__ float rcp_approx(float x) {
   float y;
@@ -251,10 +204,9 @@ __device__ __forceinline__ float gumbel_noise(uint32_t seed, uint32_t step, uint
 static inline bool mdb_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // process-wide options (mdb_set_option)
-static int g_opt_stream_kernel = 0;   // 0: tcgen05/TMA streaming kernel where possible, 1: register-streaming kernel
 static int g_opt_pdl = 1;             // programmatic dependent launch between the library's kernels
+static int g_opt_wait_limit_us = 2000000;   // bound of in-kernel waits (mirrors g_wait_limit_ns on the device)
 static int g_opt_gemm_pair = 1;       // many-row GEMMs on CTA pairs (tcgen05.mma.cta_group::2): 1 from 2048 rows, 2 from 256, 0 never
-static int g_opt_attn_kernel = 0;     // block attention: 0 = by size, 1 = mma.sync kernel, 2 = tcgen05 kernel where it applies
 
 // Launch with the programmatic-stream-serialization attribute when enabled.
 template <typename... KArgs, typename... Args>

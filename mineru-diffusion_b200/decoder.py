@@ -10,7 +10,7 @@ K/V of the step written into the paged cache on the way.  Per layer it issues
 For steps of at most 64 rows the GEMMs are the weight-streaming kernels: they
 leave fp32 split-k slices that the *next* kernel sums, rounds to bf16 and
 consumes, so no stand-alone reduction or activation pass exists.  Longer
-steps (prefill, big decode batches) use the tiled GEMM with bf16 outputs.
+steps (prefill, big decode batches) use the tile GEMM with fused epilogues.
 All buffers are allocated once here; a step allocates nothing, which is what
 lets the decode step be captured in a CUDA graph.
 """
@@ -148,15 +148,12 @@ class DecoderEngine:
         if t > SKINNY_MAX_ROWS:
             self.qkv_out = buf(t, self.nqkv)
             self.h_out = buf(t, h)
-            self.gu_out = buf(t, 2 * i)
         self.max_nsplit = 64
         ws = ops._lib.lib().mdb_attn_paged_workspace_bytes(max_seqs, block_size, hq, self.max_nsplit)
         # attention partials are only needed while CTAs are scarce: cap at what 64 requests use
         ws = min(ws, ops._lib.lib().mdb_attn_paged_workspace_bytes(min(max_seqs, 64), block_size, hq, self.max_nsplit))
         self.attn_ws = buf(max(int(ws), 16), dtype=torch.uint8)
         self.lm_ws = buf(max(ops.lmhead_workspace_bytes(max_seqs * block_size, cfg.vocab_size), 16), dtype=torch.uint8)
-        self.grid_bar = torch.zeros(4, dtype=torch.int32, device=dev)   # grid barrier words of the one-kernel step
-        self._fused_keep: list = []
         self.x0 = buf(max_seqs * block_size, dtype=torch.int32)
         self.conf = buf(max_seqs * block_size, dtype=torch.float32)
 
@@ -218,77 +215,11 @@ class DecoderEngine:
                                             out=attn.view(bs, self.block_size, hq, d))
             prev = self._row_gemm(0, attn.view(m, hq * d), lw.o, m, li)
             self._add_norm(prev, res, lw.post_ln, eps, x)
-            if skinny or (inter % 128 == 0 and h % 64 == 0 and ops.get_option(ops.OPT_STREAM_KERNEL) == 0):
-                ops.gateup_swiglu(x, lw.gate_up, out=act)
-            else:
-                gu = self.gu_out[:m]
-                ops.linear(x, lw.gate_up, out=gu)
-                ops.silu_and_mul(gu, out=act)
+            ops.gateup_swiglu(x, lw.gate_up, out=act)
             prev = self._row_gemm(1, act, lw.down, m, li)
         out = self.final[:m]
         self._add_norm(prev, res, self.w.final_ln, eps, out)
         return out
-
-    # ------------------------------------------------------------------ whole step as one kernel
-    def fused_supported(self, m: int) -> bool:
-        cfg = self.cfg
-        nqkv = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
-        return (self.tp_size == 1 and 1 <= m <= SKINNY_MAX_ROWS and cfg.hidden_size % 128 == 0
-                and cfg.hidden_size <= 8192 and nqkv % 128 == 0 and cfg.intermediate_size % 64 == 0
-                and cfg.vocab_size % 128 == 0 and len(self.w.layers) <= 64
-                and ops.get_option(ops.OPT_STREAM_KERNEL) == 0)
-
-    def build_fused_step(self, bs: int, nsplit: int, ids, positions, slots, ctx_lens, block_tables, temperatures,
-                         seed: int | None, step_dev):
-        """Descriptor of the one-kernel decode step for ``bs`` requests reading its
-        per-step inputs from the given (static) device tensors.  Returns a device
-        buffer to pass to ``run_fused_step``."""
-        import ctypes as C
-        lib = ops._lib.lib()
-        cfg = self.cfg
-        m = bs * self.block_size
-        L = len(self.w.layers)
-        P = ops._lib.FusedStepParams()
-
-        def arr(tensors):
-            a = (C.c_void_p * L)(*[t.data_ptr() for t in tensors])
-            self._fused_keep.append(a)
-            return C.cast(a, C.POINTER(C.c_void_p))
-
-        P.layers, P.m, P.bs, P.block = L, m, bs, self.block_size
-        P.hidden, P.inter, P.hq, P.hkv, P.vocab = (cfg.hidden_size, cfg.intermediate_size, cfg.num_attention_heads,
-                                                  cfg.num_key_value_heads, cfg.vocab_size)
-        P.ks_qkv, P.ks_o, P.ks_down, P.nsplit = self.ks_qkv, self.ks_o, self.ks_down, nsplit
-        P.eps, P.softmax_scale = cfg.rms_norm_eps, self.scale
-        P.w_qkv = arr([l.qkv for l in self.w.layers]); P.w_o = arr([l.o for l in self.w.layers])
-        P.w_gate_up = arr([l.gate_up for l in self.w.layers]); P.w_down = arr([l.down for l in self.w.layers])
-        P.ln1 = arr([l.input_ln for l in self.w.layers]); P.ln2 = arr([l.post_ln for l in self.w.layers])
-        P.q_norm = arr([l.q_norm for l in self.w.layers]); P.k_norm = arr([l.k_norm for l in self.w.layers])
-        P.k_cache = arr([self.kv_cache[0, i] for i in range(L)]); P.v_cache = arr([self.kv_cache[1, i] for i in range(L)])
-        P.final_ln, P.embed_table, P.embed_rows = self.w.final_ln.data_ptr(), self.w.embed.data_ptr(), self.w.embed.shape[0]
-        P.lm_head = self.w.lm_head.data_ptr()
-        P.x, P.res, P.q, P.attn = self.x.data_ptr(), self.res.data_ptr(), self.q.data_ptr(), self.attn.data_ptr()
-        P.act, P.final_rows, P.parts = self.act.data_ptr(), self.final.data_ptr(), self.partials.data_ptr()
-        P.attn_ws = self.attn_ws.data_ptr()
-        P.rope, P.max_pos = self.rope.data_ptr(), self.rope.shape[0]
-        P.ids, P.positions, P.slots = ids.data_ptr(), positions.data_ptr(), slots.data_ptr()
-        P.ctx_lens, P.block_table = ctx_lens.data_ptr(), block_tables.data_ptr()
-        P.table_stride, P.num_pages = block_tables.stride(0), self.num_pages
-        P.num_slots = self.num_pages * PAGE
-        P.temperatures = temperatures.data_ptr()
-        P.noise_mode, P.seed = (2, seed & 0xFFFFFFFF) if seed is not None else (0, 0)
-        P.step_dev = None if step_dev is None else step_dev.data_ptr()
-        P.lm_ws, P.x0, P.conf = self.lm_ws.data_ptr(), self.x0.data_ptr(), self.conf.data_ptr()
-        P.grid_bar = self.grid_bar.data_ptr()
-        desc = torch.empty(int(lib.mdb_fused_step_desc_bytes()), dtype=torch.uint8, device=self.device)
-        ops._lib.check(lib.mdb_fused_step_create(C.byref(P), desc.data_ptr()), "mdb_fused_step_create")
-        return desc
-
-    def run_fused_step(self, desc: torch.Tensor, m: int) -> torch.Tensor:
-        ops._lib.check(ops._lib.lib().mdb_fused_step_launch(desc.data_ptr(), self.grid_bar.data_ptr(), m,
-                                                            torch.cuda.current_stream().cuda_stream),
-                       "mdb_fused_step_launch")
-        return self.final[:m]
 
     # ------------------------------------------------------------------ row-parallel projections
     def attach_tp(self, pair, epoch_word: torch.Tensor):
@@ -314,8 +245,9 @@ class DecoderEngine:
             return ("tp", view, wait_ptr, ops.tp_grid_size(m, h, x_in.shape[1], ks), tag)
         ho = self.h_out[:m]
         k = x_in.shape[1]
-        if (self.tp is not None and m <= self.tp.many_rows and k % 64 == 0 and h % 8 == 0
-                and ops.get_option(ops.OPT_STREAM_KERNEL) == 0):
+        if self.tp is not None:
+            if m > self.tp.many_rows:
+                raise RuntimeError(f"step of {m} rows exceeds the tensor-parallel landing buffers ({self.tp.many_rows} rows)")
             # the all-reduce rides in the GEMM epilogue: every tile goes to the local output and, over NVLink,
             # to the peer's landing buffer; the following norm adds the two
             land, peer_ptr = self.tp.landing(which, m)
@@ -324,9 +256,6 @@ class DecoderEngine:
             slots = ops.linear_tp_rows(x_in, w, ho, peer_ptr, signal_ptr, tag, self.tp_epoch)
             return ("tp_rows", ho, land, wait_ptr, slots, tag)
         ops.linear(x_in, w, out=ho)
-        if self.tp_size > 1:
-            # shapes the tile kernel does not take keep the reference's collective: bf16 partial outputs summed by NCCL
-            torch.distributed.all_reduce(ho)
         return ("bf16", ho)
 
     def _add_norm(self, prev, res: torch.Tensor, ln: torch.Tensor, eps: float, out: torch.Tensor):
@@ -358,7 +287,7 @@ class DecoderEngine:
             # Many-row steps: the tile GEMM over half of the 256-column vocabulary tiles per rank, one sampler
             # record per tile mirrored into the peer's workspace; logits are never gathered.
             vocab = self.cfg.vocab_size
-            can_split = (noise is None and vocab % 128 == 0 and ops.get_option(ops.OPT_STREAM_KERNEL) == 0
+            can_split = (noise is None and vocab % 128 == 0
                          and ws.numel() >= lib.mdb_lmhead_tp_workspace_bytes(m, vocab))
             if not can_split:
                 # both ranks hold the whole LM head and bit-identical hidden rows: each scans all of it

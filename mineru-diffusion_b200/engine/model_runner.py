@@ -23,7 +23,7 @@ import torch
 
 from .. import ops
 from ..decoder import DecoderEngine, DecoderWeights
-from .config import Config
+from .config import Config, DecoderConfig
 from .context import Context
 from .sequence import Sequence
 from .step_inputs import build_decode_inputs, build_prefill_inputs, fill_decode_inputs_small
@@ -91,8 +91,7 @@ class _NextBlock:
 class ModelRunner:
 
     def __init__(self, config: Config, rank: int = 0, event=None, weights: DecoderWeights | None = None,
-                 weight_seed: int = 20260320, noise: str = "gumbel", noise_seed: int = 0, device: str | None = None,
-                 fused_step: bool | None = None):
+                 weight_seed: int = 20260320, noise: str = "gumbel", noise_seed: int = 0, device: str | None = None):
         if not torch.cuda.is_available():
             raise RuntimeError("ModelRunner needs a CUDA device: the decode path has no CPU implementation")
         if config.tensor_parallel_size not in (1, 2):
@@ -110,7 +109,7 @@ class ModelRunner:
         self.enforce_eager = config.enforce_eager
         self.device = torch.device(device or f"cuda:{rank}")
         torch.cuda.set_device(self.device)
-        self.full_dcfg = config.decoder_config
+        self.full_dcfg = self._decoder_config(config)
         self.dcfg = self.full_dcfg
         full = weights if weights is not None else DecoderWeights.random_init(self.full_dcfg, weight_seed, self.device)
         if self.world_size == 2:
@@ -127,11 +126,6 @@ class ModelRunner:
             self.weights = full
         self.noise = noise
         self.noise_seed = noise_seed
-        # one persistent kernel per decode step (steps of at most 64 rows, one GPU); MDB_FUSED_STEP=0/1 overrides
-        if fused_step is None:
-            fused_step = os.environ.get("MDB_FUSED_STEP", "0") == "1"
-        self.fused_step = bool(fused_step)
-        self.fused_desc: dict[tuple[int, int], torch.Tensor] = {}
         self.noise_fn = None          # explicit mode: fn(step_index, m, vocab) -> fp32 [m, vocab] CUDA tensor
         self.step_index = 0
         self.allocate_kv_cache()
@@ -162,8 +156,11 @@ class ModelRunner:
             self.engine.attach_tp(self.tp_pair, self.dv["step"][1:2])
         # sampler state: one flat device buffer and its pinned mirror, laid out per batch size as
         # ids int64 [bs, B] | counts int32 [bs] | transfer u8 [bs, B], so the results of a step come back in one copy
-        self.res_dev = torch.zeros(self.max_bs * (9 * b + 4), dtype=torch.uint8, device=self.device)
-        self.res_host = torch.zeros(self.max_bs * (9 * b + 4), dtype=torch.uint8, pin_memory=True)
+        # ... followed by the device status word of the step (4 bytes)
+        self.res_dev = torch.zeros(self.max_bs * (9 * b + 4) + 4, dtype=torch.uint8, device=self.device)
+        self.res_host = torch.zeros(self.max_bs * (9 * b + 4) + 4, dtype=torch.uint8, pin_memory=True)
+        self.quota_host = torch.ones(self.max_bs, dtype=torch.int32, pin_memory=True)
+        self.quota_dev = torch.ones(self.max_bs, dtype=torch.int32, device=self.device)
         self._res_views: dict[int, tuple] = {}
         self._decode_key = None       # lengths and page counts the pinned step inputs were last built for
         self._decode_seqs: list = []  # ... and the requests themselves
@@ -176,6 +173,29 @@ class ModelRunner:
         self.step_events = None       # benchmark: (start, end) CUDA events around the GPU work of a step
         if not self.enforce_eager:
             self.capture_cudagraph()
+
+    @staticmethod
+    def _decoder_config(config) -> DecoderConfig:
+        """Decoder dimensions of a ``Config``: this package's ``decoder_config`` field, or what the reference's
+        ``Config`` carries instead (``hf_config.language_model_config`` / ``text_config`` read from config.json,
+        ``nanovllm/config.py:16-31,56-59``)."""
+        dcfg = getattr(config, "decoder_config", None)
+        if dcfg is not None:
+            return dcfg
+        hf = getattr(config, "hf_config", None)
+        text = None
+        for name in ("language_model_config", "text_config"):
+            text = getattr(hf, name, None) if hf is not None else None
+            if text is not None:
+                break
+        if text is None:
+            text = hf
+        if text is None:
+            raise AssertionError("the config names no decoder dimensions (decoder_config or hf_config)")
+        if isinstance(text, dict):
+            from types import SimpleNamespace
+            text = SimpleNamespace(**text)
+        return DecoderConfig.from_namespace(text)
 
     # ------------------------------------------------------------------ control plane
     def call(self, method_name, *args):
@@ -222,7 +242,7 @@ class ModelRunner:
     def _result_views(self, bs: int):
         """Views of the sampler-state buffers for a step of ``bs`` requests:
         (device bytes, pinned bytes, device ids/counts/transfer, pinned ids and numpy views of the pinned
-        counts/transfer)."""
+        counts/transfer, device status word, numpy view of its pinned copy)."""
         v = self._res_views.get(bs)
         if v is None:
             b = self.block_size
@@ -230,7 +250,9 @@ class ModelRunner:
             def split(buf):
                 return (buf[:o1].view(torch.int64).view(bs, b), buf[o1:o2].view(torch.int32), buf[o2:o3].view(bs, b))
             host = split(self.res_host)
-            v = (self.res_dev[:o3], self.res_host[:o3]) + split(self.res_dev) + (host[0], host[1].numpy(), host[2].numpy())
+            v = ((self.res_dev[:o3 + 4], self.res_host[:o3 + 4]) + split(self.res_dev)
+                 + (host[0], host[1].numpy(), host[2].numpy())
+                 + (self.res_dev[o3:o3 + 4].view(torch.int32), self.res_host[o3:o3 + 4].view(torch.int32).numpy()))
             self._res_views[bs] = v
         return v
 
@@ -306,15 +328,6 @@ class ModelRunner:
         b = self.block_size
         m = bs * b
         dv, eng = self.dv, self.engine
-        if self.fused_step and self.noise != "explicit" and eng.fused_supported(m):
-            key = (bs, nsplit)
-            if key not in self.fused_desc:
-                if torch.cuda.is_current_stream_capturing():
-                    raise RuntimeError("the one-kernel step must be built before stream capture")
-                self.fused_desc[key] = eng.build_fused_step(
-                    bs, nsplit, dv["ids"], dv["pos"], dv["slots"], dv["ctx"], dv["tab"], dv["temp"],
-                    self.noise_seed if self.noise == "gumbel" else None, dv["step"])
-            return eng.run_fused_step(self.fused_desc[key], m)
         ops.gather_rows(self.weights.embed, dv["ids"][:bs].reshape(-1), out=eng.embeds[:m])
         ctx = Context(False, slot_mapping=dv["slots"][:bs], context_lens=dv["ctx"][:bs],
                       block_tables=dv["tab"][:bs], block_size=b)
@@ -354,8 +367,8 @@ class ModelRunner:
             self.dv["step"].copy_(self.hv["step"], non_blocking=True)
         ops.gather_rows(self.weights.embed, input_ids, out=eng.embeds[:m])
         for i, seq in enumerate(seqs):
-            if seq.inputs_embeds is not None and seq.num_cached_tokens == 0:
-                rows = seq.inputs_embeds
+            rows = getattr(seq, "inputs_embeds", None)      # the reference's Sequence has no such attribute
+            if rows is not None and seq.num_cached_tokens == 0:
                 eng.embeds[cu[i]:cu[i] + rows.shape[0]].copy_(rows.to(self.device, non_blocking=True))
         hidden = eng.forward(m, positions, ctx, max_seqlen=ctx.max_seqlen_q)
         # the LM head sees the last B rows of every sequence (embed_head.py:63-66 of the reference)
@@ -385,7 +398,8 @@ class ModelRunner:
         with torch.inference_mode():
             # sampler state: the host copy of each block is the source of truth, as in the reference
             # (a decode step has just sent those ids down as its input)
-            d_all, h_all, d_ids, d_counts, d_transfer, h_ids, h_counts, h_transfer = self._result_views(bs)
+            (d_all, h_all, d_ids, d_counts, d_transfer, h_ids, h_counts, h_transfer, d_status,
+             h_status) = self._result_views(bs)
             if is_prefill:
                 torch.stack([seq.current_denoising_block for seq in seqs], out=h_ids)
                 d_ids.copy_(h_ids, non_blocking=True)
@@ -394,12 +408,11 @@ class ModelRunner:
             sp = seqs[0].sampling_params
             if sp.denoising_strategy != "low_confidence_dynamic":
                 raise NotImplementedError(f"Denoising strategy {sp.denoising_strategy} not implemented")
-            quota = 1
-            if sp.denoising_steps:
-                quota = max(1, b // sp.denoising_steps)
+            quotas = self._step_quotas(seqs, is_prefill)
             m = bs * b
             ops.unmask_decide(d_ids, self.engine.x0[:m], self.engine.conf[:m], seqs[0].mask_token_id,
-                              sp.dynamic_threshold, quota, transfer=d_transfer, counts=d_counts)
+                              sp.dynamic_threshold, 1, transfer=d_transfer, counts=d_counts, quotas=quotas,
+                              status_out=d_status)
             if self.step_events is not None and not is_prefill:
                 self.step_events[1].record()
             h_all.copy_(d_all, non_blocking=True)
@@ -407,6 +420,12 @@ class ModelRunner:
                 self.last = dict(x0=self.engine.x0[:m].clone(), conf=self.engine.conf[:m].clone(),
                                  hidden=None if hidden is None else hidden.clone())
             torch.cuda.current_stream().synchronize()
+        status = int(h_status[0])
+        if status:
+            # a kernel of this step skipped an access or gave up a wait (bad slot / page / token id / position,
+            # or a bounded wait that ran out): the step's tokens cannot be trusted.  The word is already cleared.
+            raise RuntimeError(f"decode step {self.step_index}: device status word {status:#x} "
+                               "(1 bad slot, 2 bad page, 4 bad token id, 8 bad position, 16 wait timed out)")
         # one copy of the results for the whole batch; every request keeps a row of it
         blocks = h_ids.clone()
         rows = blocks.unbind(0)
@@ -423,6 +442,30 @@ class ModelRunner:
         self._last_rows, self._last_blocks = rows, blocks.numpy()   # shares memory with the rows
         self.step_index += 1
         return int(h_counts.sum())
+
+    def _step_quotas(self, seqs, is_prefill: bool):
+        """Per-request quota of this pass, or None for the nano engine's rule (one token unless more pass the
+        threshold, ``nanovllm/layers/sampler.py:44-50``).  With ``SamplingParams.denoising_steps`` set (a field
+        of this package, absent from the reference's class) a block follows the HF twin's schedule: pass ``s``
+        of a block takes ``num_transfer_tokens[min(s, steps - 1)]``
+        (``mineru_diffusion/modeling_mineru_diffusion.py:617-623,712``)."""
+        steps = getattr(seqs[0].sampling_params, "denoising_steps", None)
+        if not steps:
+            return None
+        b = self.block_size
+        table = ops.num_transfer_tokens(b, int(steps))
+        q = self.quota_host.numpy()
+        for i, seq in enumerate(seqs):
+            owner = seq.seq if type(seq) is _NextBlock else seq
+            start = len(seq)
+            # passes made on the block that starts at this length, kept on the request object itself
+            at, done = getattr(owner, "_block_passes", (-1, 0))
+            if at != start:
+                done = 0
+            q[i] = table[min(done, len(table) - 1)]
+            owner._block_passes = (start, done + 1)
+        self.quota_dev[:len(seqs)].copy_(self.quota_host[:len(seqs)], non_blocking=True)
+        return self.quota_dev
 
     def _next_block_ready(self, seq: Sequence) -> bool:
         """True when the request being committed goes on to another block (the finishing rule of
@@ -444,16 +487,11 @@ class ModelRunner:
             nsplit = self.graphs[next(x for x in self.graph_bs if x >= bs)][1]
         else:
             nsplit = self.engine.attn_nsplit(bs, self.config.max_model_len)
-        if self.fused_step and self.noise != "explicit" and self.engine.fused_supported(bs * self.block_size):
-            return 2            # the one-kernel step and the unmask rule
         per_layer = 8 + (1 if nsplit > 1 else 0)
         m = bs * self.block_size
         if m > 64:
             if ops.qkv_rope_commit_supported(m, self.dcfg.hidden_size):
                 per_layer -= 1  # q/k norm, rotary embedding and KV store run in the qkv GEMM's epilogue
-            if not (self.dcfg.intermediate_size % 128 == 0 and self.dcfg.hidden_size % 64 == 0
-                    and ops.get_option(ops.OPT_STREAM_KERNEL) == 0):
-                per_layer += 1  # stand-alone SiLU*mul on the mma.sync path
         return 1 + self.dcfg.num_hidden_layers * per_layer + 1 + 2 + 1
 
     # ------------------------------------------------------------------ CUDA graphs

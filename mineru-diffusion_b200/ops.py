@@ -37,10 +37,9 @@ def _rows(t: torch.Tensor, name: str) -> int:
     return t.stride(0)
 
 
-OPT_STREAM_KERNEL = 0   # 0: tcgen05/TMA streaming kernel for short steps (default), 1: register-streaming kernel
 OPT_PDL = 1             # programmatic dependent launch between kernels (default on)
-OPT_ATTN_KERNEL = 2     # block attention kernel: 0 by size (default), 1 mma.sync, 2 tcgen05/TMA where the shape allows
 OPT_GEMM_PAIR = 3       # many-row GEMMs on CTA pairs (tcgen05.mma.cta_group::2): 1 from 2048 rows (default), 2 from 256, 0 never
+OPT_WAIT_LIMIT_US = 4   # bound of every in-kernel wait in microseconds (default 2 s); expiry raises status bit 16
 
 
 def set_option(option: int, value: int) -> None:
@@ -307,7 +306,7 @@ def qknorm_rope_commit(qkv: torch.Tensor | None, positions: torch.Tensor, rope_t
 
 def qkv_rope_commit_supported(m: int, k: int) -> bool:
     """Whether ``qkv_proj_rope_commit`` takes this step: many rows, on the tcgen05 kernels."""
-    return m > 64 and k % 64 == 0 and get_option(OPT_STREAM_KERNEL) == 0
+    return m > 64 and k % 64 == 0
 
 
 def qkv_proj_rope_commit(x: torch.Tensor, w_qkv: torch.Tensor, positions: torch.Tensor, rope_table: torch.Tensor,
@@ -418,22 +417,41 @@ def gumbel_noise(m: int, vocab: int, seed: int, step: int, device) -> torch.Tens
 
 
 def unmask_decide(block_ids: torch.Tensor, x0: torch.Tensor, conf: torch.Tensor, mask_id: int, threshold: float,
-                  quota: int = 1, transfer: torch.Tensor | None = None, counts: torch.Tensor | None = None):
+                  quota: int = 1, transfer: torch.Tensor | None = None, counts: torch.Tensor | None = None,
+                  quotas: torch.Tensor | None = None, status_out: torch.Tensor | None = None):
     """The unmask rule of ``Sampler.forward`` (nanovllm/layers/sampler.py:28-54)
     applied in place to block_ids int64 [bs, B]; returns (transfer uint8
-    [bs, B], counts int32 [bs])."""
+    [bs, B], counts int32 [bs]).  ``quotas`` int32 [bs] gives every request its own
+    quota (the HF twin's schedule, mineru_diffusion/modeling_mineru_diffusion.py:617-623).  ``status_out``
+    (int32 [1], device) receives the device status word and clears it."""
     _need(block_ids, torch.int64, "block_ids")
     _need(x0, torch.int32, "x0")
     _need(conf, torch.float32, "conf")
     bs, block = block_ids.shape
+    if quotas is not None:
+        _need(quotas, torch.int32, "quotas")
+        if quotas.numel() < bs or not quotas.is_contiguous():
+            raise ValueError("quotas must be a contiguous int32 tensor with one entry per request")
     if transfer is None:
         transfer = torch.empty((bs, block), dtype=torch.uint8, device=block_ids.device)
     if counts is None:
         counts = torch.empty(bs, dtype=torch.int32, device=block_ids.device)
     _lib.check(_lib.lib().mdb_unmask_decide(block_ids.data_ptr(), x0.data_ptr(), conf.data_ptr(), bs, block,
-                                            int(mask_id), float(threshold), int(quota), transfer.data_ptr(),
-                                            counts.data_ptr(), _stream()), "mdb_unmask_decide")
+                                            int(mask_id), float(threshold), int(quota), _ptr(quotas),
+                                            transfer.data_ptr(), counts.data_ptr(), _ptr(status_out), _stream()),
+               "mdb_unmask_decide")
     return transfer, counts
+
+
+def num_transfer_tokens(block_length: int, steps: int) -> list[int]:
+    """Quota of every denoising step of a block, ``get_num_transfer_tokens`` of the HF twin
+    (mineru_diffusion/modeling_mineru_diffusion.py:617-623): ``block_length // steps`` tokens per step and
+    one more in each of the first ``block_length % steps`` steps.  Step ``s`` of a block uses entry
+    ``min(s, steps - 1)`` (:712)."""
+    if steps < 1:
+        raise ValueError("denoising_steps must be positive")
+    base, rem = divmod(block_length, steps)
+    return [base + (1 if s < rem else 0) for s in range(steps)]
 
 
 # -------------------------------------------------------------------------- tensor-parallel pair

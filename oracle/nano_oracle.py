@@ -242,26 +242,39 @@ def sampler_prepare(logits: torch.Tensor, temperatures: torch.Tensor, gumbel: to
     return x0, x0_p
 
 
-def unmask_decision(blocks: torch.Tensor, x0: torch.Tensor, x0_p: torch.Tensor, mask_id: int, threshold: float):
+def unmask_decision(blocks: torch.Tensor, x0: torch.Tensor, x0_p: torch.Tensor, mask_id: int, threshold: float,
+                    quotas=None):
     """NV/layers/sampler.py:28-54.  blocks [bs, B] int64 current block ids.
-    Returns (new blocks, transfer mask [bs, B] bool)."""
+    Returns (new blocks, transfer mask [bs, B] bool).  ``quotas`` (one int per request) switches a request to
+    the HF twin's rule (mineru_diffusion/modeling_mineru_diffusion.py:518-532): the positions above the
+    threshold if at least ``quota`` of them, else the ``quota`` most confident masked positions (all masked
+    positions when fewer are left -- below that the reference's topk picks among -inf entries in an order
+    torch leaves unspecified)."""
     mask_index = blocks == mask_id
     confidence = torch.where(mask_index, x0_p, torch.full_like(x0_p, -torch.inf))
     transfer = torch.zeros_like(x0, dtype=torch.bool)
     for j in range(confidence.shape[0]):
         if not mask_index[j].any():
             continue
+        quota = 1 if quotas is None else int(quotas[j])
         hi = confidence[j] > threshold
-        if int(hi.sum()) >= 1:
+        if int(hi.sum()) >= quota:
             transfer[j] = hi
         else:
-            # top-1; the lowest index wins an exact tie
-            best = confidence[j].max()
-            idx = int((confidence[j] == best).nonzero()[0, 0])
-            transfer[j, idx] = True
+            # top-quota by confidence; the lowest index wins an exact tie
+            order = sorted(range(confidence.shape[1]), key=lambda i: (-float(confidence[j, i]), i))
+            for i in order[:quota]:
+                if bool(mask_index[j, i]):
+                    transfer[j, i] = True
     out = blocks.clone()
     out[transfer] = x0[transfer]
     return out, transfer
+
+
+def num_transfer_tokens(block_length: int, steps: int) -> list[int]:
+    """Quota of each denoising step of a block, mineru_diffusion/modeling_mineru_diffusion.py:617-623."""
+    base, rem = divmod(block_length, steps)
+    return [base + (1 if s < rem else 0) for s in range(steps)]
 
 
 # --------------------------------------------------------------------------
@@ -404,15 +417,20 @@ class Decoder:
         hidden, _ = add_rms_norm(hidden, residual, self.w.final_ln, eps)
         return hidden
 
-    def compute_logits(self, hidden: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        """NV/layers/embed_head.py:61-72: prefill keeps the last B rows of every
-        sequence; logits are rounded to the storage dtype."""
+    def compute_rows(self, hidden: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        """The rows the LM head sees (NV/layers/embed_head.py:63-66): in prefill the
+        last B rows of every sequence, otherwise every row."""
         if ctx.is_prefill:
             b = ctx.block_size
             starts = ctx.cu_seqlens_q[1:].long() - b
             idx = starts.unsqueeze(1) + torch.arange(b)
             hidden = hidden[idx].contiguous()
-        return linear(hidden, self.w.lm_head)
+        return hidden
+
+    def compute_logits(self, hidden: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        """NV/layers/embed_head.py:61-72: prefill keeps the last B rows of every
+        sequence; logits are rounded to the storage dtype."""
+        return linear(self.compute_rows(hidden, ctx), self.w.lm_head)
 
 
 # --------------------------------------------------------------------------
@@ -435,6 +453,7 @@ class OracleModelRunner:
         self.prompt_embeds = prompt_embeds or {}
         self.step_index = 0
         self.last: dict = {}
+        self._block_passes: dict = {}    # seq_id -> (length at block start, passes made on the block)
 
     # NV/engine/model_runner.py:127-167
     def prepare_prefill(self, seqs):
@@ -488,7 +507,19 @@ class OracleModelRunner:
         x0, x0_p = sampler_prepare(logits, temps, noise)
         blocks = torch.stack([seq.current_denoising_block for seq in seqs], dim=0)
         thr = seqs[0].sampling_params.dynamic_threshold
-        new_blocks, transfer = unmask_decision(blocks, x0, x0_p, seqs[0].mask_token_id, thr)
+        quotas = None
+        steps = getattr(seqs[0].sampling_params, "denoising_steps", None)
+        if steps:
+            # pass s of a block takes num_transfer_tokens[min(s, steps - 1)] (modeling_mineru_diffusion.py:712)
+            table = num_transfer_tokens(self.block_size, int(steps))
+            quotas = []
+            for seq in seqs:
+                at, done = self._block_passes.get(seq.seq_id, (-1, 0))
+                if at != len(seq):
+                    done = 0
+                quotas.append(table[min(done, len(table) - 1)])
+                self._block_passes[seq.seq_id] = (len(seq), done + 1)
+        new_blocks, transfer = unmask_decision(blocks, x0, x0_p, seqs[0].mask_token_id, thr, quotas)
         for i, seq in enumerate(seqs):
             seq.current_denoising_block = new_blocks[i]
             seq.current_step_map[transfer[i]] = seq.current_denoise_step

@@ -3,7 +3,7 @@ own modules on seeded inputs.
 
 Run in a container that has the reference checkout:
 
-    TORCHDYNAMO_DISABLE=1 TRITON_INTERPRET=1 python tests/golden/make_golden.py /path/to/reference
+    TORCHDYNAMO_DISABLE=1 TRITON_INTERPRET=1 python tests/golden/make_golden.py /path/to/reference [fixture ...]
 
 The reference's nano_dvlm layers are imported unchanged and run on CPU.  What
 cannot run on a CPU is replaced by a shim *in this script only*:
@@ -438,9 +438,75 @@ def gen_decoder():
     save("decoder_tiny.npz", **rec)
 
 
+# ---------------------------------------------------------------- 6. HF twin: quota rule and schedule
+def gen_hf_twin():
+    """``_select_transfer_index`` and ``get_num_transfer_tokens`` of the HF twin
+    (mineru_diffusion/modeling_mineru_diffusion.py:518-532,617-623) on seeded confidences.  Cases keep at
+    least ``count`` masked positions and distinct confidences: below that the reference's ``topk`` picks among
+    -inf entries in an unspecified order."""
+    from mineru_diffusion.modeling_mineru_diffusion import SDARForCausalLM as HFModel
+    g = torch.Generator().manual_seed(31)
+    rec = {}
+    sched = [(32, 32), (32, 8), (32, 5), (32, 3), (16, 5), (64, 48), (8, 3), (32, 64)]
+    rec["sched_pairs"] = np.array(sched)
+    for b, steps in sched:
+        rec[f"sched_{b}_{steps}"] = HFModel.get_num_transfer_tokens(b, steps).numpy()
+    cases = []
+    for block, count, n_masked, boost in [(32, 1, 32, 0), (32, 4, 20, 0), (32, 7, 7, 0), (32, 4, 20, 6), (32, 4, 20, 2),
+                                          (16, 3, 9, 0), (64, 2, 40, 1), (8, 3, 8, 0), (32, 6, 32, 6)]:
+        bs = 5
+        conf = torch.rand(bs, block, generator=g) * 0.85            # below the threshold
+        masked = torch.zeros(bs, block, dtype=torch.bool)
+        for r in range(bs):
+            masked[r, torch.randperm(block, generator=g)[:n_masked]] = True
+            if boost:
+                idx = masked[r].nonzero().flatten()
+                pick = idx[torch.randperm(idx.numel(), generator=g)[:boost]]
+                conf[r, pick] = 0.9 + 0.09 * torch.rand(boost, generator=g) + 1e-3
+        confidence = torch.where(masked, conf, torch.full_like(conf, -torch.inf))
+        transfer = HFModel._select_transfer_index(None, confidence, 0.9, count)
+        cases.append((block, count))
+        i = len(cases) - 1
+        rec[f"q{i}_conf"] = conf
+        rec[f"q{i}_masked"] = masked
+        rec[f"q{i}_count"] = np.array(count)
+        rec[f"q{i}_transfer"] = transfer
+    rec["num_cases"] = np.array(len(cases))
+    rec["threshold"] = np.array(0.9)
+    save("hf_twin.npz", **rec)
+
+
+# ---------------------------------------------------------------- 7. attribute sets of the boundary's objects
+def gen_api_surface():
+    """What a caller that uses the reference's own classes hands to ``ModelRunner``: the attribute names of
+    ``Sequence``, ``SamplingParams`` and ``Config`` (nanovllm/engine/sequence.py:19-60,
+    nanovllm/sampling_params.py:4-15, nanovllm/config.py:33-60) with the defaults of the dataclasses."""
+    import dataclasses
+    import json
+    from nanovllm.config import Config as RefConfig
+    sp = SamplingParams()
+    seq = Sequence([1, 2, 3], sp, denoising_block_size=32, mask_token_id=151669)
+    out = {
+        "sequence_attributes": sorted(vars(seq)),
+        "sequence_class_attributes": sorted(k for k, v in vars(Sequence).items()
+                                            if not k.startswith("__") and not callable(v) and not isinstance(v, property)),
+        "sequence_properties": sorted(k for k, v in vars(Sequence).items() if isinstance(v, property)),
+        "sequence_methods": sorted(k for k, v in vars(Sequence).items() if callable(v)),
+        "sampling_params": {f.name: (None if f.default is dataclasses.MISSING else f.default)
+                            for f in dataclasses.fields(SamplingParams)},
+        "config": {f.name: (None if f.default is dataclasses.MISSING else f.default)
+                   for f in dataclasses.fields(RefConfig)},
+    }
+    path = os.path.join(HERE, "api_surface.json")
+    with open(path, "w") as f:
+        json.dump(out, f, indent=1, sort_keys=True)
+    print(f"api_surface.json: {os.path.getsize(path)} B")
+
+
+GENERATORS = {"index_contract": gen_index_contract, "layers": gen_layers, "staircase": gen_staircase,
+              "sampler": gen_sampler, "decoder": gen_decoder, "hf_twin": gen_hf_twin, "api_surface": gen_api_surface}
+
 if __name__ == "__main__":
-    gen_index_contract()
-    gen_layers()
-    gen_staircase()
-    gen_sampler()
-    gen_decoder()
+    # optional further arguments name the fixtures to (re)write; default: all
+    for name in (sys.argv[2:] or list(GENERATORS)):
+        GENERATORS[name]()

@@ -26,11 +26,11 @@ def _oracle_cfg(c):
                              max_position_embeddings=c.max_position_embeddings)
 
 
-def _make_runner(mdb, dcfg, weights, pages, eager, noise="explicit", max_seqs=4, max_len=1024, fused=False):
+def _make_runner(mdb, dcfg, weights, pages, eager, noise="explicit", max_seqs=4, max_len=1024):
     cfg = mdb.Config(max_num_batched_tokens=2048, max_num_seqs=max_seqs, max_model_len=max_len, enforce_eager=eager,
                      num_kvcache_blocks=pages, decoder_config=dcfg, mask_token_id=500)
     w = mdb.DecoderWeights.from_reference_layout(weights, DEV)
-    return cfg, mdb.ModelRunner(cfg, weights=w, noise=noise, fused_step=fused)
+    return cfg, mdb.ModelRunner(cfg, weights=w, noise=noise)
 
 
 def test_runner_matches_reference_fixture(mdb):
@@ -74,10 +74,32 @@ def _clone_seq(mdb, seq):
     return c
 
 
-LOGIT_TOL = 2e-2      # max-abs logits tolerance of the path (bf16, fp32 accumulate)
-E2E_LOGIT_TOL = 5e-2  # end-to-end bound checked below: three bf16 layers of a 256-wide model amplify the
-                      # per-op rounding differences; the reference's own two code paths (prefill vs decode form)
-                      # differ by 0.03 .. 0.09 over 4 .. 28 layers
+LOGIT_TOL = 2e-2      # max-abs logits tolerance of the path (bf16 operands, fp32 accumulation), also end to end
+                      # for the two- and three-layer decoders of this file; compared on the un-rounded fp32 logits
+                      # the two final hidden states imply (the reference rounds logits to bf16 afterwards, and one
+                      # bf16 step at |logit| >= 4 is already 0.031)
+REF_PATH_FLOOR = 0.094  # what the reference's own prefill-form and decode-form passes differ by on the same block
+                        # after 28 bf16 layers (measured with its modules on CPU); the yardstick for the full-size test
+
+
+def _record(name: str, **figures):
+    """Parity figures of a test: printed, and appended to gpurun_out/parity_tests.jsonl when that folder exists."""
+    import json
+    import os
+    line = json.dumps(dict(test=name, **figures))
+    print("PARITY " + line)
+    out = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
+    if os.path.isdir(out):
+        with open(os.path.join(out, "parity_tests.jsonl"), "a") as f:
+            f.write(line + "\n")
+
+
+def _logits_err(hidden_got, hidden_ref, lm_head):
+    """max |difference| of the fp32 logits two sets of final-norm rows imply through the same LM head."""
+    w = lm_head.float()
+    got = hidden_got.reshape(-1, hidden_got.shape[-1]).float() @ w.t()
+    ref = hidden_ref.reshape(-1, hidden_ref.shape[-1]).float() @ w.t()
+    return float((got - ref).abs().max())
 
 
 def _robust_requests(last, noise, blocks_before, mask_id, thr, temps, tol=LOGIT_TOL):
@@ -166,11 +188,11 @@ def test_teacher_forced_agreement(mdb, eager, temperature):
         ref_blocks = torch.stack([s.current_denoising_block for s in seqs])
         got_blocks = torch.stack([s.current_denoising_block for s in twins])
         # logits the CUDA path implies (its final-norm rows through the oracle's LM head) vs the oracle's
-        got_logits = orc.linear(runner.last["hidden"].cpu(), weights.lm_head).view_as(oracle.last["logits"])
-        step_err = float((got_logits.float() - oracle.last["logits"].float()).abs().max())
+        ref_hidden = oracle.decoder.compute_rows(oracle.last["hidden"], oracle.last["ctx"])
+        step_err = _logits_err(runner.last["hidden"].cpu(), ref_hidden, weights.lm_head)
         worst_logit_err = max(worst_logit_err, step_err)
         robust = _robust_requests(oracle.last, noise_store[oracle.step_index - 1], before, 500, 0.9, temps,
-                                  tol=max(LOGIT_TOL, step_err))
+                                  tol=LOGIT_TOL)
         decided = oracle.last["transfer"] | (got_blocks != ref_blocks)
         same = decided & (got_blocks == ref_blocks)
         for r, ok in enumerate(robust):
@@ -183,18 +205,18 @@ def test_teacher_forced_agreement(mdb, eager, temperature):
         sched.postprocess(seqs)
         steps += 1
     assert sched.is_finished()
-    print(f"teacher-forced agreement T={temperature} eager={eager}: all decisions {raw_agree}/{raw_total}, "
-          f"tolerance-robust decisions {rob_agree}/{rob_total}, steps {steps}, multi-token steps {multi}, "
-          f"worst end-to-end logits max-abs {worst_logit_err:.4f}")
-    assert worst_logit_err <= E2E_LOGIT_TOL
+    _record("teacher_forced_agreement", temperature=temperature, graphs=not eager, decisions=raw_total,
+            decisions_agree=raw_agree, robust_decisions=rob_total, robust_agree=rob_agree, steps=steps,
+            multi_token_steps=multi, logits_fp32_max_abs=round(worst_logit_err, 5), layers=3, hidden=256, vocab=1024)
+    assert worst_logit_err <= LOGIT_TOL
     assert rob_total > 0 and rob_agree / rob_total >= 0.995, f"committed-token agreement {rob_agree}/{rob_total}"
     if temperature >= 0.5:
-        assert rob_total >= 0.2 * raw_total
-        assert raw_agree / raw_total >= 0.9
+        assert rob_total >= 0.5 * raw_total
+        assert raw_agree / raw_total >= 0.97
     else:
-        # dividing by a small temperature magnifies logit differences 20x, so few decisions stay outside
+        # dividing by a small temperature magnifies logit differences 20x, so fewer decisions stay outside
         # the tolerance band; what matters here is that the threshold branch ran and agreed where it must
-        assert multi > 0
+        assert multi > 0 and raw_agree / raw_total >= 0.9
     assert mdb._lib.device_status(clear=True) == 0
 
 
@@ -246,11 +268,11 @@ def test_block_size_sweep(mdb, block, eager):
         runner.run(twins, is_prefill)
         ref_blocks = torch.stack([s.current_denoising_block for s in seqs])
         got_blocks = torch.stack([s.current_denoising_block for s in twins])
-        got_logits = orc.linear(runner.last["hidden"].cpu(), weights.lm_head).view_as(oracle.last["logits"])
-        step_err = float((got_logits.float() - oracle.last["logits"].float()).abs().max())
+        ref_hidden = oracle.decoder.compute_rows(oracle.last["hidden"], oracle.last["ctx"])
+        step_err = _logits_err(runner.last["hidden"].cpu(), ref_hidden, weights.lm_head)
         worst = max(worst, step_err)
         robust = _robust_requests(oracle.last, noise_store[oracle.step_index - 1], before, 500, 0.9, temps,
-                                  tol=max(LOGIT_TOL, step_err))
+                                  tol=LOGIT_TOL)
         decided = oracle.last["transfer"] | (got_blocks != ref_blocks)
         same = decided & (got_blocks == ref_blocks)
         for r, ok in enumerate(robust):
@@ -262,49 +284,12 @@ def test_block_size_sweep(mdb, block, eager):
         sched.postprocess(seqs)
         steps += 1
     assert sched.is_finished()
-    print(f"block {block} eager={eager}: decisions {raw_agree}/{raw_total}, tolerance-robust {rob_agree}/{rob_total}, "
-          f"steps {steps}, worst logits max-abs {worst:.4f}")
-    assert worst <= E2E_LOGIT_TOL
+    _record("block_size_sweep", block=block, graphs=not eager, decisions=raw_total, decisions_agree=raw_agree,
+            robust_decisions=rob_total, robust_agree=rob_agree, steps=steps, logits_fp32_max_abs=round(worst, 5),
+            layers=2, hidden=256, vocab=1024)
+    assert worst <= LOGIT_TOL
     assert rob_total > 0 and rob_agree / rob_total >= 0.995
-    assert raw_agree / raw_total >= 0.9
-    assert mdb._lib.device_status(clear=True) == 0
-
-
-@pytest.mark.parametrize("eager", [True, False])
-def test_one_kernel_step_matches_separate_kernels(mdb, eager):
-    """The persistent one-kernel decode step against the chain of separate
-    kernels: same requests, same counter-based noise, teacher-forced.  The two
-    run the same arithmetic (only the RMSNorm row sum is ordered differently),
-    so sampled tokens must agree and hidden rows stay within a few bf16 steps."""
-    dcfg = _tiny_cfg(mdb, vocab=1024, layers=3)
-    weights = orc.make_weights(_oracle_cfg(dcfg), seed=5)
-    cfg_a, ra = _make_runner(mdb, dcfg, weights, pages=8, eager=eager, noise="gumbel", fused=True)
-    cfg_b, rb = _make_runner(mdb, dcfg, weights, pages=8, eager=eager, noise="gumbel", fused=False)
-    ra.keep_last = rb.keep_last = True
-    gen = torch.Generator().manual_seed(3)
-    sched = mdb.Scheduler(cfg_a)
-    for plen in (150, 40, 260):
-        sp = mdb.SamplingParams(temperature=1.0, max_new_tokens=64, ignore_eos=True)
-        sched.add(mdb.Sequence(torch.randint(0, 490, (plen,), generator=gen).tolist(), sp, denoising_block_size=32,
-                               mask_token_id=500))
-    steps = agree = total = 0
-    worst = 0.0
-    while not sched.is_finished() and steps < 300:
-        seqs, is_prefill = sched.schedule()
-        twins = [_clone_seq(mdb, s) for s in seqs]
-        ra.run(seqs, is_prefill)
-        rb.run(twins, is_prefill)
-        same = ra.last["x0"] == rb.last["x0"]
-        agree += int(same.sum())
-        total += same.numel()
-        worst = max(worst, float((ra.last["hidden"].float() - rb.last["hidden"].float()).abs().max()))
-        assert torch.allclose(ra.last["conf"][same], rb.last["conf"][same], rtol=5e-2)
-        sched.postprocess(seqs)
-        steps += 1
-    assert sched.is_finished()
-    print(f"one-kernel step vs separate kernels (eager={eager}): sampled tokens {agree}/{total}, "
-          f"hidden max-abs {worst:.4f}, steps {steps}")
-    assert agree / total >= 0.99 and worst <= 0.05
+    assert raw_agree / raw_total >= 0.97
     assert mdb._lib.device_status(clear=True) == 0
 
 
@@ -405,4 +390,245 @@ def test_reused_step_inputs_change_nothing(mdb):
         runner.exit()
     for (tok_a, map_a), (tok_b, map_b) in zip(*outs):
         assert tok_a == tok_b and map_a == map_b
+    assert mdb._lib.device_status(clear=True) == 0
+
+
+# --------------------------------------------------------------------- full-size decoder
+@pytest.fixture(scope="module")
+def full_size(mdb):
+    """The decoder at the reference's configuration defaults (28 layers, hidden 2048, 16 query / 8 KV heads,
+    vocabulary 151936: BASELINE configs 2-5) with seeded N(0, 0.02) weights, on the CPU for the oracle and on
+    the GPU for the runner."""
+    ocfg = orc.DecoderConfig()
+    g = torch.Generator().manual_seed(20260320)
+    bf = torch.bfloat16
+
+    def mat(r, c):
+        return (torch.randn(r, c, generator=g) * 0.02).to(bf)
+
+    h, i, d = ocfg.hidden_size, ocfg.intermediate_size, ocfg.head_dim
+    hq, hkv = ocfg.num_attention_heads, ocfg.num_key_value_heads
+    ones_h, ones_d = torch.ones(h, dtype=bf), torch.ones(d, dtype=bf)
+    # one layer is drawn, the others are row-rotated copies of it: distinct matrices for a twenty-eighth of the draws
+    base = orc.LayerWeights(ones_h, mat((hq + 2 * hkv) * d, h), ones_d, ones_d, mat(h, hq * d), ones_h, mat(2 * i, h),
+                            mat(h, i))
+    layers = [base] + [orc.LayerWeights(ones_h, base.qkv.roll(j, 0).contiguous(), ones_d, ones_d,
+                                        base.o.roll(j, 0).contiguous(), ones_h, base.gate_up.roll(j, 0).contiguous(),
+                                        base.down.roll(j, 0).contiguous()) for j in range(1, ocfg.num_hidden_layers)]
+    weights = orc.DecoderWeights(mat(ocfg.vocab_size, h), layers, ones_h, mat(ocfg.vocab_size, h))
+    return ocfg, weights, mdb.DecoderWeights.from_reference_layout(weights, DEV)
+
+
+@pytest.mark.parametrize("temperature", [1.0, 0.005])
+def test_full_size_decoder_teacher_forced(mdb, full_size, temperature):
+    """One request on the full-size decoder, context ~1.1K (the middle of BASELINE config 2), decode-form
+    passes under CUDA graphs against the oracle: sampled tokens, transfer masks, block ids and the K/V rows
+    the commit pass caches.  At temperature 1 random-init weights commit one token per pass by the top-1 rule;
+    at 0.005 confidences pass the threshold and passes commit several tokens."""
+    from oracle import parity
+    ocfg, weights, gpu_weights = full_size
+    passes = 10 if temperature >= 0.5 else 8
+    r = parity.decode_parity(mdb, ocfg, weights, context=1056, passes=passes, temperature=temperature, threshold=0.9,
+                             seed=11, device="cuda:0", eager=False, gpu_weights=gpu_weights)
+    _record("full_size_decoder_teacher_forced", **r)
+    assert r["device_status"] == 0
+    assert r["passes"] == passes
+    # end to end over 28 bf16 layers: reported next to, and bounded by, what the reference's own two code
+    # paths differ by on the same block
+    assert r["logits_fp32_max_abs"] <= REF_PATH_FLOOR, r["logits_fp32_max_abs"]
+    assert r["robust_decisions"] == 0 or r["robust_agreement"] >= 0.995, r
+    # every differing decision must be a tie within the error of the path: the oracle's own margin at that
+    # position (sampled token or confidence ranking) is below twice the logits error of that pass over T
+    for d in r["disagreements"]:
+        eps = 2 * max(d["pass_logits_err"], LOGIT_TOL) / temperature
+        gap = d["confidence_log_gap"] if d["confidence_log_gap"] is not None else float("inf")
+        assert d["noisy_top2_margin"] <= eps or gap <= eps, d
+    assert r["x0_agree"] / max(r["x0_total"], 1) >= 0.9
+    if temperature < 0.5:
+        assert r["multi_token_passes"] > 0 and r["commit_passes"] >= 1
+        assert r["kv_rows"] > 0 and r["kv_max_abs"] <= 0.13 and r["kv_exact_frac"] >= 0.9
+    assert mdb._lib.device_status(clear=True) == 0
+
+
+# --------------------------------------------------------------------- the drop-in with the reference's own classes
+def _reference_like_classes():
+    """Stand-ins that carry exactly the attributes of the reference's ``Sequence``, ``SamplingParams`` and
+    ``Config`` (recorded from its modules in tests/golden/api_surface.json): any read of a name the reference
+    does not have raises AttributeError, as it would with the real objects."""
+    import json
+    import os
+    from types import SimpleNamespace
+    from conftest import GOLDEN
+    with open(os.path.join(GOLDEN, "api_surface.json")) as f:
+        api = json.load(f)
+
+    class RefSequence:
+        kvcache_block_size = 256
+
+        def __init__(self, seq_id, token_ids, sampling_params, denoising_block_size, mask_token_id, status):
+            self.seq_id = seq_id
+            self.status = status
+            self.token_ids = list(token_ids)
+            self.step_map = []
+            self.last_token = token_ids[-1]
+            self.num_tokens = len(token_ids)
+            self.num_prompt_tokens = len(token_ids)
+            self.num_cached_tokens = 0
+            self.block_table = []
+            self.sampling_params = sampling_params
+            self.temperature = sampling_params.temperature
+            self.max_new_tokens = sampling_params.max_new_tokens
+            self.ignore_eos = sampling_params.ignore_eos
+            self.pixel_values = None
+            self.image_grid_thw = None
+            self.denoising_block_size = denoising_block_size
+            self.mask_token_id = mask_token_id
+            self.current_denoising_block = torch.full((denoising_block_size,), mask_token_id, dtype=torch.int64)
+            self.current_step_map = torch.zeros(denoising_block_size, dtype=torch.int32)
+            self.current_denoise_step = 0
+
+        def __len__(self):
+            return self.num_tokens
+
+        def __getitem__(self, key):
+            return self.token_ids[key]
+
+        is_finished = property(lambda self: self.status.name == "FINISHED")
+        is_caching = property(lambda self: self.status.name == "CACHING")
+        num_completion_tokens = property(lambda self: self.num_tokens - self.num_prompt_tokens)
+        completion_token_ids = property(lambda self: self.token_ids[self.num_prompt_tokens:])
+        num_cached_blocks = property(lambda self: self.num_cached_tokens // 256)
+        num_blocks = property(lambda self: (self.num_tokens + 255) // 256)
+        last_block_num_tokens = property(lambda self: self.num_tokens - (self.num_blocks - 1) * 256)
+
+        def block(self, i):
+            return self.token_ids[i * 256:(i + 1) * 256]
+
+        def append_block(self):
+            self.token_ids.extend(self.current_denoising_block.tolist())
+            self.step_map.extend(self.current_step_map.tolist())
+            self.num_tokens += self.denoising_block_size
+            self.last_token = self.token_ids[-1]
+            self.current_denoising_block = torch.full((self.denoising_block_size,), self.mask_token_id,
+                                                      dtype=torch.int64)
+
+        def need_new_block(self):
+            return self.num_tokens + self.denoising_block_size > 256 * len(self.block_table)
+
+        def get_slots(self, lo, hi):
+            return orc.get_slots(self.block_table, lo, hi)
+
+    probe = RefSequence(0, [1, 2], SimpleNamespace(temperature=1.0, max_new_tokens=1, ignore_eos=True), 32, 9, None)
+    assert sorted(vars(probe)) == api["sequence_attributes"]
+    return api, RefSequence
+
+
+def test_runner_accepts_the_reference_attribute_sets(mdb):
+    """``ModelRunner`` driven with objects that have exactly the attribute sets of the reference's ``Config``
+    (``hf_config`` with the decoder dimensions, no ``decoder_config``), ``SamplingParams`` (no
+    ``denoising_steps``) and ``Sequence`` (no ``inputs_embeds``) through the loop of ``LLMEngine.step``
+    (nanovllm/engine/llm_engine.py:66-73): same tokens as with this package's own classes."""
+    from types import SimpleNamespace
+    api, RefSequence = _reference_like_classes()
+    dcfg = _tiny_cfg(mdb, vocab=1024, layers=2)
+    weights = orc.make_weights(_oracle_cfg(dcfg), seed=17)
+    gw = mdb.DecoderWeights.from_reference_layout(weights, DEV)
+    gen = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(0, 490, (n,), generator=gen).tolist() for n in (100, 300, 31)]
+    news = (64, 96, 32)
+
+    def run(reference_like: bool):
+        if reference_like:
+            text = SimpleNamespace(vocab_size=dcfg.vocab_size, hidden_size=dcfg.hidden_size,
+                                   intermediate_size=dcfg.intermediate_size, num_hidden_layers=dcfg.num_hidden_layers,
+                                   num_attention_heads=dcfg.num_attention_heads,
+                                   num_key_value_heads=dcfg.num_key_value_heads, head_dim=dcfg.head_dim,
+                                   rms_norm_eps=dcfg.rms_norm_eps, rope_theta=dcfg.rope_theta,
+                                   max_position_embeddings=dcfg.max_position_embeddings, tie_word_embeddings=False)
+            fields = dict(api["config"])
+            fields.update(model="unused", max_num_batched_tokens=2048, max_num_seqs=4, max_model_len=1024,
+                          enforce_eager=False, num_kvcache_blocks=10, mask_token_id=500,
+                          hf_config=SimpleNamespace(language_model_config=text))
+            cfg = SimpleNamespace(**fields)
+            assert set(vars(cfg)) == set(api["config"])
+        else:
+            cfg = mdb.Config(max_num_batched_tokens=2048, max_num_seqs=4, max_model_len=1024, enforce_eager=False,
+                             num_kvcache_blocks=10, decoder_config=dcfg, mask_token_id=500)
+        runner = mdb.ModelRunner(cfg, weights=gw, noise="gumbel", noise_seed=3)
+        sched = mdb.Scheduler(cfg)
+        seqs = []
+        for i, (ids, new) in enumerate(zip(prompts, news)):
+            if reference_like:
+                sp_fields = dict(api["sampling_params"])
+                sp_fields.update(temperature=0.05, max_new_tokens=new, ignore_eos=True, stop_token_ids=[])
+                sp = SimpleNamespace(**sp_fields)
+                seq = RefSequence(i, ids, sp, 32, 500, mdb.SequenceStatus.WAITING)
+            else:
+                sp = mdb.SamplingParams(temperature=0.05, max_new_tokens=new, ignore_eos=True)
+                seq = mdb.Sequence(ids, sp, denoising_block_size=32, mask_token_id=500)
+            seqs.append(seq)
+            sched.add(seq)
+        total = 0
+        while not sched.is_finished():
+            batch, is_prefill = sched.schedule()                      # llm_engine.py:67
+            n = runner.call("run", batch, is_prefill)                 # :69
+            sched.postprocess(batch)                                  # :70
+            total += n
+        runner.exit()
+        return [s.completion_token_ids for s in seqs], total
+
+    want, n_want = run(False)
+    got, n_got = run(True)
+    assert got == want and n_got == n_want
+    for toks, new in zip(got, news):
+        assert len(toks) == new and 500 not in toks
+    assert mdb._lib.device_status(clear=True) == 0
+
+
+def test_runner_follows_quota_schedule(mdb):
+    """``SamplingParams.denoising_steps``: pass ``s`` of a block unmasks ``num_transfer_tokens[min(s, steps-1)]``
+    positions (mineru_diffusion/modeling_mineru_diffusion.py:617-623,712) when the threshold does not take
+    more; the oracle runner follows the same schedule and decides the same positions."""
+    dcfg = _tiny_cfg(mdb, vocab=1024, layers=2)
+    ocfg = _oracle_cfg(dcfg)
+    weights = orc.make_weights(ocfg, seed=19)
+    steps_per_block = 5                                   # 32 tokens over 5 passes: 7, 7, 6, 6, 6
+    cfg, runner = _make_runner(mdb, dcfg, weights, pages=8, eager=True)
+    gen = torch.Generator().manual_seed(9)
+    noise_store = {}
+
+    def oracle_noise(step, shape):
+        noise_store[step] = -torch.empty(shape).exponential_(generator=gen).log()
+        return noise_store[step]
+
+    runner.noise_fn = lambda step, m, v: noise_store[step].reshape(m, v).contiguous().to(DEV)
+    oracle = orc.OracleModelRunner(ocfg, weights, num_pages=8, block_size=32, mask_token_id=500, noise_fn=oracle_noise)
+    sched = mdb.Scheduler(cfg)
+    for plen in (90, 200):
+        sp = mdb.SamplingParams(temperature=1.0, max_new_tokens=64, ignore_eos=True, dynamic_threshold=0.9,
+                                denoising_steps=steps_per_block)
+        sched.add(mdb.Sequence(torch.randint(0, 490, (plen,), generator=gen).tolist(), sp, denoising_block_size=32,
+                               mask_token_id=500))
+    counts, steps, same, total = [], 0, 0, 0
+    while not sched.is_finished() and steps < 100:
+        seqs, is_prefill = sched.schedule()
+        twins = [_clone_seq(mdb, s) for s in seqs]
+        caching = [s.is_caching for s in seqs]
+        n_ref = oracle.run(seqs, is_prefill)
+        n_got = runner.run(twins, is_prefill)
+        moved_ref = oracle.last["transfer"]
+        for r, (s, t) in enumerate(zip(seqs, twins)):
+            if not caching[r]:
+                counts.append(int(moved_ref[r].sum()))
+            eq = t.current_denoising_block == s.current_denoising_block
+            same += int(eq.sum())
+            total += eq.numel()
+            s._block_passes = getattr(t, "_block_passes", None)   # the twin of the next step is a fresh copy
+        assert n_got == n_ref
+        sched.postprocess(seqs)
+        steps += 1
+    assert sched.is_finished()
+    # two requests x two blocks, five denoising passes each (random weights never reach the threshold)
+    assert counts == [7, 7, 7, 7, 6, 6, 6, 6, 6, 6] * 2, counts
+    assert same / total >= 0.97
     assert mdb._lib.device_status(clear=True) == 0

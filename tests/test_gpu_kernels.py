@@ -220,20 +220,9 @@ def test_silu_mul_and_gather(mdb):
 
 
 # --------------------------------------------------------------------- GEMMs
-@pytest.fixture(params=["regs", "tc"])
-def stream_kernel(mdb, request):
-    """Short steps run either on the register-streaming kernel (mma.sync) or on
-    the tcgen05/TMA streaming kernel; both must give the same results."""
-    old = mdb.ops.get_option(mdb.ops.OPT_STREAM_KERNEL)
-    mdb.ops.set_option(mdb.ops.OPT_STREAM_KERNEL, 1 if request.param == "regs" else 0)
-    yield request.param
-    mdb.ops.set_option(mdb.ops.OPT_STREAM_KERNEL, old)
-    assert mdb._lib.device_status(clear=True) == 0
-
-
 @pytest.mark.parametrize("m", [1, 16, 32, 33, 64])
 @pytest.mark.parametrize("n,k", [(512, 256), (2048, 2048), (4096, 6144)])
-def test_gemm_streaming(mdb, stream_kernel, m, n, k):
+def test_gemm_streaming(mdb, m, n, k):
     gen = torch.Generator().manual_seed(m * 7 + n)
     x = torch.randn(m, k, generator=gen).to(BF)
     w = (0.02 * torch.randn(n, k, generator=gen)).to(BF)
@@ -251,7 +240,7 @@ def test_gemm_streaming(mdb, stream_kernel, m, n, k):
 
 
 @pytest.mark.parametrize("m", [8, 32, 48])
-def test_gemm_gateup_swiglu(mdb, stream_kernel, m):
+def test_gemm_gateup_swiglu(mdb, m):
     gen = torch.Generator().manual_seed(m)
     k, inter = 512, 768
     x = torch.randn(m, k, generator=gen).to(BF)
@@ -279,8 +268,8 @@ def test_gemm_gateup_swiglu_many_rows(mdb, m):
 
 
 @pytest.mark.parametrize("m,n,k", [(65, 384, 256), (200, 4096, 2048), (1088, 2048, 6144), (129, 136, 64),
-                                   (2048, 4096, 2048)])
-def test_gemm_tiled(mdb, stream_kernel, m, n, k):
+                                   (2048, 4096, 2048), (20, 136, 64)])
+def test_gemm_tile_kernel(mdb, m, n, k):
     gen = torch.Generator().manual_seed(m + n)
     x = torch.randn(m, k, generator=gen).to(BF)
     w = (0.02 * torch.randn(n, k, generator=gen)).to(BF)
@@ -354,15 +343,6 @@ def test_gemm_rejects_bad_arguments(mdb):
 
 
 # --------------------------------------------------------------------- block attention over the paged cache
-@pytest.fixture(params=["mma", "tc"])
-def attn_kernel(request, mdb):
-    """Runs a test once per block-attention kernel: the mma.sync one and the
-    tcgen05/TMA one (which takes over where block * hq / hkv <= 64)."""
-    mdb.ops.set_option(mdb.ops.OPT_ATTN_KERNEL, 1 if request.param == "mma" else 2)
-    yield request.param
-    mdb.ops.set_option(mdb.ops.OPT_ATTN_KERNEL, 0)
-
-
 def _paged_case(seed, bs, block, hq, hkv, prefix_lens, pages_extra=3, poison=False):
     gen = torch.Generator().manual_seed(seed)
     ctx = [p + block if p >= 0 else 0 for p in prefix_lens]
@@ -392,7 +372,7 @@ def _paged_case(seed, bs, block, hq, hkv, prefix_lens, pages_extra=3, poison=Fal
 
 @pytest.mark.parametrize("hq,hkv", [(16, 2), (16, 8), (8, 4), (4, 4)])
 @pytest.mark.parametrize("nsplit", [1, 3, 16])
-def test_attn_paged_config1(mdb, attn_kernel, hq, hkv, nsplit):
+def test_attn_paged_config1(mdb, hq, hkv, nsplit):
     """BASELINE config 1 (decode form): batch 4, prefix lengths uniform in
     [256, 2048] (seed 1), block 32, head_dim 128, 256-token pages in a
     permuted page table."""
@@ -409,7 +389,7 @@ def test_attn_paged_config1(mdb, attn_kernel, hq, hkv, nsplit):
 
 
 @pytest.mark.parametrize("block", [8, 16, 32, 64])
-def test_attn_paged_edges(mdb, attn_kernel, block):
+def test_attn_paged_edges(mdb, block):
     # prefix 0 (context = the block only), a request with context 0 (padding row), page-straddling lengths,
     # contexts that end inside a key tile with NaN / Inf in the cache slots behind them
     prefix = [0, -1, 250, 513, 1000, 128 - block, 256 - block]
@@ -423,7 +403,7 @@ def test_attn_paged_edges(mdb, attn_kernel, block):
     _status_clean(mdb)
 
 
-def test_attn_paged_properties_at_full_size(mdb, attn_kernel):
+def test_attn_paged_properties_at_full_size(mdb):
     """BASELINE config 3 shape (64 requests, contexts up to ~6K, 8 KV heads):
     too big for the CPU oracle, checked through invariants instead."""
     gen = torch.Generator(device=DEV).manual_seed(3)
@@ -468,7 +448,7 @@ def test_attn_paged_properties_at_full_size(mdb, attn_kernel):
 # --------------------------------------------------------------------- staircase prefill attention
 @pytest.mark.parametrize("stairs", [8, 32])
 @pytest.mark.parametrize("hq,hkv", [(16, 2), (4, 2), (4, 4), (6, 2)])
-def test_attn_staircase_vs_oracle(mdb, attn_kernel, stairs, hq, hkv):
+def test_attn_staircase_vs_oracle(mdb, stairs, hq, hkv):
     gen = torch.Generator().manual_seed(stairs + hq)
     lens = [288 + 5, 32, 1, 700, 95]
     cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32)
@@ -483,7 +463,7 @@ def test_attn_staircase_vs_oracle(mdb, attn_kernel, stairs, hq, hkv):
     _status_clean(mdb)
 
 
-def test_attn_staircase_config1_and_golden(mdb, attn_kernel):
+def test_attn_staircase_config1_and_golden(mdb):
     """BASELINE config 1 prefill form (every row of prefix+block is a query)
     and the reference Triton kernel's own fp32 outputs."""
     gen = torch.Generator().manual_seed(1)
@@ -506,11 +486,11 @@ def test_attn_staircase_config1_and_golden(mdb, attn_kernel):
         assert (got.float() - ref).abs().max() <= 3e-2
 
 
-def test_attn_staircase_long_sequences_kernels_agree(mdb):
-    """Prefill shapes too long for the CPU oracle (the decoder's 16 query / 8 KV
-    heads, sequences up to 3001 tokens, lengths around the 128-key tile edges):
-    the tcgen05 kernel against the mma.sync kernel, which the oracle pins on
-    the short cases above, and one short sequence of the batch against the oracle."""
+def test_attn_staircase_long_sequences(mdb):
+    """Prefill shapes too long for the CPU oracle as a whole (the decoder's 16 query / 8 KV heads, sequences
+    up to 3001 tokens, lengths around the 128-key tile edges): every sequence of up to 257 tokens against the
+    oracle, and for the long ones two invariants -- a sequence's rows do not depend on what else is packed
+    with it, and the rows of the first stairs do not depend on the tokens behind them (block causality)."""
     gen = torch.Generator(device=DEV).manual_seed(11)
     lens = [1, 31, 32, 33, 127, 128, 129, 1000, 3001, 257]
     cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32)
@@ -518,17 +498,30 @@ def test_attn_staircase_long_sequences_kernels_agree(mdb):
     q = torch.randn(n, 16, 128, generator=gen, device=DEV).to(BF)
     k = torch.randn(n, 8, 128, generator=gen, device=DEV).to(BF)
     v = torch.randn(n, 8, 128, generator=gen, device=DEV).to(BF)
-    outs = {}
-    for name, opt in (("mma", 1), ("tc", 2)):
-        mdb.ops.set_option(mdb.ops.OPT_ATTN_KERNEL, opt)
-        outs[name] = mdb.ops.sparse_attn_varlen(q, k, v, cu.to(DEV), cu.to(DEV), 32)
-    mdb.ops.set_option(mdb.ops.OPT_ATTN_KERNEL, 0)
-    err = (outs["tc"].float() - outs["mma"].float()).abs()
-    assert float(err.max()) <= 2e-2 and float(err.mean()) <= 3e-4, (float(err.max()), float(err.mean()))
-    a, b = int(cu[4]), int(cu[5])           # the 127-token sequence
+    out = mdb.ops.sparse_attn_varlen(q, k, v, cu.to(DEV), cu.to(DEV), 32)
+    for i, t in enumerate(lens):
+        a, b = int(cu[i]), int(cu[i + 1])
+        one = torch.tensor([0, t], dtype=torch.int32)
+        if t <= 257:
+            want = orc.attn_staircase_varlen(q[a:b].cpu(), k[a:b].cpu(), v[a:b].cpu(), one, one, 32, mirror_rounding=True)
+            assert float((out[a:b].cpu().float() - want.float()).abs().max()) <= 2e-2, t
+        else:
+            alone = mdb.ops.sparse_attn_varlen(q[a:b].contiguous(), k[a:b].contiguous(), v[a:b].contiguous(),
+                                               one.to(DEV), one.to(DEV), 32)
+            assert torch.equal(alone, out[a:b])
+            # right-aligned stairs: with T' = T - 32 * j the stair edges stay where they are, so the first
+            # T' rows of the long sequence equal the rows of its T'-token prefix run on its own
+            tp = t - 32 * 7
+            cut = torch.tensor([0, tp], dtype=torch.int32).to(DEV)
+            head = mdb.ops.sparse_attn_varlen(q[a:a + tp].contiguous(), k[a:a + tp].contiguous(),
+                                              v[a:a + tp].contiguous(), cut, cut, 32)
+            # (the lazy running maximum is shared by the rows of a warp, so only fp32 rounding may differ)
+            assert float((head.float() - out[a:a + tp].float()).abs().max()) <= 4e-3
+    # the tail of the 1000-token sequence against the oracle (its last 64 rows see every key)
+    a, b = int(cu[7]), int(cu[8])
     one = torch.tensor([0, b - a], dtype=torch.int32)
     want = orc.attn_staircase_varlen(q[a:b].cpu(), k[a:b].cpu(), v[a:b].cpu(), one, one, 32, mirror_rounding=True)
-    assert float((outs["tc"][a:b].cpu().float() - want.float()).abs().max()) <= 2e-2
+    assert float((out[a:b].cpu().float() - want.float()).abs().max()) <= 2e-2
     _status_clean(mdb)
 
 
@@ -556,8 +549,8 @@ def test_logits_sample_golden(mdb):
 @pytest.mark.parametrize("m,block,v", [(32, 32, 4096), (64, 32, 4096), (16, 8, 4096), (128, 32, 4096),
                                        (320, 32, 4096), (160, 32, 1000)])
 @pytest.mark.parametrize("mode", ["none", "explicit", "counter"])
-def test_lmhead_sample(mdb, stream_kernel, m, block, v, mode):
-    """Short steps: weight-streaming kernels with the sampler in the epilogue.
+def test_lmhead_sample(mdb, m, block, v, mode):
+    """Short steps: weight-streaming kernel with the sampler in the epilogue.
     Many rows (m > 64): the tcgen05 tile GEMM with the sampler epilogue, also
     with a partial last row tile (320) and a partial last vocabulary tile
     (1000); explicit noise arrays go through materialised logits."""
@@ -617,3 +610,115 @@ def test_unmask_decide_vs_oracle(mdb):
         assert torch.equal(d_blocks.cpu(), want)
         assert torch.equal(t.cpu().bool(), want_t)
         assert torch.equal(counts.cpu().long(), want_t.sum(1))
+
+
+def test_unmask_decide_hf_twin_quota(mdb):
+    """Per-request quotas: the HF twin's ``_select_transfer_index`` on its own fixture
+    (mineru_diffusion/modeling_mineru_diffusion.py:518-532) and the quota schedule helper."""
+    g = load_golden("hf_twin.npz")
+    for b, steps in g["sched_pairs"].tolist():
+        assert mdb.ops.num_transfer_tokens(b, steps) == g[f"sched_{b}_{steps}"].tolist()
+    thr, mask_id = float(g["threshold"]), 151669
+    for i in range(int(g["num_cases"])):
+        conf = torch.from_numpy(g[f"q{i}_conf"])
+        masked = torch.from_numpy(g[f"q{i}_masked"])
+        count = int(g[f"q{i}_count"])
+        bs, block = conf.shape
+        blocks = torch.where(masked, torch.full(masked.shape, mask_id, dtype=torch.int64),
+                             torch.zeros(masked.shape, dtype=torch.int64))
+        x0 = (torch.arange(conf.numel(), dtype=torch.int32) + 1).view(conf.shape)
+        d_blocks = blocks.to(DEV)
+        quotas = torch.full((bs,), count, dtype=torch.int32, device=DEV)
+        t, counts = mdb.ops.unmask_decide(d_blocks, x0.to(DEV).view(-1), conf.to(DEV).view(-1), mask_id, thr,
+                                          quotas=quotas)
+        want = torch.from_numpy(g[f"q{i}_transfer"])
+        assert torch.equal(t.cpu().bool(), want), i
+        assert torch.equal(counts.cpu().long(), want.sum(1))
+        assert torch.equal(d_blocks.cpu()[want], x0.long()[want])
+        # the same quota as one scalar for the whole batch
+        d2 = blocks.to(DEV)
+        t2, _ = mdb.ops.unmask_decide(d2, x0.to(DEV).view(-1), conf.to(DEV).view(-1), mask_id, thr, quota=count)
+        assert torch.equal(t2, t)
+    # a quota of 0 (more steps than tokens) leaves only the threshold branch; fewer masked than the quota: all go
+    conf = torch.tensor([[0.5, 0.95, 0.2, 0.1], [0.5, 0.6, 0.2, 0.1]])
+    blocks = torch.full((2, 4), mask_id, dtype=torch.int64)
+    blocks[1, 0] = 3
+    x0 = torch.arange(8, dtype=torch.int32) + 100
+    d = blocks.to(DEV)
+    t, c = mdb.ops.unmask_decide(d, x0.to(DEV), conf.to(DEV).view(-1), mask_id, thr,
+                                 quotas=torch.tensor([0, 7], dtype=torch.int32, device=DEV))
+    assert t.cpu().tolist() == [[0, 1, 0, 0], [0, 1, 1, 1]] and c.cpu().tolist() == [1, 3]
+    _status_clean(mdb)
+
+
+def test_unmask_decide_hands_over_status_word(mdb):
+    """The last kernel of a step copies the device status word next to its results and clears it."""
+    kc = torch.zeros(1, 256, 2, 128, dtype=BF, device=DEV)
+    src = torch.ones(1, 2, 128, dtype=BF, device=DEV)
+    mdb.ops.store_kvcache(src, src, kc, kc.clone(), torch.tensor([999999], dtype=torch.int32, device=DEV))   # bad slot
+    blocks = torch.full((1, 32), 7, dtype=torch.int64, device=DEV)
+    word = torch.zeros(1, dtype=torch.int32, device=DEV)
+    mdb.ops.unmask_decide(blocks, torch.zeros(32, dtype=torch.int32, device=DEV), torch.zeros(32, device=DEV), 9, 0.9,
+                          status_out=word)
+    assert int(word.item()) == 1
+    assert mdb._lib.device_status(clear=True) == 0
+
+
+def test_attn_paged_context_beyond_page_table(mdb):
+    """A context length the page-table row cannot address (device data the host never validates): the kernel
+    cuts it to the row, raises MDB_STATUS_BAD_PAGE and never reads the table past the request's row; so does a
+    page id outside the pool.  Outputs stay finite."""
+    q, kc, vc, ctx, table = _paged_case(5, 3, 32, 16, 8, [200, 480, 300])
+    assert table.shape[1] == 2
+    bad_ctx = ctx.clone()
+    bad_ctx[2] = 2 * 256 + 40                      # the last request: one tile past its (and the buffer's) last row
+    got = mdb.ops.block_attn_with_kvcache(q.to(DEV), kc.to(DEV), vc.to(DEV), bad_ctx.to(DEV), table.to(DEV), nsplit=1)
+    assert mdb._lib.device_status(clear=True) & 2
+    assert bool(torch.isfinite(got.float()).all())
+    want = orc.attn_paged(q, kc, vc, ctx, table, 128 ** -0.5)
+    assert (got[:2].cpu().float() - want[:2].float()).abs().max() <= 2e-2      # the other requests are untouched
+    bad_table = table.clone()
+    bad_table[1, 1] = kc.shape[0] + 3
+    got = mdb.ops.block_attn_with_kvcache(q.to(DEV), kc.to(DEV), vc.to(DEV), ctx.to(DEV), bad_table.to(DEV), nsplit=2)
+    assert mdb._lib.device_status(clear=True) & 2
+    assert bool(torch.isfinite(got.float()).all())
+
+
+def test_bounded_wait_runs_out(mdb):
+    """The error contract of the in-kernel waits: a consumer that waits for flag slots nobody raises gives up
+    after the wait limit, the call returns, the kernel finishes, and MDB_STATUS_WAIT_TIMEOUT (bit 16) is set --
+    and cleared by reading it.  One GPU, no peer: the slots are plain local memory that stays zero."""
+    lib = mdb._lib.lib()
+    old = mdb.ops.get_option(mdb.ops.OPT_WAIT_LIMIT_US)
+    mdb.ops.set_option(mdb.ops.OPT_WAIT_LIMIT_US, 2000)          # 2 ms instead of 2 s
+    try:
+        m, h = 8, 256
+        parts = torch.zeros(2, m, h, device=DEV)
+        res = torch.zeros(m, h, dtype=BF, device=DEV)
+        w = torch.ones(h, dtype=BF, device=DEV)
+        y, r = torch.empty_like(res), torch.empty_like(res)
+        flags = torch.zeros(4, dtype=torch.int32, device=DEV)    # never raised
+        epoch = torch.ones(1, dtype=torch.int32, device=DEV)
+        torch.cuda.synchronize()
+        t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        mdb._lib.check(lib.mdb_add_rmsnorm_tp(None, parts.data_ptr(), 2, res.data_ptr(), w.data_ptr(), 1e-6,
+                                              y.data_ptr(), r.data_ptr(), m, h, flags.data_ptr(), 4, 5,
+                                              epoch.data_ptr(), torch.cuda.current_stream().cuda_stream),
+                       "mdb_add_rmsnorm_tp")
+        t1.record()
+        torch.cuda.synchronize()
+        assert t0.elapsed_time(t1) < 500.0                       # gave up after ~2 ms, not 2 s
+        assert mdb._lib.device_status(clear=False) & 16
+        assert mdb._lib.device_status(clear=True) & 16
+        assert mdb._lib.device_status(clear=True) == 0
+        assert bool((y == 0).all())                              # the kernel still wrote its rows
+        # raised slots: no wait, no status
+        flags.fill_(1 * 256 + 5)
+        mdb._lib.check(lib.mdb_add_rmsnorm_tp(None, parts.data_ptr(), 2, res.data_ptr(), w.data_ptr(), 1e-6,
+                                              y.data_ptr(), r.data_ptr(), m, h, flags.data_ptr(), 4, 5,
+                                              epoch.data_ptr(), torch.cuda.current_stream().cuda_stream),
+                       "mdb_add_rmsnorm_tp")
+        assert mdb._lib.device_status(clear=True) == 0
+    finally:
+        mdb.ops.set_option(mdb.ops.OPT_WAIT_LIMIT_US, old)

@@ -158,3 +158,24 @@ def test_decoder_steps_match_reference_modules():
             v_rows = bf16_from_bits(g[p + "v_l0_first_rows"])
             assert int(ulp_diff_bf16(kv[0, 0, tab[0], :8], k_rows).max()) <= 1
             assert int(ulp_diff_bf16(kv[1, 0, tab[0], :8], v_rows).max()) <= 1
+
+
+def test_hf_twin_quota_rule_and_schedule():
+    """The quota form of the unmask rule and the per-block quota schedule against the HF twin's own
+    ``_select_transfer_index`` / ``get_num_transfer_tokens``
+    (mineru_diffusion/modeling_mineru_diffusion.py:518-532,617-623)."""
+    g = load_golden("hf_twin.npz")
+    for b, steps in g["sched_pairs"].tolist():
+        assert orc.num_transfer_tokens(b, steps) == g[f"sched_{b}_{steps}"].tolist()
+    thr = float(g["threshold"])
+    mask_id = 99999
+    for i in range(int(g["num_cases"])):
+        conf = torch.from_numpy(g[f"q{i}_conf"])
+        masked = torch.from_numpy(g[f"q{i}_masked"])
+        count = int(g[f"q{i}_count"])
+        blocks = torch.where(masked, torch.full(masked.shape, mask_id, dtype=torch.int64),
+                             torch.zeros(masked.shape, dtype=torch.int64))
+        x0 = torch.arange(conf.numel(), dtype=torch.int64).view(conf.shape) + 1
+        out, transfer = orc.unmask_decision(blocks, x0, conf, mask_id, thr, quotas=[count] * conf.shape[0])
+        assert torch.equal(transfer, torch.from_numpy(g[f"q{i}_transfer"])), i
+        assert torch.equal(out[transfer], x0[transfer]) and torch.equal(out[~transfer], blocks[~transfer])

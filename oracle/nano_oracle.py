@@ -369,6 +369,7 @@ class Decoder:
                                     cfg.num_key_value_heads, cfg.head_dim, dtype=dtype)
         self.rope = rope_table(cfg.max_position_embeddings, cfg.head_dim, cfg.rope_theta)
         self.scale = cfg.head_dim ** -0.5
+        self.round_p = True              # decode attention rounds probabilities to bf16 before PV, as flash-attn does
         self.trace: dict | None = None   # filled with intermediates when set to {}
 
     def embed(self, input_ids: torch.Tensor) -> torch.Tensor:
@@ -403,7 +404,7 @@ class Decoder:
                 o = attn_staircase_varlen(q, k, v, ctx.cu_seqlens_q, ctx.cu_seqlens_k, ctx.block_size)
                 o = o.flatten(1)
             else:
-                o = attn_paged(q, k_cache, v_cache, ctx.context_lens, ctx.block_tables, self.scale, round_p=True)
+                o = attn_paged(q, k_cache, v_cache, ctx.context_lens, ctx.block_tables, self.scale, round_p=self.round_p)
                 o = o.flatten(2)
             if self.trace is not None and li == 0:
                 self.trace.update(q0=q.clone(), k0=k.clone(), v0=v.clone(), attn0=o.clone())

@@ -61,6 +61,11 @@ def decode_parity(pkg, ocfg: "orc.DecoderConfig", weights: "orc.DecoderWeights",
     * ``logits_fp32_max_abs``: worst |CUDA - oracle| over the un-rounded fp32 logits implied by the two
       final-norm hidden states (both through the oracle's LM head); ``logits_bf16_max_ulp``: the same after
       the reference's rounding of the logits to bf16, in bf16 steps;
+    * ``oracle_floor_logits_fp32_max_abs``: the same figure between the oracle and itself with the one rounding
+      inside its attention left out (probabilities kept in fp32 instead of rounded to bf16 before PV, which
+      flash-attn does per key tile against a running maximum and no restatement can place identically), on the
+      first pass: what two equally valid implementations of the reference's arithmetic differ by at this depth
+      and width;
     * ``conf_max_rel``: worst relative difference of the confidences where the sampled tokens agree;
     * ``kv_rows``: committed K/V rows compared after each commit pass, ``kv_max_abs`` their worst difference,
       ``kv_exact_frac`` the share of identical bf16 values;
@@ -123,10 +128,18 @@ def _decode_parity(pkg, ocfg, weights, context, passes, temperature, threshold, 
         return s
 
     ref_seq, got_seq = make(), make()
+    # the yardstick: the oracle against itself with its attention's probability rounding left out, first pass
+    twin = orc.OracleModelRunner(ocfg, weights, num_pages=pages, block_size=block, mask_token_id=mask_id, noise_fn=None)
+    twin.decoder.kv_cache.copy_(oracle.decoder.kv_cache)
+    twin.decoder.round_p = False
+    twin.run([make()], False)
+    twin_hidden = twin.last["hidden"].reshape(block, -1).float()
+    del twin
+    lm_w32 = weights.lm_head.float()
     out = dict(decisions=0, decisions_agree=0, robust_decisions=0, robust_agree=0, x0_total=0, x0_agree=0,
                logits_fp32_max_abs=0.0, logits_bf16_max_ulp=0, conf_max_rel=0.0, kv_rows=0, kv_max_abs=0.0,
-               kv_exact_frac=1.0, passes=0, commit_passes=0, multi_token_passes=0, disagreements=[])
-    lm_w32 = weights.lm_head.float()
+               kv_exact_frac=1.0, passes=0, commit_passes=0, multi_token_passes=0, disagreements=[],
+               oracle_floor_logits_fp32_max_abs=None)
     for _ in range(passes):
         before = ref_seq.current_denoising_block.clone()
         is_commit = not bool((before == mask_id).any())
@@ -139,6 +152,8 @@ def _decode_parity(pkg, ocfg, weights, context, passes, temperature, threshold, 
         h_ref = last["hidden"].reshape(block, -1).float()
         h_got = runner.last["hidden"].cpu().float()
         lf_ref, lf_got = h_ref @ lm_w32.t(), h_got @ lm_w32.t()
+        if out["oracle_floor_logits_fp32_max_abs"] is None:
+            out["oracle_floor_logits_fp32_max_abs"] = round(float((lf_ref - twin_hidden @ lm_w32.t()).abs().max()), 6)
         err = float((lf_ref - lf_got).abs().max())
         out["logits_fp32_max_abs"] = max(out["logits_fp32_max_abs"], err)
         a = lf_ref.to(torch.bfloat16).view(torch.int16).to(torch.int32)

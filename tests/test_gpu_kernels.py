@@ -722,3 +722,30 @@ def test_bounded_wait_runs_out(mdb):
         assert mdb._lib.device_status(clear=True) == 0
     finally:
         mdb.ops.set_option(mdb.ops.OPT_WAIT_LIMIT_US, old)
+
+
+@pytest.mark.parametrize("m", [32, 256])
+def test_lmhead_sample_full_vocabulary(mdb, m):
+    """The LM head at the decoder's own size (hidden 2048, vocabulary 151936) on identical inputs: a short
+    step (weight-streaming kernel) and a many-row step (tile GEMM with the sampler epilogue).  Sampled tokens
+    and confidences against the oracle's ``F.linear`` + ``Sampler.prepare``; a differing token must be a tie
+    within one bf16 step of the logits."""
+    gen = torch.Generator().manual_seed(m)
+    h, v, block = 2048, 151936, 32
+    hidden = torch.randn(m, h, generator=gen).to(BF)
+    w = (0.02 * torch.randn(v, h, generator=gen)).to(BF)
+    temps = torch.tensor([1.0, 0.3] * (m // block // 2) + [1.0] * (m // block % 2))
+    noise = mdb.ops.gumbel_noise(m, v, 77, 3, DEV).cpu()
+    x0, conf = mdb.ops.lm_head_sample(hidden.to(DEV), w.to(DEV), temps.to(DEV), block, seed=77, step=3)
+    logits = orc.linear(hidden, w).view(m // block, block, v)
+    want_x0, want_p = orc.sampler_prepare(logits, temps.view(-1, 1), noise.view(m // block, block, v))
+    want_x0, want_p = want_x0.view(-1), want_p.view(-1)
+    got = x0.cpu().long()
+    agree = got == want_x0
+    lf = logits.float().view(m, v) / temps.repeat_interleave(block).view(m, 1)
+    noisy = lf + noise
+    for i in (~agree).nonzero().flatten().tolist():
+        assert abs(float(noisy[i, got[i]] - noisy[i, want_x0[i]])) <= 0.04 / float(temps[i // block])
+    assert float(agree.float().mean()) >= 0.95
+    assert torch.allclose(conf.cpu()[agree], want_p[agree], rtol=3e-2)
+    _status_clean(mdb)

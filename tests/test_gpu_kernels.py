@@ -747,5 +747,8 @@ def test_lmhead_sample_full_vocabulary(mdb, m):
     for i in (~agree).nonzero().flatten().tolist():
         assert abs(float(noisy[i, got[i]] - noisy[i, want_x0[i]])) <= 0.04 / float(temps[i // block])
     assert float(agree.float().mean()) >= 0.95
-    assert torch.allclose(conf.cpu()[agree], want_p[agree], rtol=3e-2)
+    # one bf16 step of the sampled token's logit (2^-5 at |logit| in [4, 8)) moves its probability by e^(step / T)
+    row_t = temps.repeat_interleave(block)[agree]
+    rel = (conf.cpu()[agree] - want_p[agree]).abs() / want_p[agree]
+    assert bool((rel <= torch.expm1(0.03125 / row_t) + 2e-3).all()), float(rel.max())
     _status_clean(mdb)

@@ -14,10 +14,14 @@ namespace mdb {
 // Keys per key-range part of one request: an even share of its context rounded up to whole key tiles, but
 // never fewer than 256 keys, so that a part count chosen for the longest admissible context does not cut a
 // short one into single-tile parts (the trailing parts are then empty and cost one zero record each).
+#ifndef MDB_ATTN_MIN_PART_KEYS
+#define MDB_ATTN_MIN_PART_KEYS 256
+#endif
+constexpr int kAttnMinPartKeys = MDB_ATTN_MIN_PART_KEYS;
 __host__ __device__ __forceinline__ int attn_part_keys(int ctx, int nsplit, int tile_keys) {
   if (ctx <= 0) return 0;
   const int share = ((ctx + nsplit - 1) / nsplit + tile_keys - 1) / tile_keys * tile_keys;
-  return nsplit > 1 && share < 256 ? 256 : share;
+  return nsplit > 1 && share < kAttnMinPartKeys ? kAttnMinPartKeys : share;
 }
 
 struct AttnPagedArgs {

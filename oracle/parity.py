@@ -59,8 +59,8 @@ def decode_parity(pkg, ocfg: "orc.DecoderConfig", weights: "orc.DecoderWeights",
       ``LOGIT_TOL`` cannot flip (fixed tolerance, not widened by the measured error);
     * ``x0_agree`` / ``x0_total``: sampled tokens over all rows of all passes;
     * ``logits_fp32_max_abs``: worst |CUDA - oracle| over the un-rounded fp32 logits implied by the two
-      final-norm hidden states (both through the oracle's LM head); ``logits_bf16_max_ulp``: the same after
-      the reference's rounding of the logits to bf16, in bf16 steps;
+      final-norm hidden states (both through the oracle's LM head); ``logits_bf16_max_abs``: the same after
+      the reference's rounding of the logits to bf16 (one bf16 step at |logit| >= 4 is 0.031);
     * ``oracle_floor_logits_fp32_max_abs``: the same figure between the oracle and itself with the one rounding
       inside its attention left out (probabilities kept in fp32 instead of rounded to bf16 before PV, which
       flash-attn does per key tile against a running maximum and no restatement can place identically), on the
@@ -137,7 +137,7 @@ def _decode_parity(pkg, ocfg, weights, context, passes, temperature, threshold, 
     del twin
     lm_w32 = weights.lm_head.float()
     out = dict(decisions=0, decisions_agree=0, robust_decisions=0, robust_agree=0, x0_total=0, x0_agree=0,
-               logits_fp32_max_abs=0.0, logits_bf16_max_ulp=0, conf_max_rel=0.0, kv_rows=0, kv_max_abs=0.0,
+               logits_fp32_max_abs=0.0, logits_bf16_max_abs=0.0, conf_max_rel=0.0, kv_rows=0, kv_max_abs=0.0,
                kv_exact_frac=1.0, passes=0, commit_passes=0, multi_token_passes=0, disagreements=[],
                oracle_floor_logits_fp32_max_abs=None)
     for _ in range(passes):
@@ -156,10 +156,8 @@ def _decode_parity(pkg, ocfg, weights, context, passes, temperature, threshold, 
             out["oracle_floor_logits_fp32_max_abs"] = round(float((lf_ref - twin_hidden @ lm_w32.t()).abs().max()), 6)
         err = float((lf_ref - lf_got).abs().max())
         out["logits_fp32_max_abs"] = max(out["logits_fp32_max_abs"], err)
-        a = lf_ref.to(torch.bfloat16).view(torch.int16).to(torch.int32)
-        b = lf_got.to(torch.bfloat16).view(torch.int16).to(torch.int32)
-        key = lambda i: torch.where(i < 0, -(i & 0x7FFF), i)      # noqa: E731  (monotone integer image of bf16)
-        out["logits_bf16_max_ulp"] = max(out["logits_bf16_max_ulp"], int((key(a) - key(b)).abs().max()))
+        out["logits_bf16_max_abs"] = max(out["logits_bf16_max_abs"],
+                                         float((lf_ref.to(torch.bfloat16).float() - lf_got.to(torch.bfloat16).float()).abs().max()))
         if not is_commit:
             x0_ref = last["x0"].view(-1)
             x0_got = runner.last["x0"].cpu().long()
@@ -213,7 +211,7 @@ def _decode_parity(pkg, ocfg, weights, context, passes, temperature, threshold, 
     out.update(device_status=status, context=context, temperature=temperature, threshold=threshold, block=block,
                layers=ocfg.num_hidden_layers, hidden=ocfg.hidden_size, vocab=vocab, graphs=not eager,
                logit_tol=LOGIT_TOL, seconds=round(time.perf_counter() - t_start, 1))
-    for k in ("logits_fp32_max_abs", "conf_max_rel", "kv_max_abs", "kv_exact_frac"):
+    for k in ("logits_fp32_max_abs", "logits_bf16_max_abs", "conf_max_rel", "kv_max_abs", "kv_exact_frac"):
         out[k] = round(out[k], 6)
     out["decision_agreement"] = round(out["decisions_agree"] / max(out["decisions"], 1), 5)
     out["robust_agreement"] = round(out["robust_agree"] / max(out["robust_decisions"], 1), 5)

@@ -8,6 +8,7 @@ import sys as _sys
 
 from . import _lib, ops
 from .decoder import DecoderEngine, DecoderWeights, LayerWeights
+from .loader import load_decoder_weights
 from .engine import (BlockManager, Config, Context, DecoderConfig, SamplingParams, Scheduler, Sequence,
                      SequenceStatus)
 from .engine.llm_engine import LLMEngine
@@ -15,5 +16,5 @@ from .engine.model_runner import ModelRunner
 
 _sys.modules.setdefault("mineru_diffusion_b200", _sys.modules[__name__])
 
-__all__ = ["ops", "DecoderEngine", "DecoderWeights", "LayerWeights", "BlockManager", "Config", "Context",
+__all__ = ["ops", "DecoderEngine", "DecoderWeights", "LayerWeights", "load_decoder_weights", "BlockManager", "Config", "Context",
            "DecoderConfig", "SamplingParams", "Scheduler", "Sequence", "SequenceStatus", "LLMEngine", "ModelRunner"]

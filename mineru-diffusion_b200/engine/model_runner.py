@@ -111,7 +111,9 @@ class ModelRunner:
         torch.cuda.set_device(self.device)
         self.full_dcfg = self._decoder_config(config)
         self.dcfg = self.full_dcfg
-        full = weights if weights is not None else DecoderWeights.random_init(self.full_dcfg, weight_seed, self.device)
+        from .. import loader
+        model_dir = getattr(config, "model", None)
+        from_checkpoint = weights is None and loader.has_checkpoint(model_dir)
         if self.world_size == 2:
             # One process per GPU, every rank calling run() with the same requests (the sampler's decisions
             # are bit-identical on both ranks, so the two schedulers stay in step without a control channel).
@@ -120,10 +122,17 @@ class ModelRunner:
                 torch.distributed.init_process_group("nccl", init_method="tcp://127.0.0.1:2333", world_size=2,
                                                      rank=rank, device_id=self.device)
             self.dcfg = tp_mod.shard_config(self.full_dcfg, 2)
-            self.weights = tp_mod.shard_weights(full, self.full_dcfg, rank, 2)
-            del full
+        if from_checkpoint:
+            # the model directory holds safetensors files: read this rank's share, as the reference's load_model does
+            self.weights = loader.load_decoder_weights(model_dir, self.full_dcfg, self.device, rank if self.world_size == 2
+                                                       else 0, self.world_size)
         else:
-            self.weights = full
+            full = weights if weights is not None else DecoderWeights.random_init(self.full_dcfg, weight_seed, self.device)
+            if self.world_size == 2:
+                self.weights = tp_mod.shard_weights(full, self.full_dcfg, rank, 2)
+                del full
+            else:
+                self.weights = full
         self.noise = noise
         self.noise_seed = noise_seed
         self.noise_fn = None          # explicit mode: fn(step_index, m, vocab) -> fp32 [m, vocab] CUDA tensor

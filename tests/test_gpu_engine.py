@@ -638,3 +638,51 @@ def test_runner_follows_quota_schedule(mdb):
     assert counts == [7, 7, 7, 7, 6, 6, 6, 6, 6, 6] * 2, counts
     assert same / total >= 0.97
     assert mdb._lib.device_status(clear=True) == 0
+
+
+def test_runner_loads_a_checkpoint_directory(mdb, tmp_path):
+    """``Config(model=<directory>)`` with a config.json and safetensors files in the reference's parameter names
+    (nanovllm/config.py:55-59, nanovllm/utils/loader.py:12-28): the runner built from the directory generates
+    the tokens of the runner handed the same weights in memory."""
+    import json
+    from safetensors.torch import save_file
+    dcfg = _tiny_cfg(mdb, vocab=1024, layers=2)
+    w = orc.make_weights(_oracle_cfg(dcfg), seed=23)
+    hq, hkv, d, inter = dcfg.num_attention_heads, dcfg.num_key_value_heads, dcfg.head_dim, dcfg.intermediate_size
+    t = {"language_model.model.embed_tokens.weight": w.embed, "language_model.model.norm.weight": w.final_ln,
+         "language_model.lm_head.weight": w.lm_head}
+    for li, lw in enumerate(w.layers):
+        p = f"language_model.model.layers.{li}."
+        q, k, v = lw.qkv.split([hq * d, hkv * d, hkv * d], dim=0)
+        gate, up = lw.gate_up.split([inter, inter], dim=0)
+        t.update({p + "self_attn.q_proj.weight": q, p + "self_attn.k_proj.weight": k, p + "self_attn.v_proj.weight": v,
+                  p + "self_attn.o_proj.weight": lw.o, p + "self_attn.q_norm.weight": lw.q_norm,
+                  p + "self_attn.k_norm.weight": lw.k_norm, p + "input_layernorm.weight": lw.input_ln,
+                  p + "post_attention_layernorm.weight": lw.post_ln, p + "mlp.gate_proj.weight": gate,
+                  p + "mlp.up_proj.weight": up, p + "mlp.down_proj.weight": lw.down})
+    save_file({n: x.contiguous() for n, x in t.items()}, str(tmp_path / "model.safetensors"))
+    text = dict(vocab_size=dcfg.vocab_size, hidden_size=dcfg.hidden_size, intermediate_size=inter,
+                num_hidden_layers=dcfg.num_hidden_layers, num_attention_heads=hq, num_key_value_heads=hkv, head_dim=d,
+                rms_norm_eps=dcfg.rms_norm_eps, rope_theta=dcfg.rope_theta,
+                max_position_embeddings=dcfg.max_position_embeddings, tie_word_embeddings=False)
+    with open(tmp_path / "config.json", "w") as f:
+        json.dump({"model_type": "mineru_diffusion", "text_config": text}, f)
+    gen = torch.Generator().manual_seed(2)
+    prompt = torch.randint(0, 490, (120,), generator=gen).tolist()
+    outs = []
+    for from_dir in (False, True):
+        kw = dict(max_num_batched_tokens=2048, max_num_seqs=1, max_model_len=1024, enforce_eager=True,
+                  num_kvcache_blocks=4, mask_token_id=500)
+        if from_dir:
+            cfg = mdb.Config(model=str(tmp_path), **kw)
+            runner = mdb.ModelRunner(cfg, noise="none")
+        else:
+            cfg = mdb.Config(decoder_config=dcfg, **kw)
+            runner = mdb.ModelRunner(cfg, weights=mdb.DecoderWeights.from_reference_layout(w, DEV), noise="none")
+        engine = mdb.LLMEngine(cfg, runner)
+        sp = mdb.SamplingParams(temperature=0.05, max_new_tokens=64, ignore_eos=True)
+        seq = mdb.Sequence(list(prompt), sp, denoising_block_size=32, mask_token_id=500)
+        done, _ = engine.generate([seq])
+        outs.append(done[seq.seq_id][0])
+        runner.exit()
+    assert outs[0] == outs[1] and len(outs[0]) == 64

@@ -105,6 +105,7 @@ def test_block_attention_against_flash_attn_with_kvcache(mdb, hkv):
 
 def test_swiglu_epilogue_against_liger(mdb):
     try:
+        import torch.distributed.tensor  # noqa: F401  (liger 0.8 reads this submodule without importing it)
         from liger_kernel.ops.swiglu import LigerSiLUMulFunction
     except Exception as exc:            # noqa: BLE001
         pytest.skip(f"liger-kernel does not import: {exc!r}")

@@ -5,6 +5,7 @@
     python microbench.py gemm --m 2048
     python microbench.py lmhead --m 2048
     python microbench.py elementwise --m 2048
+    python microbench.py kvcommit --m 32768
 
 Each operator is captured ``--reps`` times into one CUDA graph and the graph
 is timed with CUDA events, so host launch cost stays out of the figure; the
@@ -188,6 +189,38 @@ def bench_lmhead(a) -> None:
     line(f"lm_head+sampler (argmax) m={m} v={v}", ms, 2.0 * m * v * h, 2.0 * v * h)
 
 
+def kvcommit_cases(m: int, hq: int = 16, hkv: int = 8, reps: int = 10, plain: bool = False, seed: int = 3) -> list[dict]:
+    """The paged KV write/commit at ``m`` token rows: the plain row scatter (``store_kvcache``) and the step's
+    form fused with the q/k norm and the rotary embedding.  Bytes = what each must move once: the scatter reads
+    and writes the K and V rows (2 * 2 * m * hkv * 128 * 2 B); the fused form reads the bf16 qkv row and writes
+    q plus the K and V cache rows."""
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    d = 128
+    pages = (m + 255) // 256 + 1
+    k = torch.randn(m, hkv, d, generator=g, device=DEV).to(BF)
+    v = torch.randn(m, hkv, d, generator=g, device=DEV).to(BF)
+    kc = torch.zeros(pages, 256, hkv, d, dtype=BF, device=DEV)
+    vc = torch.zeros_like(kc)
+    slots = torch.randperm(pages * 256, generator=g, device=DEV)[:m].int()
+    out = [dict(op="kv_commit", m=m, ms=timed(lambda: ops.store_kvcache(k, v, kc, vc, slots), reps, plain),
+                bytes=2.0 * 2 * m * hkv * d * 2)]
+    qkv = torch.randn(m, (hq + 2 * hkv) * d, generator=g, device=DEV).to(BF)
+    pos = torch.arange(m, device=DEV) % 4096
+    table = pkg.decoder.rope_table(4096, d, 1e6, DEV)
+    ones = torch.ones(d, dtype=BF, device=DEV)
+    q = torch.empty(m, hq, d, dtype=BF, device=DEV)
+    out.append(dict(op="qknorm_rope_commit", m=m,
+                    ms=timed(lambda: ops.qknorm_rope_commit(qkv, pos, table, ones, ones, 1e-6, hq, hkv, slots, kc, vc,
+                                                            q_out=q), reps, plain),
+                    bytes=2.0 * m * (hq + 2 * hkv) * d * 2))
+    return out
+
+
+def bench_kvcommit(a) -> None:
+    for c in kvcommit_cases(a.m, a.hq, a.hkv, a.reps, a.plain, a.seed):
+        line(f"{c['op']} m={c['m']}", c["ms"], None, c["bytes"])
+
+
 def bench_elementwise(a) -> None:
     g = torch.Generator(device=DEV).manual_seed(a.seed)
     m, h = a.m, a.hidden
@@ -203,7 +236,7 @@ def bench_elementwise(a) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("op", choices=["attn", "stair", "gemm", "lmhead", "elementwise"])
+    ap.add_argument("op", choices=["attn", "stair", "gemm", "lmhead", "elementwise", "kvcommit"])
     ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--plain", action="store_true", help="launch without a CUDA graph")
     ap.add_argument("--seed", type=int, default=3)
@@ -222,7 +255,8 @@ def main() -> None:
     a = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("needs a GPU")
-    {"attn": bench_attn, "stair": bench_stair, "gemm": bench_gemm, "lmhead": bench_lmhead, "elementwise": bench_elementwise}[a.op](a)
+    {"attn": bench_attn, "stair": bench_stair, "gemm": bench_gemm, "lmhead": bench_lmhead, "elementwise": bench_elementwise,
+     "kvcommit": bench_kvcommit}[a.op](a)
     status = pkg._lib.device_status()
     print("device status", status)
     if status:

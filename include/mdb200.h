@@ -41,7 +41,8 @@ enum {
                                    longer than the page-table row can address (cut to the row): output rows invalid */
   MDB_STATUS_BAD_TOKEN = 4u,    /* token id outside the embedding table: row zeroed */
   MDB_STATUS_BAD_POSITION = 8u, /* position outside the rotary table: row left unrotated */
-  MDB_STATUS_WAIT_TIMEOUT = 16u /* a bounded wait on a peer flag or barrier expired */
+  MDB_STATUS_WAIT_TIMEOUT = 16u, /* a bounded wait on a peer flag or barrier expired */
+  MDB_STATUS_LAYOUT = 32u        /* a kernel found its shared memory placed otherwise than it was built for and did nothing */
 };
 
 const char* mdb_strerror(int code);

@@ -10,8 +10,11 @@
 // One work unit = the query rows of `tokens x group` (tokens of one request or
 // sequence times the query heads that share a KV head; row = token * group +
 // head_in_group) against a key range.  ROWS = 64 or 128 rows per unit: the MMA
-// is always M = 128, with ROWS = 64 the upper operand rows are whatever follows
-// in shared memory and only feed accumulator lanes nobody reads.  Persistent
+// is always M = 128.  With ROWS = 64 (paged form) the Q tile holds the rows
+// twice, so that S carries every row in two tensor-memory lanes and the softmax
+// of a tile is spread over four warps, two per row, 64 keys each; the P tile has
+// the 64 real rows only (the upper operand rows of P V are whatever follows in
+// shared memory and feed accumulator lanes nobody reads).  Persistent
 // CTAs, one per SM, walk the units; inside a CTA
 //   producer warp  TMA: the Q tile (3-D box: 64 channels x group x tokens) and
 //            128-key K and V tiles ([tokens, hkv*128] seen as a matrix, boxes
@@ -40,14 +43,24 @@ constexpr float kAtRescaleStep = 8.0f;                // log2 units a row maximu
 constexpr int kAtMaxRanked = 512;                     // batches above this are walked in request order
 
 // Shared-memory plan for ROWS query rows per unit (224 KB of tiles either way).
-template <int ROWS>
+//
+// DUP (64-row units of the paged form): the softmax of a 128-key tile is bound by the exponential unit of the
+// sub-partitions that hold the softmax warps (128 ex2 per row on a quarter-rate pipe), so the 64 rows are spread
+// over all four: the Q tile holds the 64 rows twice (operand rows 64..127 repeat rows 0..63), S = Q K^T therefore
+// carries every row in two tensor-memory lanes, and the thread of lane r takes keys 0..63 of the tile while the
+// thread of lane r + 64 takes keys 64..127 of the same row.  The two exchange their row maximum through shared
+// memory, write their halves of the same P row, and add up their partial sums at the end of the unit.
+template <int ROWS, bool DUP = false>
 struct AtPlan {
-  static constexpr int kQBufs = ROWS == 64 ? 2 : 1;
+  static_assert(!DUP || ROWS == 64, "row duplication exists for the 64-row units");
+  static constexpr int kQRows = DUP ? 128 : ROWS;     // rows of the Q operand tile
+  static constexpr int kQBufs = (ROWS == 64 && !DUP) ? 2 : 1;
   static constexpr int kKStages = 2;
   static constexpr int kVStages = ROWS == 64 ? 3 : 2;
-  static constexpr int kQBytes = 2 * ROWS * 128;      // two channel halves of [ROWS][128 B]
+  static constexpr int kQBytes = 2 * kQRows * 128;    // two channel halves of [kQRows][128 B]
   static constexpr int kPBytes = 2 * ROWS * 128;      // two key halves of [ROWS][128 B]
-  static constexpr int kSoftmaxWarps = ROWS / 32;
+  static constexpr int kSoftmaxWarps = DUP ? 4 : ROWS / 32;
+  static constexpr int kCols = DUP ? 64 : 128;        // keys of a tile one softmax thread handles
   static constexpr int kProducerWarp = kSoftmaxWarps, kMmaWarp = kSoftmaxWarps + 1;
   static constexpr int kThreads = (kSoftmaxWarps + 2) * 32;
   static constexpr int kOffQ = 0;
@@ -55,7 +68,12 @@ struct AtPlan {
   static constexpr int kOffK = kOffP + 2 * kPBytes;
   static constexpr int kOffV = kOffK + kKStages * kAtTileBytes;
   static constexpr int kOffBars = kOffV + kVStages * kAtTileBytes;
-  static constexpr int kSmemBytes = 1024 + kOffBars + 256 + 2 * kAtMaxRanked;   // + barriers, tensor-memory slot, ranks
+  static constexpr int kMaxRanked = DUP ? 256 : kAtMaxRanked;          // batches above this are walked in request order
+  static constexpr int kOffXch = kOffBars + 256 + 2 * kMaxRanked;   // DUP: [2][128] tagged values swapped by the two threads of a row
+  // + barriers, tensor-memory slot, ranks; up to 1 KB in front to reach a 1024-byte boundary.  The DUP layout has
+  // no room for that slack: it counts on the dynamic shared memory starting on such a boundary (it does when the
+  // kernel has no static shared memory) and the kernel checks the size it was given before it touches anything.
+  static constexpr int kSmemBytes = DUP ? kOffXch + 2 * 128 * 8 + 128 : 1024 + kOffXch;
 };
 
 // barrier slots (8 bytes each) after the tiles
@@ -158,7 +176,8 @@ struct AtUnit {
 };
 
 template <bool STAIR>
-__device__ __forceinline__ AtUnit at_unit(const AtArgs& a, const uint16_t* order, int units, int wave) {
+__device__ __forceinline__ AtUnit at_unit(const AtArgs& a, const uint16_t* order, int units, int wave,
+                                          int max_ranked = kAtMaxRanked) {
   AtUnit w = {};
   const int G = static_cast<int>(gridDim.x), c = static_cast<int>(blockIdx.x);
   if (STAIR) {
@@ -188,7 +207,7 @@ __device__ __forceinline__ AtUnit at_unit(const AtArgs& a, const uint16_t* order
   w.valid = true;
   const int per_req = a.hkv * a.row_blocks * a.nsplit;
   const int ranked = p / per_req, rem = p % per_req;
-  w.req = a.bs <= kAtMaxRanked ? static_cast<int>(order[ranked]) : ranked;
+  w.req = a.bs <= max_ranked ? static_cast<int>(order[ranked]) : ranked;
   w.kvh = rem / (a.row_blocks * a.nsplit);
   w.tok0 = (rem / a.nsplit) % a.row_blocks * a.tokens_per_unit;
   w.split = rem % a.nsplit;
@@ -214,15 +233,48 @@ struct AtRing {
   }
 };
 
-template <int ROWS, bool STAIR>
-__global__ void __launch_bounds__(AtPlan<ROWS>::kThreads, 1)
+// DUP layout: the two threads that share a query row (tensor-memory lanes r and r + 64, in different warps) swap
+// one float.  Each writes (running number, value) as one 8-byte word into its slot of buffer `number & 1` and polls
+// the partner's slot of the same buffer until it carries the same number; a thread starts swap n + 2 only after
+// it has read the partner's word of swap n + 1, which the partner wrote after reading this thread's word of swap
+// n, so two buffers are enough.  The wait is bounded like every other wait of the kernel.
+__device__ __forceinline__ bool at_swap(volatile unsigned long long* xch, int lane_row, uint32_t number, float mine,
+                                        float& other) {
+  volatile unsigned long long* buf = xch + (number & 1u) * 128;
+  buf[lane_row] = (static_cast<unsigned long long>(number) << 32) | __float_as_uint(mine);
+  unsigned long long deadline = 0;
+  for (uint32_t it = 0;; ++it) {
+    const unsigned long long v = buf[lane_row ^ 64];
+    if (static_cast<uint32_t>(v >> 32) == number) {
+      other = __uint_as_float(static_cast<uint32_t>(v));
+      return true;
+    }
+    if ((it & 1023u) == 1023u) {
+      const unsigned long long now = global_timer_ns();
+      if (deadline == 0) deadline = now + g_wait_limit_ns;
+      else if (now > deadline) return false;
+    }
+  }
+}
+
+template <int ROWS, bool STAIR, bool DUP = false>
+__global__ void __launch_bounds__(AtPlan<ROWS, DUP>::kThreads, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const AtArgs a, const int units) {
-  using P = AtPlan<ROWS>;
-  extern __shared__ unsigned char at_smem_raw[];
+  using P = AtPlan<ROWS, DUP>;
+  static_assert(!(DUP && STAIR), "row duplication is a paged-form layout");
+  extern __shared__ __align__(1024) unsigned char at_smem_raw[];
   const uint32_t raw = smem_u32(at_smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char* gen_base = at_smem_raw + (base - raw);
+  if (DUP) {
+    uint32_t given;
+    asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(given));
+    if ((base - raw) + static_cast<uint32_t>(P::kOffXch + 2 * 128 * 8) > given) {   // never on the boards this was built for
+      if (threadIdx.x == 0) report_status(MDB_STATUS_LAYOUT);
+      return;
+    }
+  }
   const uint32_t bars = base + P::kOffBars;
   auto bar = [&](int slot) { return bars + 8u * static_cast<uint32_t>(slot); };
   volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(gen_base + P::kOffBars + 8 * kAtBarCount);
@@ -235,7 +287,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 
   if (threadIdx.x == 0) trace_event(30, 0);
   pdl_launch_dependents();
-  if (!STAIR && a.bs <= kAtMaxRanked) {
+  if (!STAIR && a.bs <= P::kMaxRanked) {
     // context lengths are step inputs, not written by the kernels this one is chained to
     for (int r = threadIdx.x; r < a.bs; r += P::kThreads) {
       const int mine = a.ctx_lens[r];
@@ -246,6 +298,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       }
       order[rank] = static_cast<uint16_t>(r);
     }
+  }
+  if (DUP) {
+    unsigned long long* xz = reinterpret_cast<unsigned long long*>(gen_base + P::kOffXch);
+    for (int i = threadIdx.x; i < 256; i += P::kThreads) xz[i] = 0ull;
   }
   if (threadIdx.x == 0) {
     for (int s = 0; s < kAtBarCount; ++s) {
@@ -290,16 +346,20 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         return true;
       };
       for (int wave = 0; wave < waves && ok; ++wave) {
-        const AtUnit w = at_unit<STAIR>(a, order, units, wave);
+        const AtUnit w = at_unit<STAIR>(a, order, units, wave, P::kMaxRanked);
         if (w.ctx_clamped) report_status(MDB_STATUS_BAD_PAGE);
         if (w.ntiles == 0) continue;
         if (!mbar_wait(bar(kAtBarQEmpty + qr.stage), qr.phase ^ 1)) { ok = false; break; }
         {
           const uint32_t full = bar(kAtBarQFull + qr.stage);
           const uint32_t dst = base + P::kOffQ + qr.stage * P::kQBytes;
-          mbar_arrive_expect_tx(full, static_cast<uint32_t>(rows_used) * 256u);
+          mbar_arrive_expect_tx(full, static_cast<uint32_t>(rows_used) * (DUP ? 512u : 256u));
           tma_load_3d(dst, &map_q, 0, w.kvh * group, w.q_tok0, full);
-          tma_load_3d(dst + ROWS * 128, &map_q, 64, w.kvh * group, w.q_tok0, full);
+          tma_load_3d(dst + P::kQRows * 128, &map_q, 64, w.kvh * group, w.q_tok0, full);
+          if (DUP) {      // the same rows once more as operand rows 64..
+            tma_load_3d(dst + 64 * 128, &map_q, 0, w.kvh * group, w.q_tok0, full);
+            tma_load_3d(dst + P::kQRows * 128 + 64 * 128, &map_q, 64, w.kvh * group, w.q_tok0, full);
+          }
           pend_q |= 1u << qr.stage;
           par_q = (par_q & ~(1u << qr.stage)) | (qr.phase << qr.stage);
           qr.advance(P::kQBufs);
@@ -344,7 +404,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       uint32_t o_phase = 0;             // parity of the o_empty phase to wait for
       bool ok = true;
       for (int wave = 0; wave < waves && ok; ++wave) {
-        const AtUnit w = at_unit<STAIR>(a, order, units, wave);
+        const AtUnit w = at_unit<STAIR>(a, order, units, wave, P::kMaxRanked);
         if (w.ntiles == 0) continue;
         // staircase form: the softmax warps scale q in place first
         if (!mbar_wait(bar((STAIR ? kAtBarQReady : kAtBarQFull) + qr.stage), qr.phase)) { ok = false; break; }
@@ -357,7 +417,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           const uint32_t d_tmem = tmem_base + sr.stage * kAtKeys;
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
-            const uint64_t adesc = umma_desc_sw128(q_tile + (kk >> 2) * (ROWS * 128)) + 2 * (kk & 3);
+            const uint64_t adesc = umma_desc_sw128(q_tile + (kk >> 2) * (P::kQRows * 128)) + 2 * (kk & 3);
             const uint64_t bdesc = umma_desc_sw128(k_tile + (kk >> 2) * kAtHalfBytes) + 2 * (kk & 3);
             umma_bf16(d_tmem, adesc, bdesc, idesc_s, kk > 0 ? 1u : 0u);
           }
@@ -400,15 +460,21 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     }
   } else {
     // ------------------------------------------------------------------- softmax
-    const int row = 32 * warp + lane;
+    const int lane_row = 32 * warp + lane;                 // tensor-memory lane of this thread
+    const int row = DUP ? (lane_row & 63) : lane_row;      // query row of the unit
+    const int half = DUP ? (lane_row >> 6) : 0;            // DUP: which 64 keys of a tile this thread takes
+    const int col0 = 64 * half;
+    constexpr int NC = P::kCols;
     const int tok_local = row / group, head_in_group = row % group;
     const uint32_t lane_field = static_cast<uint32_t>(32 * warp) << 16;
+    volatile unsigned long long* xch = reinterpret_cast<volatile unsigned long long*>(gen_base + P::kOffXch);
+    uint32_t xseq = 0;                                     // DUP: running number of the swaps of this thread
     AtRing sr, pr, vr, qr;             // positions of the tile being handled in the S, P, V and Q rings
     uint32_t prev_p_stage = 0, prev_p_phase = 0;   // P ring position of the previous tile (its P V frees O for a rescale)
     uint32_t o_phase = 0;
     bool ok = true;
     for (int wave = 0; wave < waves && ok; ++wave) {
-      const AtUnit w = at_unit<STAIR>(a, order, units, wave);
+      const AtUnit w = at_unit<STAIR>(a, order, units, wave, P::kMaxRanked);
       if (!w.valid) continue;
       const int head = w.kvh * group + head_in_group;
       bool row_valid = row < rows_used;
@@ -430,7 +496,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         out_row = a.out + ((static_cast<int64_t>(w.req) * a.block + tk) * a.hq + head) * kHeadDim;
       }
       if (w.ntiles == 0) {           // paged form only: an empty key range
-        if (row_valid) {
+        if (row_valid && half == 0) {
           if (a.nsplit == 1) {
 #pragma unroll
             for (int c = 0; c < 16; ++c) reinterpret_cast<uint4*>(out_row)[c] = make_uint4(0u, 0u, 0u, 0u);
@@ -476,25 +542,33 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const int key0 = w.kbeg + j * kAtKeys;
         // keys of this tile the row sees: [0, nvalid)
         const int nvalid = STAIR ? max(0, min(kAtKeys, limit + 1 - key0)) : min(kAtKeys, w.kend - key0);
-        // the whole score row into registers, then the S buffer goes back to the MMA warp
-        float s[kAtKeys];
+        // the thread's share of the score row into registers, then the S buffer goes back to the MMA warp
+        float s[NC];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + 32 * c, s + 32 * c);
+        for (int c = 0; c < NC / 32; ++c) tmem_ld32(s_addr + col0 + 32 * c, s + 32 * c);
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(kAtBarSEmpty + sr.stage));
-        if (nvalid < kAtKeys) {
+        const int nv = nvalid - col0;               // valid keys among this thread's columns: [0, nv)
+        if (nv < NC) {
 #pragma unroll
-          for (int i = 0; i < kAtKeys; ++i) if (i >= nvalid) s[i] = -INFINITY;   // also replaces NaN from stale rows
+          for (int i = 0; i < NC; ++i) if (i >= nv) s[i] = -INFINITY;   // also replaces NaN from stale rows
         }
         float mx0 = fmaxf(s[0], s[1]), mx1 = fmaxf(s[2], s[3]);
 #pragma unroll
-        for (int i = 4; i < kAtKeys; i += 4) {
+        for (int i = 4; i < NC; i += 4) {
           mx0 = fmaxf(mx0, fmaxf(s[i], s[i + 1]));
           mx1 = fmaxf(mx1, fmaxf(s[i + 2], s[i + 3]));
         }
         float mx = fmaxf(mx0, mx1);
+        if (DUP) {
+          // the other half of the row's keys is with the thread 64 lanes away (two warps further): swap maxima
+          float other;
+          ok = at_swap(xch, lane_row, ++xseq, mx, other);
+          if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+          mx = fmaxf(mx, other);
+        }
         if (!row_valid) mx = 0.f;                             // rows past the block hold whatever the tile held
         const float m_tile = mx * a.scale_log2;
         // a row that sees no key of this tile (staircase form, rows above the tile's diagonal) keeps its state
@@ -503,7 +577,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           const float m_new = fmaxf(m_ref, m_tile);
           const float f = m_ref == -INFINITY ? 0.f : ex2_approx(m_ref - m_new);
           l *= f;
-          if (j > 0) {
+          if (j > 0 && half == 0) {     // (DUP: the rows' accumulators are read from lanes 0..63, whose threads rescale them)
             // O is quiet once the previous tile's P V has completed
             ok = mbar_wait(bar(kAtBarPEmpty + prev_p_stage), prev_p_phase);
             if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
@@ -523,10 +597,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         }
         // P = 2^(s * scale - m_ref) rounded to bf16; a masked key gives 2^-inf = 0
         const float m_use = m_ref == -INFINITY ? 0.f : m_ref;   // nothing seen yet: every s is -inf, P = 0
-        uint32_t pk[kAtKeys / 2];
+        uint32_t pk[NC / 2];
         float l0 = 0.f, l1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < kAtKeys; i += 2) {
+        for (int i = 0; i < NC; i += 2) {
           const float p0 = ex2_approx(fmaf(s[i], a.scale_log2, -m_use));
           const float p1 = ex2_approx(fmaf(s[i + 1], a.scale_log2, -m_use));
           l0 += p0;
@@ -540,9 +614,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         // K-major swizzled P tile: 16-byte chunk q of key half h holds keys 64 h + 8 q .. + 7
         const uint32_t p_row = base + P::kOffP + pr.stage * P::kPBytes + row * 128;
 #pragma unroll
-        for (int q = 0; q < 16; ++q) {
+        for (int q = 0; q < NC / 8; ++q) {
           const uint32_t chunk = static_cast<uint32_t>(q & 7) ^ static_cast<uint32_t>(row & 7);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + (q >> 3) * (ROWS * 128) + (chunk << 4)),
+          const int key_half = DUP ? half : (q >> 3);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + key_half * (ROWS * 128) + (chunk << 4)),
                        "r"(pk[4 * q]), "r"(pk[4 * q + 1]), "r"(pk[4 * q + 2]), "r"(pk[4 * q + 3])
                        : "memory");
         }
@@ -551,7 +626,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           ok = mbar_wait(bar(kAtBarVFull + vr.stage), vr.phase);
           if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
           const uint32_t v_tile = base + P::kOffV + vr.stage * kAtTileBytes;
-          for (int r = nvalid + row; r < kAtKeys; r += ROWS) {
+          for (int r = nvalid + lane_row; r < kAtKeys; r += 32 * P::kSoftmaxWarps) {
 #pragma unroll
             for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -576,7 +651,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
       o_phase ^= 1;
       tc_fence_after();
-      if (STAIR || a.nsplit == 1) {
+      if (DUP) {                       // the row's sum of probabilities: this thread's keys + the partner's
+        float other;
+        ok = at_swap(xch, lane_row, ++xseq, l, other);
+        if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+        l += other;
+      }
+      if (half != 0) {
+        // DUP: lanes 64..127 of O belong to operand rows nobody wrote; the rows' outputs leave from lanes 0..63
+      } else if (STAIR || a.nsplit == 1) {
         const float inv = l > 0.f ? 1.0f / l : 0.f;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
@@ -679,22 +762,22 @@ static int at_sm_count() {
   return sm_count;
 }
 
-template <int ROWS, bool STAIR>
+template <int ROWS, bool STAIR, bool DUP = false>
 static int at_launch(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, const AtArgs& a,
                      int64_t units, cudaStream_t st) {
-  using P = AtPlan<ROWS>;
+  using P = AtPlan<ROWS, DUP>;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(attn_tc_kernel<ROWS, STAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, P::kSmemBytes) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(attn_tc_kernel<ROWS, STAIR, DUP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             P::kSmemBytes) != cudaSuccess)
       return MDB_ERR_CUDA;
     attr_set = true;
   }
   if (units > (1 << 30)) return MDB_ERR_UNSUPPORTED;
   const int sms = at_sm_count();
   const int grid = units < sms ? static_cast<int>(units) : sms;
-  return mdb_launch(attn_tc_kernel<ROWS, STAIR>, dim3(grid), dim3(P::kThreads), P::kSmemBytes, st, map_q, map_k, map_v, a,
-                    static_cast<int>(units));
+  return mdb_launch(attn_tc_kernel<ROWS, STAIR, DUP>, dim3(grid), dim3(P::kThreads), P::kSmemBytes, st, map_q, map_k,
+                    map_v, a, static_cast<int>(units));
 }
 
 // ---- paged form ----
@@ -730,7 +813,7 @@ static int attn_tc_launch(const AttnPagedArgs& pa, int bs, cudaStream_t st) {
   if (!get_tensor_map(pa.k_cache, cache_rows, pa.hkv * kHeadDim, pa.hkv * kHeadDim, kAtKeys, &map_k)) return MDB_ERR_CUDA;
   if (!get_tensor_map(pa.v_cache, cache_rows, pa.hkv * kHeadDim, pa.hkv * kHeadDim, kAtKeys, &map_v)) return MDB_ERR_CUDA;
   const int64_t units = static_cast<int64_t>(bs) * pa.hkv * a.row_blocks * pa.nsplit;
-  return rows == 64 ? at_launch<64, false>(map_q, map_k, map_v, a, units, st)
+  return rows == 64 ? at_launch<64, false, true>(map_q, map_k, map_v, a, units, st)
                     : at_launch<128, false>(map_q, map_k, map_v, a, units, st);
 }
 

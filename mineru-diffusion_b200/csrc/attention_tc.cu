@@ -394,7 +394,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     }
   } else if (warp == P::kMmaWarp) {
     // ----------------------------------------------------------------- MMA issue
-    if (lane == 0) {
+    // All 32 lanes walk the loops with warp-uniform operands and one elected lane issues each tcgen05
+    // instruction: issued from a single lane of a divergent warp every tcgen05.mma costs ~130 cycles of issue
+    // time, which at 16 instructions per key tile is twice the time the tensor pipe needs for them.
+    {
       // bf16 x bf16 -> fp32, M = 128, N = 128; bit 16 set: B operand MN-major
       const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kAtKeys >> 3) << 17) |
                                (static_cast<uint32_t>(128 >> 4) << 24);
@@ -407,11 +410,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const AtUnit w = at_unit<STAIR>(a, order, units, wave, P::kMaxRanked);
         if (w.ntiles == 0) continue;
         // staircase form: the softmax warps scale q in place first
-        if (!mbar_wait(bar((STAIR ? kAtBarQReady : kAtBarQFull) + qr.stage), qr.phase)) { ok = false; break; }
+        if (!mbar_wait_w(bar((STAIR ? kAtBarQReady : kAtBarQFull) + qr.stage), qr.phase)) { ok = false; break; }
         const uint32_t q_tile = base + P::kOffQ + qr.stage * P::kQBytes;
         auto issue_s = [&](int j) {
-          if (!mbar_wait(bar(kAtBarKFull + kr.stage), kr.phase)) return false;
-          if (!mbar_wait(bar(kAtBarSEmpty + sr.stage), sr.phase ^ 1)) return false;
+          if (!mbar_wait_w(bar(kAtBarKFull + kr.stage), kr.phase)) return false;
+          if (!mbar_wait_w(bar(kAtBarSEmpty + sr.stage), sr.phase ^ 1)) return false;
           tc_fence_after();
           const uint32_t k_tile = base + P::kOffK + kr.stage * kAtTileBytes;
           const uint32_t d_tmem = tmem_base + sr.stage * kAtKeys;
@@ -419,11 +422,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           for (int kk = 0; kk < 8; ++kk) {
             const uint64_t adesc = umma_desc_sw128(q_tile + (kk >> 2) * (P::kQRows * 128)) + 2 * (kk & 3);
             const uint64_t bdesc = umma_desc_sw128(k_tile + (kk >> 2) * kAtHalfBytes) + 2 * (kk & 3);
-            umma_bf16(d_tmem, adesc, bdesc, idesc_s, kk > 0 ? 1u : 0u);
+            umma_bf16_w(d_tmem, adesc, bdesc, idesc_s, kk > 0 ? 1u : 0u);
           }
-          umma_commit(bar(kAtBarKEmpty + kr.stage));
-          umma_commit(bar(kAtBarSFull + sr.stage));
-          if (j == w.ntiles - 1) umma_commit(bar(kAtBarQEmpty + qr.stage));
+          umma_commit_w(bar(kAtBarKEmpty + kr.stage));
+          umma_commit_w(bar(kAtBarSFull + sr.stage));
+          if (j == w.ntiles - 1) umma_commit_w(bar(kAtBarQEmpty + qr.stage));
           kr.advance(P::kKStages);
           sr.advance(2);
           return true;
@@ -432,11 +435,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         for (int j = 0; j < w.ntiles && ok; ++j) {
           if (j + 1 < w.ntiles) ok = issue_s(j + 1);
           if (!ok) break;
-          if (!mbar_wait(bar(kAtBarVFull + vr.stage), vr.phase)) { ok = false; break; }
-          if (!mbar_wait(bar(kAtBarPFull + pr.stage), pr.phase)) { ok = false; break; }
+          if (!mbar_wait_w(bar(kAtBarVFull + vr.stage), vr.phase)) { ok = false; break; }
+          if (!mbar_wait_w(bar(kAtBarPFull + pr.stage), pr.phase)) { ok = false; break; }
           if (j == 0) {
             // the previous unit's accumulator must have been read out
-            if (!mbar_wait(bar(kAtBarOEmpty), o_phase ^ 1)) { ok = false; break; }
+            if (!mbar_wait_w(bar(kAtBarOEmpty), o_phase ^ 1)) { ok = false; break; }
             o_phase ^= 1;
           }
           tc_fence_after();
@@ -446,17 +449,17 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           for (int kk = 0; kk < 8; ++kk) {
             const uint64_t adesc = umma_desc_sw128(p_tile + (kk >> 2) * (ROWS * 128)) + 2 * (kk & 3);
             const uint64_t bdesc = umma_desc_sw128_mn(v_tile + kk * 2048);
-            umma_bf16(tmem_o, adesc, bdesc, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+            umma_bf16_w(tmem_o, adesc, bdesc, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
           }
-          umma_commit(bar(kAtBarVEmpty + vr.stage));
-          umma_commit(bar(kAtBarPEmpty + pr.stage));
-          if (j == w.ntiles - 1) umma_commit(bar(kAtBarOFull));
+          umma_commit_w(bar(kAtBarVEmpty + vr.stage));
+          umma_commit_w(bar(kAtBarPEmpty + pr.stage));
+          if (j == w.ntiles - 1) umma_commit_w(bar(kAtBarOFull));
           vr.advance(P::kVStages);
           pr.advance(2);
         }
         qr.advance(P::kQBufs);
       }
-      if (!ok) report_status(MDB_STATUS_WAIT_TIMEOUT);
+      if (!ok && lane == 0) report_status(MDB_STATUS_WAIT_TIMEOUT);
     }
   } else {
     // ------------------------------------------------------------------- softmax
@@ -555,13 +558,16 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < NC; ++i) if (i >= nv) s[i] = -INFINITY;   // also replaces NaN from stale rows
         }
-        float mx0 = fmaxf(s[0], s[1]), mx1 = fmaxf(s[2], s[3]);
+        // eight independent chains: the warp is alone on its sub-partition, nothing else hides the ALU latency
+        float mxv[8];
 #pragma unroll
-        for (int i = 4; i < NC; i += 4) {
-          mx0 = fmaxf(mx0, fmaxf(s[i], s[i + 1]));
-          mx1 = fmaxf(mx1, fmaxf(s[i + 2], s[i + 3]));
+        for (int k = 0; k < 8; ++k) mxv[k] = s[k];
+#pragma unroll
+        for (int i = 8; i < NC; i += 8) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) mxv[k] = fmaxf(mxv[k], s[i + k]);
         }
-        float mx = fmaxf(mx0, mx1);
+        float mx = fmaxf(fmaxf(fmaxf(mxv[0], mxv[1]), fmaxf(mxv[2], mxv[3])), fmaxf(fmaxf(mxv[4], mxv[5]), fmaxf(mxv[6], mxv[7])));
         if (DUP) {
           // the other half of the row's keys is with the thread 64 lanes away (two warps further): swap maxima
           float other;
@@ -598,16 +604,18 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         // P = 2^(s * scale - m_ref) rounded to bf16; a masked key gives 2^-inf = 0
         const float m_use = m_ref == -INFINITY ? 0.f : m_ref;   // nothing seen yet: every s is -inf, P = 0
         uint32_t pk[NC / 2];
-        float l0 = 0.f, l1 = 0.f;
+        float lv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int i = 0; i < NC; i += 2) {
-          const float p0 = ex2_approx(fmaf(s[i], a.scale_log2, -m_use));
-          const float p1 = ex2_approx(fmaf(s[i + 1], a.scale_log2, -m_use));
-          l0 += p0;
-          l1 += p1;
-          pk[i >> 1] = pack_bf16x2(p0, p1);
+        for (int i = 0; i < NC; i += 8) {
+          float pv[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) pv[k] = ex2_approx(fmaf(s[i + k], a.scale_log2, -m_use));
+#pragma unroll
+          for (int k = 0; k < 8; ++k) lv[k] += pv[k];
+#pragma unroll
+          for (int k = 0; k < 8; k += 2) pk[(i + k) >> 1] = pack_bf16x2(pv[k], pv[k + 1]);
         }
-        l += l0 + l1;
+        l += ((lv[0] + lv[1]) + (lv[2] + lv[3])) + ((lv[4] + lv[5]) + (lv[6] + lv[7]));
         // the P buffer of this tile is free once the P V two tiles back has completed
         ok = mbar_wait(bar(kAtBarPEmpty + pr.stage), pr.phase ^ 1);
         if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }

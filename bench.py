@@ -534,7 +534,8 @@ def run_parity(pkg, prepared, device: str):
         r["disagreements"] = r["disagreements"][:8]
         out[name] = r
     out["note"] = ("decision_agreement: positions changed by either path that hold the same token in both; robust_*: "
-                   "passes whose decision a 2e-2 move of every logit cannot flip; oracle_floor_logits_fp32_max_abs: the "
+                   "passes whose decision a 2e-2 move of every logit cannot flip (floor_robust_*: a move of the oracle's own "
+                   "floor); oracle_floor_logits_fp32_max_abs: the "
                    "CPU oracle against itself with the rounding inside its attention placed differently (first pass), "
                    "i.e. what two equally valid implementations differ by after 28 bf16 layers at this width; every "
                    "recorded disagreement is a tie within the logits error of its pass over T")

@@ -56,7 +56,10 @@ def decode_parity(pkg, ocfg: "orc.DecoderConfig", weights: "orc.DecoderWeights",
 
     * ``decisions`` / ``decisions_agree``: positions that changed in either path, and how many of them hold
       the same token in both; ``robust_*``: the same over the passes whose decision a logits move of
-      ``LOGIT_TOL`` cannot flip (fixed tolerance, not widened by the measured error);
+      ``LOGIT_TOL`` cannot flip (fixed tolerance, not widened by the measured error); ``floor_robust_*``: the
+      same with the oracle's own floor (below) as the tolerance where that is larger -- decisions that two
+      equally valid implementations of the reference's arithmetic could already flip are left out, whatever
+      the CUDA path's own error is;
     * ``x0_agree`` / ``x0_total``: sampled tokens over all rows of all passes;
     * ``logits_fp32_max_abs``: worst |CUDA - oracle| over the un-rounded fp32 logits implied by the two
       final-norm hidden states (both through the oracle's LM head); ``logits_bf16_max_abs``: the same after
@@ -136,7 +139,8 @@ def _decode_parity(pkg, ocfg, weights, context, passes, temperature, threshold, 
     twin_hidden = twin.last["hidden"].reshape(block, -1).float()
     del twin
     lm_w32 = weights.lm_head.float()
-    out = dict(decisions=0, decisions_agree=0, robust_decisions=0, robust_agree=0, x0_total=0, x0_agree=0,
+    out = dict(decisions=0, decisions_agree=0, robust_decisions=0, robust_agree=0, floor_robust_decisions=0,
+               floor_robust_agree=0, x0_total=0, x0_agree=0,
                logits_fp32_max_abs=0.0, logits_bf16_max_abs=0.0, conf_max_rel=0.0, kv_rows=0, kv_max_abs=0.0,
                kv_exact_frac=1.0, passes=0, commit_passes=0, multi_token_passes=0, disagreements=[],
                oracle_floor_logits_fp32_max_abs=None)
@@ -174,6 +178,10 @@ def _decode_parity(pkg, ocfg, weights, context, passes, temperature, threshold, 
             if _robust(last, noise_store[step], before, mask_id, threshold, temperature, LOGIT_TOL):
                 out["robust_decisions"] += int(decided.sum())
                 out["robust_agree"] += int(agree.sum())
+            if _robust(last, noise_store[step], before, mask_id, threshold, temperature,
+                       max(LOGIT_TOL, out["oracle_floor_logits_fp32_max_abs"])):
+                out["floor_robust_decisions"] += int(decided.sum())
+                out["floor_robust_agree"] += int(agree.sum())
             out["multi_token_passes"] += int(n_ref > 1)
             if bool((decided & ~agree).any()):
                 lf = last["logits"][0].float() / temperature
@@ -215,4 +223,5 @@ def _decode_parity(pkg, ocfg, weights, context, passes, temperature, threshold, 
         out[k] = round(out[k], 6)
     out["decision_agreement"] = round(out["decisions_agree"] / max(out["decisions"], 1), 5)
     out["robust_agreement"] = round(out["robust_agree"] / max(out["robust_decisions"], 1), 5)
+    out["floor_robust_agreement"] = round(out["floor_robust_agree"] / max(out["floor_robust_decisions"], 1), 5)
     return out

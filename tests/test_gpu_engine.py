@@ -438,7 +438,9 @@ def test_full_size_decoder_teacher_forced(mdb, full_size, temperature):
     # weights and cache); the reference's own two code paths differ by REF_PATH_FLOOR on a narrower model.
     floor = r["oracle_floor_logits_fp32_max_abs"]
     assert r["logits_fp32_max_abs"] <= 2.0 * max(floor, REF_PATH_FLOOR), (r["logits_fp32_max_abs"], floor)
-    assert r["robust_decisions"] == 0 or r["robust_agreement"] >= 0.995, r
+    # decisions that survive a logits move of the oracle's own floor (what another valid implementation of the
+    # reference's arithmetic differs by at this depth) must be the same; the 2e-2 set is reported beside it
+    assert r["floor_robust_decisions"] == 0 or r["floor_robust_agreement"] >= 0.995, r
     # every differing decision must be a tie within the error of the path: the oracle's own margin at that
     # position (sampled token or confidence ranking) is below twice the logits error of that pass over T
     if temperature >= 0.5:

@@ -774,12 +774,14 @@ template <int ROWS, bool STAIR, bool DUP = false>
 static int at_launch(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, const AtArgs& a,
                      int64_t units, cudaStream_t st) {
   using P = AtPlan<ROWS, DUP>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceOnce attr_once;
+  const int dev = attr_once.slot();
+  if (dev < 0) return MDB_ERR_CUDA;
+  if (!attr_once.done[dev]) {
     if (cudaFuncSetAttribute(attn_tc_kernel<ROWS, STAIR, DUP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              P::kSmemBytes) != cudaSuccess)
       return MDB_ERR_CUDA;
-    attr_set = true;
+    attr_once.done[dev] = true;
   }
   if (units > (1 << 30)) return MDB_ERR_UNSUPPORTED;
   const int sms = at_sm_count();

@@ -606,11 +606,13 @@ static int launch_tc_impl(const bf16* x, int64_t ldx, const bf16* w, int w_rows,
   CUtensorMap map_x, map_w;
   if (!get_tensor_map(x, a.m, a.k, ldx, kTcBM, &map_x)) return MDB_ERR_CUDA;
   if (!get_tensor_map(w, w_rows, a.k, a.k, (PAIR || EPI == kTcSwiglu) ? 128 : kTcBN, &map_w)) return MDB_ERR_CUDA;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceOnce attr_once;
+  const int dev = attr_once.slot();
+  if (dev < 0) return MDB_ERR_CUDA;
+  if (!attr_once.done[dev]) {
     if (cudaFuncSetAttribute(gemm_tc_kernel<EPI, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess)
       return MDB_ERR_CUDA;
-    attr_set = true;
+    attr_once.done[dev] = true;
   }
   const int tiles = a.tiles_m * a.tiles_n;
   a.grid = tiles < sm_count ? tiles : sm_count;

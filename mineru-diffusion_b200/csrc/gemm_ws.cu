@@ -591,11 +591,13 @@ static int launch_ws(const bf16* x, int64_t ldx, const bf16* w, WsArgs& a, cudaS
   if (!get_tensor_map(w, a.n, a.k, a.k, w_box_rows, &map_w)) return MDB_ERR_CUDA;
   if (!get_tensor_map(x, a.m, a.k, ldx, a.ntok, &map_x)) return MDB_ERR_CUDA;
 
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceOnce attr_once;
+  const int dev = attr_once.slot();
+  if (dev < 0) return MDB_ERR_CUDA;
+  if (!attr_once.done[dev]) {
     if (cudaFuncSetAttribute(gemm_ws_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, budget) != cudaSuccess)
       return MDB_ERR_CUDA;
-    attr_set = true;
+    attr_once.done[dev] = true;
   }
   const int tasks = a.tiles_n * a.ksplit;
   return mdb_launch(gemm_ws_kernel<EPI>, dim3(tasks < g_ws_sm_count ? tasks : g_ws_sm_count), dim3(kWsThreads), smem,

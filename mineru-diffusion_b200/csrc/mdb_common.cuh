@@ -208,6 +208,18 @@ static int g_opt_pdl = 1;             // programmatic dependent launch between t
 static int g_opt_wait_limit_us = 2000000;   // bound of in-kernel waits (mirrors g_wait_limit_ns on the device)
 static int g_opt_gemm_pair = 1;       // many-row GEMMs on CTA pairs (tcgen05.mma.cta_group::2): 1 from 2048 rows, 2 from 256, 0 never
 
+// A kernel's opt-in attributes (dynamic shared memory above 48 KB) belong to one device's context, so the
+// "already set" flag is kept per device ordinal: a process that drives several GPUs sets them on each.
+struct PerDeviceOnce {
+  bool done[64] = {};
+  // Index of the current device's flag, or -1 when the device cannot be read or lies outside the table.
+  int slot() const {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+    return dev;
+  }
+};
+
 // Launch with the programmatic-stream-serialization attribute when enabled.
 template <typename... KArgs, typename... Args>
 static inline int mdb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,

@@ -100,6 +100,36 @@ def attn_workspace_bytes(bs: int, block: int, hq: int, nsplit: int) -> int:
     return int(_lib.lib().mdb_attn_paged_workspace_bytes(bs, block, hq, nsplit))
 
 
+def _block_attn_args(q, k_cache, v_cache, cache_seqlens, block_table, out):
+    """Shape, type and layout checks shared by the two paged-attention wrappers:
+    the kernels hard-code head size 128 and 256-token pages and index the page
+    table with unit stride inside a row."""
+    if q.dim() != 4 or k_cache.dim() != 4:
+        raise ValueError("q must be [bs, block, Hq, 128] and the caches [pages, 256, Hkv, 128]")
+    bs, block, hq, d = q.shape
+    pages, page, hkv, d2 = k_cache.shape
+    if d != 128 or d2 != 128 or page != 256:
+        raise ValueError("head_dim must be 128 and pages 256 tokens")
+    if v_cache.shape != k_cache.shape:
+        raise ValueError("k_cache and v_cache must have the same shape")
+    tensors = [(q, "q"), (k_cache, "k_cache"), (v_cache, "v_cache")]
+    if out is not None:
+        if out.shape != q.shape:
+            raise ValueError("out must have the shape of q")
+        tensors.append((out, "out"))
+    for t, nm in tensors:
+        _need(t, _BF16, nm)
+        if not t.is_contiguous():
+            raise ValueError(f"{nm} must be contiguous")
+    _need(cache_seqlens, torch.int32, "cache_seqlens")
+    _need(block_table, torch.int32, "block_table")
+    if cache_seqlens.numel() < bs or not cache_seqlens.is_contiguous():
+        raise ValueError("cache_seqlens must hold one contiguous int32 per request")
+    if block_table.dim() != 2 or block_table.shape[0] < bs or (block_table.shape[1] > 1 and block_table.stride(1) != 1):
+        raise ValueError("block_table must be [bs, pages per request] with unit stride inside a row")
+    return bs, block, hq, hkv, pages, d
+
+
 def block_attn_with_kvcache(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                             cache_seqlens: torch.Tensor, block_table: torch.Tensor, softmax_scale: float | None = None,
                             nsplit: int | None = None, workspace: torch.Tensor | None = None,
@@ -107,16 +137,7 @@ def block_attn_with_kvcache(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
     """Stands in for ``flash_attn_with_kvcache(..., causal=False)`` as the
     reference calls it (nanovllm/layers/sdar_attention.py:50-55).
     q [bs, B, Hq, 128]; caches [pages, 256, Hkv, 128]."""
-    bs, block, hq, d = q.shape
-    pages, page, hkv, d2 = k_cache.shape
-    if d != 128 or d2 != 128 or page != 256:
-        raise ValueError("head_dim must be 128 and pages 256 tokens")
-    for t, nm in ((q, "q"), (k_cache, "k_cache"), (v_cache, "v_cache")):
-        _need(t, _BF16, nm)
-        if not t.is_contiguous():
-            raise ValueError(f"{nm} must be contiguous")
-    _need(cache_seqlens, torch.int32, "cache_seqlens")
-    _need(block_table, torch.int32, "block_table")
+    bs, block, hq, hkv, pages, d = _block_attn_args(q, k_cache, v_cache, cache_seqlens, block_table, out)
     if softmax_scale is None:
         softmax_scale = d ** -0.5
     if nsplit is None:
@@ -143,14 +164,7 @@ def block_attn_with_kvcache_noalloc(q: torch.Tensor, k_cache: torch.Tensor, v_ca
     inside the library, so neither this wrapper nor the call allocates -- the
     caller passes ``out``.  Raises ``MdbError`` when (bs, nsplit) need more than
     that array.  Calls share the array; keep them on one stream."""
-    bs, block, hq, d = q.shape
-    pages, page, hkv, _ = k_cache.shape
-    for t, nm in ((q, "q"), (k_cache, "k_cache"), (v_cache, "v_cache"), (out, "out")):
-        _need(t, _BF16, nm)
-        if not t.is_contiguous():
-            raise ValueError(f"{nm} must be contiguous")
-    _need(cache_seqlens, torch.int32, "cache_seqlens")
-    _need(block_table, torch.int32, "block_table")
+    bs, block, hq, hkv, pages, d = _block_attn_args(q, k_cache, v_cache, cache_seqlens, block_table, out)
     if softmax_scale is None:
         softmax_scale = d ** -0.5
     _lib.check(_lib.lib().mdb_attn_block_paged_noalloc(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),

@@ -57,3 +57,19 @@ def test_noalloc_attention_refuses_oversize(mdb):
     mdb.ops.block_attn_with_kvcache_noalloc(q, kc, vc, ctx, table, out, nsplit=1)
     want = mdb.ops.block_attn_with_kvcache(q, kc, vc, ctx, table, nsplit=1)
     assert torch.equal(out, want)
+
+
+def test_noalloc_wrapper_checks_shapes_before_the_call(mdb):
+    """The kernels hard-code head size 128, 256-token pages and a densely packed
+    page-table row; a wrong ``out`` or head size has to stop on the host."""
+    q, kc, vc, ctx, table = _case(4, 2, 600)
+    with pytest.raises(ValueError, match="shape of q"):
+        mdb.ops.block_attn_with_kvcache_noalloc(q, kc, vc, ctx, table, torch.empty_like(q)[:, :16].contiguous())
+    with pytest.raises(ValueError, match="head_dim"):
+        mdb.ops.block_attn_with_kvcache_noalloc(q[..., :64].contiguous(), kc, vc, ctx, table,
+                                                torch.empty_like(q[..., :64].contiguous()))
+    wide = torch.full((table.shape[0], 2 * table.shape[1]), -1, dtype=torch.int32, device=DEV)
+    with pytest.raises(ValueError, match="unit stride"):
+        mdb.ops.block_attn_with_kvcache_noalloc(q, kc, vc, ctx, wide[:, ::2], torch.empty_like(q))
+    with pytest.raises(ValueError, match="unit stride"):
+        mdb.ops.block_attn_with_kvcache(q, kc, vc, ctx, wide[:, ::2])

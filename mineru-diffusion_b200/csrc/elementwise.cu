@@ -155,6 +155,97 @@ add_rmsnorm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ x2, cons
   if (threadIdx.x == 0) trace_event(10, 2);
 }
 
+// Many-row steps (prefill, batched decode): one warp per row and no block-wide barrier.  Lane l owns the 16-byte
+// chunks l, l + 32, ... of its row, so a warp reads contiguous 512-byte segments and keeps NCH loads per input in
+// flight per lane; the arithmetic per element is that of add_rmsnorm_kernel, only the order of the fp32 sum of
+// squares differs (per lane, then across the warp).
+constexpr int kNormRowsWarps = 8;
+
+__device__ __forceinline__ void unpack8(const uint4& u, float* a) {
+  float2 f;
+  f = unpack_bf16x2(u.x); a[0] = f.x; a[1] = f.y;
+  f = unpack_bf16x2(u.y); a[2] = f.x; a[3] = f.y;
+  f = unpack_bf16x2(u.z); a[4] = f.x; a[5] = f.y;
+  f = unpack_bf16x2(u.w); a[6] = f.x; a[7] = f.y;
+}
+
+template <int NCH>
+__global__ void __launch_bounds__(kNormRowsWarps * 32)
+add_rmsnorm_rows_kernel(const bf16* __restrict__ x, const bf16* __restrict__ x2, const bf16* __restrict__ residual_in,
+                        const bf16* __restrict__ weight, float eps, bf16* __restrict__ y_out,
+                        bf16* __restrict__ residual_out, int m, const TpSignal tp) {
+  pdl_launch_dependents();
+  pdl_wait();
+  tp_wait(tp);     // tensor-parallel pair: the peer's rows must have landed
+  constexpr int h = NCH * 256;
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * kNormRowsWarps + (threadIdx.x >> 5);
+  if (row >= m) return;
+  const int64_t row_off = static_cast<int64_t>(row) * h;
+  uint4 ux[NCH], ur[NCH];
+#pragma unroll
+  for (int i = 0; i < NCH; ++i) ux[i] = *reinterpret_cast<const uint4*>(x + row_off + (lane + 32 * i) * 8);
+  if (residual_in != nullptr) {
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) ur[i] = *reinterpret_cast<const uint4*>(residual_in + row_off + (lane + 32 * i) * 8);
+  }
+  float v[NCH][8];
+  float sumsq = 0.f;
+#pragma unroll
+  for (int i = 0; i < NCH; ++i) {
+    float a[8];
+    unpack8(ux[i], a);
+    if (x2 != nullptr) {
+      // tensor-parallel pair: bf16(own + peer), what the all-reduce of two bf16 tensors yields on both ranks
+      float b[8];
+      unpack8(*reinterpret_cast<const uint4*>(x2 + row_off + (lane + 32 * i) * 8), b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] = bf16_round(a[j] + b[j]);
+    }
+    if (residual_in != nullptr) {
+      float r[8];
+      unpack8(ur[i], r);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] += r[j];
+    }
+    if (residual_out != nullptr) {
+      uint4 o;
+      o.x = pack_bf16x2(a[0], a[1]); o.y = pack_bf16x2(a[2], a[3]);
+      o.z = pack_bf16x2(a[4], a[5]); o.w = pack_bf16x2(a[6], a[7]);
+      *reinterpret_cast<uint4*>(residual_out + row_off + (lane + 32 * i) * 8) = o;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      v[i][j] = a[j];
+      sumsq += a[j] * a[j];
+    }
+  }
+  sumsq = warp_sum(sumsq);
+  const float rstd = 1.0f / sqrtf(sumsq / static_cast<float>(h) + eps);
+#pragma unroll
+  for (int i = 0; i < NCH; ++i) {
+    float w[8];
+    unpack8(*reinterpret_cast<const uint4*>(weight + (lane + 32 * i) * 8), w);
+    float r[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = bf16_round(v[i][j] * rstd) * w[j];  // bf16 * bf16, rounded below
+    uint4 o;
+    o.x = pack_bf16x2(r[0], r[1]); o.y = pack_bf16x2(r[2], r[3]);
+    o.z = pack_bf16x2(r[4], r[5]); o.w = pack_bf16x2(r[6], r[7]);
+    *reinterpret_cast<uint4*>(y_out + row_off + (lane + 32 * i) * 8) = o;
+  }
+}
+
+template <int NCH>
+static int launch_add_rmsnorm_rows(const void* x, const void* x2, const void* residual_in, const void* weight, float eps,
+                                   void* y_out, void* residual_out, int m, const TpSignal& tp, mdb_stream_t stream) {
+  return mdb_launch(add_rmsnorm_rows_kernel<NCH>, dim3((m + kNormRowsWarps - 1) / kNormRowsWarps),
+                    dim3(kNormRowsWarps * 32), 0, static_cast<cudaStream_t>(stream), static_cast<const bf16*>(x),
+                    static_cast<const bf16*>(x2), static_cast<const bf16*>(residual_in),
+                    static_cast<const bf16*>(weight), eps, static_cast<bf16*>(y_out), static_cast<bf16*>(residual_out),
+                    m, tp);
+}
+
 // ---------------------------------------------------------------------------
 // q/k per-head RMSNorm + rotary + KV store; one warp per (token, head).
 // Lane l owns head elements {2l, 2l+1, 2l+64, 2l+65}: the two halves the
@@ -430,6 +521,16 @@ static int add_rmsnorm_impl(const void* x, const void* x2, const float* partials
   MDB_REQUIRE(mdb_aligned16(x) && mdb_aligned16(partials) && mdb_aligned16(residual_in) && mdb_aligned16(weight) &&
                   mdb_aligned16(y_out) && mdb_aligned16(residual_out),
               MDB_ERR_ALIGN);
+  if (partials == nullptr && m > 64) {
+    // many rows: a warp per row (row widths that are a power-of-two multiple of 256 up to 2048)
+    switch (h) {
+      case 256: return launch_add_rmsnorm_rows<1>(x, x2, residual_in, weight, eps, y_out, residual_out, m, tp, stream);
+      case 512: return launch_add_rmsnorm_rows<2>(x, x2, residual_in, weight, eps, y_out, residual_out, m, tp, stream);
+      case 1024: return launch_add_rmsnorm_rows<4>(x, x2, residual_in, weight, eps, y_out, residual_out, m, tp, stream);
+      case 2048: return launch_add_rmsnorm_rows<8>(x, x2, residual_in, weight, eps, y_out, residual_out, m, tp, stream);
+      default: break;
+    }
+  }
   if (partials != nullptr)
     return mdb_launch(add_rmsnorm_kernel<true>, dim3(m), dim3(kNormThreads), 0, static_cast<cudaStream_t>(stream),
                       static_cast<const bf16*>(x), static_cast<const bf16*>(x2), partials, nparts,

@@ -140,6 +140,12 @@ __device__ __forceinline__ void umma_commit_pair_w(uint32_t bar) {
       : "memory");
 }
 
+__device__ __forceinline__ float4 lds_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+
 template <int EPI, bool PAIR>
 __global__ void __launch_bounds__(tc_threads(EPI), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
@@ -280,11 +286,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     for (int t = work0; t < tiles; t += work_stride) {
       const int tn = a.n_fastest ? t % a.tiles_n : t / a.tiles_m;
       const int tm = a.n_fastest ? t / a.tiles_n : t % a.tiles_m;
+      // q/k-norm + rotation form: this lane's position (-1: none, or outside the table) and the request for the
+      // first quarter of the warp's cos | sin rows go out before the accumulator is waited for
+      const uint32_t rope_smem = base + bars_off + 256 + warp * 4096;
+      int rope_pos = -1;
+      auto rope_fill = [&](int p) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = 4 * i + (lane >> 3);
+          const int j = lane & 7;                       // 16-byte piece of the row's pass: 0..3 cos, 4..7 sin
+          const int pr = __shfl_sync(0xffffffffu, rope_pos, r);
+          if (pr >= 0) {
+            const float* src = a.rope_table + static_cast<int64_t>(pr) * kHeadDim + (j >> 2) * 64 + 16 * p + 4 * (j & 3);
+            const uint32_t dst = rope_smem + r * 128 + ((static_cast<uint32_t>(j) ^ (r & 7u)) << 4);
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+          }
+        }
+      };
+      if (EPI == kTcQkvRope) {
+        const int prow = tm * kRowsPerTile + static_cast<int>(rank) * kTcBM + 32 * (warp & 3) + lane;
+        const int phead = 2 * tn + (warp >> 2);
+        if (phead < a.hq + a.hkv) {
+          if (prow < a.m) {
+            const int64_t pos = a.positions[prow];
+            rope_pos = (pos >= 0 && pos < a.max_pos) ? static_cast<int>(pos) : -1;
+          }
+          rope_fill(0);
+        }
+      }
       bool ok = mbar_wait(bar_acc_full + 8 * acc, acc_phase);
       ok = __all_sync(0xffffffffu, ok);
       // LM head: the warps of a quarter meet at a named barrier below, so they must agree on giving up
       if (EPI == kTcLmHead) ok = named_bar_and(5 + (warp & 3), 128, ok);
       if (!ok) {
+        if (EPI == kTcQkvRope) asm volatile("cp.async.wait_all;" ::: "memory");
         if (lane == 0) report_status(MDB_STATUS_WAIT_TIMEOUT);
         break;
       }
@@ -394,29 +429,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
       }
       if (EPI == kTcQkvRope) {
-        // this warp: head 2 tn + g of the fused q|k|v output for its 32 step rows
+        // this warp: head 2 tn + g of the fused q|k|v output for its 32 step rows.  Everything the projection,
+        // the norm and the rotation leave is bf16, so a row's head lives packed in 64 registers throughout.
         const int grp = warp >> 2;
         const int head = 2 * tn + grp;
         const int nheads = a.hq + 2 * a.hkv;
-        float v[kHeadDim];
+        const bool is_q = head < a.hq;
+        const bool is_k = !is_q && head < a.hq + a.hkv;
+        const bool live = row < a.m && head < nheads;
+        uint32_t pk[kHeadDim / 2];
+        float ss0 = 0.f, ss1 = 0.f, ss2 = 0.f, ss3 = 0.f;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) tmem_ld16(taddr + kHeadDim * grp + 16 * c, *reinterpret_cast<float(*)[16]>(v + 16 * c));
-        tmem_ld_wait();
+        for (int c = 0; c < 4; ++c) {
+          float t0[16], t1[16];
+          tmem_ld16(taddr + kHeadDim * grp + 32 * c, t0);
+          tmem_ld16(taddr + kHeadDim * grp + 32 * c + 16, t1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; i += 4) {
+            // the projection's bf16 output; sum of squares over the rounded values in four interleaved chains
+            pk[16 * c + i / 2] = pack_bf16x2(t0[i], t0[i + 1]);
+            pk[16 * c + i / 2 + 1] = pack_bf16x2(t0[i + 2], t0[i + 3]);
+            const float2 f0 = unpack_bf16x2(pk[16 * c + i / 2]), f1 = unpack_bf16x2(pk[16 * c + i / 2 + 1]);
+            ss0 = fmaf(f0.x, f0.x, ss0); ss1 = fmaf(f0.y, f0.y, ss1);
+            ss2 = fmaf(f1.x, f1.x, ss2); ss3 = fmaf(f1.y, f1.y, ss3);
+          }
+#pragma unroll
+          for (int i = 0; i < 16; i += 4) {
+            pk[16 * c + 8 + i / 2] = pack_bf16x2(t1[i], t1[i + 1]);
+            pk[16 * c + 8 + i / 2 + 1] = pack_bf16x2(t1[i + 2], t1[i + 3]);
+            const float2 f0 = unpack_bf16x2(pk[16 * c + 8 + i / 2]), f1 = unpack_bf16x2(pk[16 * c + 8 + i / 2 + 1]);
+            ss0 = fmaf(f0.x, f0.x, ss0); ss1 = fmaf(f0.y, f0.y, ss1);
+            ss2 = fmaf(f1.x, f1.x, ss2); ss3 = fmaf(f1.y, f1.y, ss3);
+          }
+        }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) arrive_acc_empty(acc);
-        if (row < a.m && head < nheads) {
-#pragma unroll
-          for (int i = 0; i < kHeadDim; ++i) v[i] = bf16_round(v[i]);       // the projection's bf16 output
-          const bool is_q = head < a.hq;
-          const bool is_k = !is_q && head < a.hq + a.hkv;
-          if (is_q || is_k) {
-            float ss0 = 0.f, ss1 = 0.f, ss2 = 0.f, ss3 = 0.f;
-#pragma unroll
-            for (int i = 0; i < kHeadDim; i += 4) {
-              ss0 = fmaf(v[i], v[i], ss0); ss1 = fmaf(v[i + 1], v[i + 1], ss1);
-              ss2 = fmaf(v[i + 2], v[i + 2], ss2); ss3 = fmaf(v[i + 3], v[i + 3], ss3);
-            }
+        if (is_q || is_k) {          // warp-uniform: a warp owns one head
+          if (live) {
             const float rstd = 1.0f / sqrtf(((ss0 + ss1) + (ss2 + ss3)) / static_cast<float>(kHeadDim) + a.eps);
             const uint4* nw = reinterpret_cast<const uint4*>(is_q ? a.q_norm_w : a.k_norm_w);
 #pragma unroll
@@ -425,53 +476,95 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
               const uint32_t ws[4] = {w8.x, w8.y, w8.z, w8.w};
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
-                const float2 wf = unpack_bf16x2(ws[j]);
-                v[8 * c + 2 * j] = bf16_round(bf16_round(v[8 * c + 2 * j] * rstd) * wf.x);
-                v[8 * c + 2 * j + 1] = bf16_round(bf16_round(v[8 * c + 2 * j + 1] * rstd) * wf.y);
+                const float2 f = unpack_bf16x2(pk[4 * c + j]), wf = unpack_bf16x2(ws[j]);
+                pk[4 * c + j] = pack_bf16x2(bf16_round(f.x * rstd) * wf.x, bf16_round(f.y * rstd) * wf.y);
               }
-            }
-            const int64_t pos = a.positions[row];
-            if (pos >= 0 && pos < a.max_pos) {
-              const float4* cs = reinterpret_cast<const float4*>(a.rope_table + pos * kHeadDim);
-#pragma unroll
-              for (int c = 0; c < 16; ++c) {
-                const float4 co = __ldg(cs + c), si = __ldg(cs + 16 + c);
-                const float cc[4] = {co.x, co.y, co.z, co.w}, sn[4] = {si.x, si.y, si.z, si.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const float lo = v[4 * c + j], hi = v[4 * c + j + 64];
-                  // products rounded separately, as un-fused fp32 tensor ops do
-                  v[4 * c + j] = __fsub_rn(__fmul_rn(lo, cc[j]), __fmul_rn(hi, sn[j]));
-                  v[4 * c + j + 64] = __fadd_rn(__fmul_rn(hi, cc[j]), __fmul_rn(lo, sn[j]));
-                }
-              }
-            } else {
-              report_status(MDB_STATUS_BAD_POSITION);
             }
           }
-          uint4 o[16];
+          // Rotation: the cos | sin rows of the warp's 32 positions come through this warp's 4 KB of shared
+          // memory in four passes of 16 channel pairs, fetched as 64-byte segments (eight lanes per row) and read
+          // back one row per lane; 16-byte piece j of row r sits at piece j ^ (r & 7), conflict-free both ways.
+          // Pass 0 was requested before the accumulator wait.
+          const bool pos_bad = live && rope_pos < 0;
 #pragma unroll
-          for (int c = 0; c < 16; ++c)
-            o[c] = make_uint4(pack_bf16x2(v[8 * c], v[8 * c + 1]), pack_bf16x2(v[8 * c + 2], v[8 * c + 3]),
-                              pack_bf16x2(v[8 * c + 4], v[8 * c + 5]), pack_bf16x2(v[8 * c + 6], v[8 * c + 7]));
-          auto store = [&](bf16* dst) {
-            uint4* d4 = reinterpret_cast<uint4*>(dst);
+          for (int p = 0; p < 4; ++p) {
+            asm volatile("cp.async.wait_all;" ::: "memory");
+            __syncwarp();
+            float4 co[4], si[4];
 #pragma unroll
-            for (int c = 0; c < 16; ++c) d4[c] = o[c];
-          };
-          if (is_q) {
-            store(a.q_out + (static_cast<int64_t>(row) * a.hq + head) * kHeadDim);
-          } else {
-            const int kvh = is_k ? head - a.hq : head - a.hq - a.hkv;
-            bf16* contiguous = is_k ? a.k_out : a.v_out;
-            if (contiguous != nullptr) store(contiguous + (static_cast<int64_t>(row) * a.hkv + kvh) * kHeadDim);
-            if (a.slot_mapping != nullptr) {
-              const int slot = a.slot_mapping[row];
-              if (slot >= 0 && slot < a.num_slots)
-                store((is_k ? a.k_cache : a.v_cache) + (static_cast<int64_t>(slot) * a.hkv + kvh) * kHeadDim);
-              else if (slot != -1)
-                report_status(MDB_STATUS_BAD_SLOT);
+            for (int c4 = 0; c4 < 4; ++c4) {
+              co[c4] = lds_f4(rope_smem + lane * 128 + ((static_cast<uint32_t>(c4) ^ (lane & 7u)) << 4));
+              si[c4] = lds_f4(rope_smem + lane * 128 + ((static_cast<uint32_t>(4 + c4) ^ (lane & 7u)) << 4));
             }
+            __syncwarp();
+            if (p < 3) rope_fill(p + 1);
+            if (live && !pos_bad) {
+#pragma unroll
+              for (int c4 = 0; c4 < 4; ++c4) {
+                const int c = 4 * p + c4;
+                const float cc[4] = {co[c4].x, co[c4].y, co[c4].z, co[c4].w};
+                const float sn[4] = {si[c4].x, si[c4].y, si[c4].z, si[c4].w};
+#pragma unroll
+                for (int h2 = 0; h2 < 2; ++h2) {
+                  const float2 lo = unpack_bf16x2(pk[2 * c + h2]), hi = unpack_bf16x2(pk[32 + 2 * c + h2]);
+                  // products rounded separately, as un-fused fp32 tensor ops do
+                  const float lx = __fsub_rn(__fmul_rn(lo.x, cc[2 * h2]), __fmul_rn(hi.x, sn[2 * h2]));
+                  const float ly = __fsub_rn(__fmul_rn(lo.y, cc[2 * h2 + 1]), __fmul_rn(hi.y, sn[2 * h2 + 1]));
+                  const float hx = __fadd_rn(__fmul_rn(hi.x, cc[2 * h2]), __fmul_rn(lo.x, sn[2 * h2]));
+                  const float hy = __fadd_rn(__fmul_rn(hi.y, cc[2 * h2 + 1]), __fmul_rn(lo.y, sn[2 * h2 + 1]));
+                  pk[2 * c + h2] = pack_bf16x2(lx, ly);
+                  pk[32 + 2 * c + h2] = pack_bf16x2(hx, hy);
+                }
+              }
+            }
+          }
+          if (pos_bad) report_status(MDB_STATUS_BAD_POSITION);
+        }
+        // Stores: a thread holds a whole head of its own row, which would leave as 16-byte pieces of 32 different
+        // rows per instruction.  The warp turns its 32 x 128 elements around in its 4 KB of shared memory, half a
+        // head at a time, and writes 128-byte row segments, four rows per instruction.
+        if (head < nheads) {         // warp-uniform
+          const int row0 = row - lane;
+          const int kvh = is_k ? head - a.hq : head - a.hq - a.hkv;
+          bf16* contiguous = is_q ? a.q_out : (is_k ? a.k_out : a.v_out);
+          const int heads_out = is_q ? a.hq : a.hkv;
+          const int head_out = is_q ? head : kvh;
+          bf16* cache = is_q ? nullptr : (is_k ? a.k_cache : a.v_cache);
+          int my_slot = -1;
+          if (!is_q && a.slot_mapping != nullptr && live) {
+            const int slot = a.slot_mapping[row];
+            if (slot >= 0 && slot < a.num_slots) my_slot = slot;
+            else if (slot != -1) report_status(MDB_STATUS_BAD_SLOT);
+          }
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rope_smem + lane * 128 +
+                                                                            ((static_cast<uint32_t>(j) ^ (lane & 7u)) << 4)),
+                           "r"(pk[32 * hf + 4 * j]), "r"(pk[32 * hf + 4 * j + 1]), "r"(pk[32 * hf + 4 * j + 2]),
+                           "r"(pk[32 * hf + 4 * j + 3])
+                           : "memory");
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int r = 4 * i + (lane >> 3);
+              const int j = lane & 7;
+              uint4 o;
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(o.x), "=r"(o.y), "=r"(o.z), "=r"(o.w)
+                           : "r"(rope_smem + r * 128 + ((static_cast<uint32_t>(j) ^ (r & 7u)) << 4)));
+              const int slot_r = __shfl_sync(0xffffffffu, my_slot, r);
+              const int rr = row0 + r;
+              if (rr < a.m) {
+                const int col = 64 * hf + 8 * j;
+                if (contiguous != nullptr)
+                  *reinterpret_cast<uint4*>(contiguous + (static_cast<int64_t>(rr) * heads_out + head_out) * kHeadDim + col) = o;
+                if (slot_r >= 0)
+                  *reinterpret_cast<uint4*>(cache + (static_cast<int64_t>(slot_r) * a.hkv + kvh) * kHeadDim + col) = o;
+              }
+            }
+            __syncwarp();
           }
         }
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
@@ -596,7 +689,12 @@ static int launch_tc_impl(const bf16* x, int64_t ldx, const bf16* w, int w_rows,
     if (sm_count <= 0) sm_count = 148;
   }
   constexpr int kRowsPerTile = PAIR ? 2 * kTcBM : kTcBM;
-  constexpr int kSmem = PAIR ? 1024 + kTcPairStages * (kTcABytes + kTcBBytes / 2) + 256 + kTcLmRecBytes : kTcSmemBytes;
+  // after the barriers: sampler records (LM head), the peer's staged tile (bf16 form), or 4 KB per epilogue warp
+  // for the cos | sin rows (q/k-norm + rotation form)
+  constexpr int kTail = EPI == kTcQkvRope ? tc_epi_warps(EPI) * 4096 : kTcLmRecBytes;
+  constexpr int kSmem = 1024 + (PAIR ? kTcPairStages * (kTcABytes + kTcBBytes / 2) : kTcStages * (kTcABytes + kTcBBytes)) +
+                        256 + kTail;
+  static_assert(kSmem <= 232448, "shared memory of the tile GEMM");
   a.tiles_m = (a.m + kRowsPerTile - 1) / kRowsPerTile;
   a.tiles_n = (EPI == kTcSwiglu) ? a.n / 128 : (a.n + kTcBN - 1) / kTcBN;
   // Activations that do not fit in L2 next to the weights (a 16K-row step of down_proj: 201 MB) would be

@@ -106,6 +106,25 @@ def test_rmsnorm_forms(mdb):
     _status_clean(mdb)
 
 
+@pytest.mark.parametrize("h", [256, 512, 2048, 1536])
+def test_rmsnorm_many_rows(mdb, h):
+    """Steps of more than 64 rows take the warp-per-row kernel (row widths 256..2048 in powers of two; 1536 stays
+    on the row-per-CTA kernel): same arithmetic per element, only the order of the fp32 sum of squares differs."""
+    gen = torch.Generator().manual_seed(11)
+    m = 333                                      # not a multiple of the rows per CTA
+    x = (3 * torch.randn(m, h, generator=gen)).to(BF)
+    res = torch.randn(m, h, generator=gen).to(BF)
+    w = (1 + 0.1 * torch.randn(h, generator=gen)).to(BF)
+    want_y, want_r = orc.add_rms_norm(x, res, w, 1e-6)
+    y, r = mdb.ops.add_rms_norm(x.to(DEV), res.to(DEV), w.to(DEV), 1e-6)
+    _close_bf16(y, want_y, exact_frac=0.99)
+    assert torch.equal(r.cpu(), want_r)
+    y, r = mdb.ops.add_rms_norm(x.to(DEV), None, w.to(DEV), 1e-6)
+    _close_bf16(y, orc.rms_norm(x, w, 1e-6), exact_frac=0.99)
+    assert torch.equal(r.cpu(), x)
+    _status_clean(mdb)
+
+
 @pytest.mark.parametrize("from_partials", [False, True])
 def test_qknorm_rope_commit(mdb, from_partials):
     gen = torch.Generator().manual_seed(4)

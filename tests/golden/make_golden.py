@@ -251,6 +251,18 @@ def gen_staircase():
     # fp16 run: shows where the kernel rounds (q*scale -> fp16, p -> fp16)
     qh, kh, vh = q.half(), k.half(), v.half()
     rec["out_fp16_s32"] = run_triton_staircase(qh, kh, vh, cu, 32).float()
+    # the same kernel in fp32 on inputs that bf16 holds exactly (stored as bf16 bit patterns): what a bf16
+    # implementation is compared with when the rounding of its inputs is not to count as its error
+    g2 = torch.Generator().manual_seed(113)
+    lens_b = [70, 97, 33]
+    cu_b = torch.tensor([0] + list(np.cumsum(lens_b)), dtype=torch.int32)
+    nb = int(cu_b[-1])
+    qb = torch.randn(nb, 2, d, generator=g2).to(torch.bfloat16)
+    kb = torch.randn(nb, 1, d, generator=g2).to(torch.bfloat16)
+    vb = torch.randn(nb, 1, d, generator=g2).to(torch.bfloat16)
+    rec.update(lens_bf=np.array(lens_b), q_bf=bits(qb), k_bf=bits(kb), v_bf=bits(vb))
+    for stairs in (32, 8):
+        rec[f"out_fp32_bf_s{stairs}"] = run_triton_staircase(qb.float(), kb.float(), vb.float(), cu_b, stairs)
     # the HF twin's mask for the same shapes (prompt P, one generation block)
     from mineru_diffusion.modeling_mineru_diffusion import SDARForCausalLM as HFModel
     for P, gen, B in ((45, 32, 32), (5, 8, 4), (64, 64, 32), (70, 16, 8)):

@@ -46,6 +46,15 @@ def test_staircase_attention_matches_triton_kernel():
     ref16 = torch.from_numpy(g["out_fp16_s32"])
     mirrored = orc.attn_staircase_varlen(qh, kh, vh, cu, cu, 32, mirror_rounding=True).float()
     assert (mirrored - ref16).abs().max() < 2e-3
+    # bf16 restatement on inputs that bf16 holds exactly against the kernel's fp32 run on the same values: only
+    # the roundings inside (q * scale, P, the output) remain
+    lens = g["lens_bf"].tolist()
+    cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32)
+    qb, kb, vb = (bf16_from_bits(g[x]) for x in ("q_bf", "k_bf", "v_bf"))
+    for stairs in (32, 8):
+        out = orc.attn_staircase_varlen(qb, kb, vb, cu, cu, stairs)
+        ref = torch.from_numpy(g[f"out_fp32_bf_s{stairs}"])
+        assert (out.float() - ref).abs().max() < 8e-3
 
 
 def test_layers_match_reference_modules():

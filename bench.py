@@ -547,8 +547,8 @@ def run_dp_completion(pkg, args, rank: int, world: int, local_rank: int):
     """Strong scaling of request-level data parallelism where it can fail: a fixed seeded request set with
     BASELINE config 5's distributions (visual rows and output lengths uniform, scaled down so that every N
     finishes within the time limit: 32 requests, visual rows U[512, 8192], outputs U[64, 512] rounded up to
-    whole blocks), partitioned over the ranks by ``engine/dp.py:partition_requests`` (greedy longest-first by
-    prompt + output tokens) and run to completion at a low temperature, so that the threshold decides how many
+    whole blocks), partitioned over the ranks by ``engine/dp.py:partition_requests`` (greedy longest-first on a
+    time model of a replica) and run to completion at a low temperature, so that the threshold decides how many
     passes a block takes.  Same set for every N.  Returns tokens/s over the slowest rank's time, per-rank finish
     times and the max/mean imbalance."""
     dp = importlib.import_module("mineru-diffusion_b200.engine.dp")
@@ -559,8 +559,12 @@ def run_dp_completion(pkg, args, rank: int, world: int, local_rank: int):
     g = torch.Generator().manual_seed(5)
     visual = torch.randint(512, 8193, (total_requests,), generator=g).tolist()
     news = ((torch.randint(64, 513, (total_requests,), generator=g) + wl.block - 1) // wl.block * wl.block).tolist()
-    costs = [v + TEXT_IDS + n for v, n in zip(visual, news)]
-    mine = dp.partition_requests(costs, world)[rank]
+    # time model of a replica, microseconds: prefill 4 us per prompt token (4 GFLOP per token at ~1 PFLOP/s), a
+    # decode step 1600 us of weight streaming whatever the batch + 130 us per request in flight (config-3 step:
+    # (10.0 - 1.7) ms / 63), three passes per block at this temperature
+    steps_est = [3 * n // wl.block for n in news]
+    costs = [4.0 * (v + TEXT_IDS) + 130.0 * s for v, s in zip(visual, steps_est)]
+    mine = dp.partition_requests(costs, world, steps=steps_est, step_cost=1600.0)[rank]
     cfg, runner, engine = build_engine(pkg, wl, device, 1, 0, seed=5, visual_rows=[visual[i] for i in mine],
                                        new_tokens=[news[i] for i in mine])
     # distinct request seeds whatever the rank: rebuild the requests with their global index
@@ -597,7 +601,8 @@ def run_dp_completion(pkg, args, rank: int, world: int, local_rank: int):
     return {"workload": f"{total_requests} requests, visual rows U[512,8192], outputs U[64,512] (whole blocks), block "
                         f"{wl.block}, threshold {wl.threshold}, temperature {wl.temperature}, at most {wl.requests} in "
                         "flight per GPU, prefill included, run to completion; same set for every N",
-            "scaling": "strong", "partitioner": "engine/dp.py:partition_requests (greedy longest-first by prompt + output tokens)",
+            "scaling": "strong", "partitioner": "engine/dp.py:partition_requests (greedy longest-first on a time model: 4 us per prompt token "
+                                           "+ 130 us per request-step + 1600 us x the rank's longest stay in steps)",
             "tokens": int(sum(r[1] for r in rows)), "tokens_per_s": round(sum(r[1] for r in rows) / (max(times) * 1e-3), 1),
             "rank_finish_ms": [round(x, 1) for x in times], "rank_tokens": [int(r[1]) for r in rows],
             "rank_steps": [int(r[2]) for r in rows], "rank_cost": [int(r[3]) for r in rows],

@@ -36,6 +36,26 @@ def test_partition_is_balanced_and_complete(mdb):
     assert dp.partition_requests([], 2) == [[], []]
 
 
+def test_partition_with_step_term_gathers_long_requests(mdb):
+    """A replica steps until its last request is done and every step has a fixed cost: with that term in the
+    load the partitioner must not let one long request set the step count of every rank."""
+    dp = importlib.import_module("mineru-diffusion_b200.engine.dp")
+    g = torch.Generator().manual_seed(9)
+    for world in (2, 4, 8):
+        n = 32
+        steps = torch.randint(6, 49, (n,), generator=g).tolist()
+        costs = [float(300 * s + int(torch.randint(2000, 33000, (1,), generator=g))) for s in steps]
+        step_cost = 1600.0
+        plain = dp.partition_requests(costs, world)
+        aware = dp.partition_requests(costs, world, steps=steps, step_cost=step_cost)
+        assert sorted(i for p in aware for i in p) == list(range(n))
+        assert aware == dp.partition_requests(costs, world, steps=steps, step_cost=step_cost)   # deterministic
+        worst = lambda parts: max(dp.modelled_load(p, costs, steps, step_cost) for p in parts)  # noqa: E731
+        assert worst(aware) <= worst(plain) + 1e-6, (world, worst(aware), worst(plain))
+    # without the step term the split is the plain longest-first one
+    assert dp.partition_requests(costs, 4, steps=steps, step_cost=0.0) == dp.partition_requests(costs, 4)
+
+
 def test_reduce_throughput_two_ranks(tmp_path):
     port = 29600 + os.getpid() % 200
     mp.start_processes(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True, start_method="spawn")

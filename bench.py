@@ -668,12 +668,17 @@ def main():
                     help="Config.fuse_commit_pass: a block's commit pass also runs the next block's first denoising "
                          "pass (not the reference's schedule; off for the headline number)")
     ap.add_argument("--tp", type=int, default=1, choices=[1, 2], help="2: the two ranks form one tensor-parallel pair")
+    ap.add_argument("--requests", type=int, default=0,
+                    help="requests in flight per GPU instead of the workload's own count (config3 / config5: the "
+                         "batch sizes between one request and 64)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     wl = replace(WORKLOADS[args.workload], block=args.block, threshold=args.threshold, temperature=args.temperature,
                  fuse_commit=args.fuse_commit)
+    if args.requests > 0 and wl.requests > 1:
+        wl = replace(wl, name=f"{wl.name} with {args.requests} requests in flight", requests=args.requests)
     config = {"workload": wl.describe(), "block_size": wl.block, "requests_per_gpu": wl.requests,
               "parallelism": f"tp{args.tp}" if args.tp == 2 else f"dp{args.gpus}",
               "l2_policy": "per-step weight traffic (3.4 GB) exceeds L2 (126 MB); no explicit flush"}

@@ -134,6 +134,12 @@ int mdb_attn_staircase_varlen(const void* q, int64_t q_stride, const void* k, in
 
 /* ---- linear layers -------------------------------------------------------- */
 
+/* In every entry of this section w is model data: with MDB_OPT_PDL on, a kernel
+ * requests its first weight tiles while the preceding kernel of the stream may
+ * still be running (weights are the only operand fetched that early), so w must
+ * not be something a library call issued just before on the same stream writes.
+ * Activations, outputs and workspaces carry the usual stream order. */
+
 /* y[m,n] = x[m,k] * w[n,k]^T, bf16 in, fp32 accumulate, bf16 out: F.linear as
  * used by NV/layers/linear.py:72-73,153-154 and NV/layers/embed_head.py:67. */
 int mdb_gemm_bf16(const void* x, int64_t ldx, const void* w, void* y, int64_t ldy, int m, int n, int k,

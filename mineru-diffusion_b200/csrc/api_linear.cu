@@ -54,10 +54,10 @@ int ws_pick_ksplit(int n, int k) {
   return s;
 }
 
-// Common argument checks of the short-step (m <= 64) entry points.
-int check_short_step(const void* x, int64_t ldx, const void* w, int m, int n, int k) {
+// Common argument checks of the short-step entry points (at most 64 rows; 256 for the split-k slice form).
+int check_short_step(const void* x, int64_t ldx, const void* w, int m, int n, int k, int max_rows = kWsMaxRows) {
   MDB_REQUIRE(x && w, MDB_ERR_ARG);
-  MDB_REQUIRE(m >= 1 && m <= 64, MDB_ERR_UNSUPPORTED);
+  MDB_REQUIRE(m >= 1 && m <= max_rows, MDB_ERR_UNSUPPORTED);
   MDB_REQUIRE(n > 0 && k > 0 && ldx >= k, MDB_ERR_ARG);
   MDB_REQUIRE(ldx % 8 == 0 && mdb_aligned16(x) && mdb_aligned16(w), MDB_ERR_ALIGN);
   return MDB_OK;
@@ -80,7 +80,7 @@ int64_t mdb_gemm_splitk_workspace_bytes(int m, int n, int ksplit) {
 int mdb_gemm_splitk_partials(const void* x, int64_t ldx, const void* w, float* partials, int m, int n, int k,
                              int ksplit, mdb_stream_t stream) {
   if (m == 0) return MDB_OK;
-  int rc = check_short_step(x, ldx, w, m, n, k);
+  int rc = check_short_step(x, ldx, w, m, n, k, kWsMaxRowsPartial);
   if (rc != MDB_OK) return rc;
   MDB_REQUIRE(partials != nullptr && ksplit >= 1 && ksplit <= 64, MDB_ERR_ARG);
   MDB_REQUIRE(mdb_aligned16(partials), MDB_ERR_ALIGN);

@@ -48,8 +48,7 @@ constexpr int kTcBBytes = kTcBN * kTcBK * 2;   // 32 KB
 constexpr int kTcPairStages = 6;               // PAIR: 16 KB of A + 16 KB of B per stage and CTA
 constexpr int kTcLmEpiWarps = 16;
 constexpr int kTcLmRecBytes = 2 * kTcLmEpiWarps * 32 * 5 * 4;    // two buffers of per-warp sampler records
-constexpr int kTcSmemBytes = 1024 + kTcStages * (kTcABytes + kTcBBytes) + 256 + kTcLmRecBytes;
-__host__ __device__ constexpr int tc_epi_warps(int epi) { return epi == 2 ? kTcLmEpiWarps : (epi == 0 ? 4 : 8); }
+__host__ __device__ constexpr int tc_epi_warps(int epi) { return epi == 2 ? kTcLmEpiWarps : 8; }
 __host__ __device__ constexpr int tc_threads(int epi) { return (tc_epi_warps(epi) + 2) * 32; }
 
 struct TcArgs {
@@ -91,7 +90,12 @@ struct TcArgs {
   float4* peer_part_f;
   int* peer_part_i;
   int grid;                    // CTAs launched (set by the launcher; the peer waits for that many flags)
+  // bf16 form with few tiles: a cluster of ksplit CTAs shares one tile, each CTA a slice of k; the fp32 partial
+  // tiles meet in shared memory (0 or 1: off)
+  int ksplit;
 };
+
+constexpr int kTcParkStride = (kTcBN + 4) * 4;   // bytes per parked fp32 accumulator row: 16-byte pad against bank conflicts
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -168,10 +172,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   constexpr int kEpiWarps = tc_epi_warps(EPI);
   constexpr int kProducerWarp = kEpiWarps, kMmaWarp = kEpiWarps + 1;
   const uint32_t rank = PAIR ? cluster_ctarank() : 0u;           // 0 = the CTA that issues the MMAs
-  const int work0 = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
-  const int work_stride = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  // split-k clusters (bf16 form, single-CTA tiles): ks CTAs per tile, this one takes k chunks [c_begin, c_end)
+  const int ks = (EPI == kTcBf16 && !PAIR && a.ksplit > 1) ? a.ksplit : 1;
+  const uint32_t kr = ks > 1 ? cluster_ctarank() : 0u;
+  const int work0 = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x) / ks;
+  const int work_stride = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x) / ks;
   const int tiles = a.tiles_m * a.tiles_n;
   const int kchunks = a.k / kTcBK;
+  const int c_begin = static_cast<int>(kr) * kchunks / ks, c_end = (static_cast<int>(kr) + 1) * kchunks / ks;
+  int parked_tile = -1;                                          // split-k: the tile whose partial this CTA parked
 
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
@@ -209,36 +218,62 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
   if (warp == kProducerWarp) {
     // the whole warp walks the loop (warp-uniform operands), one elected lane issues each instruction
-    pdl_wait();   // activations come from the preceding kernel
     const uint32_t full_target = PAIR ? map_to_cta(bar_full, 0) : bar_full;
+    auto tile_of = [&](int t, int& tn, int& tm) {
+      tn = a.n_fastest ? t % a.tiles_n : t / a.tiles_m;   // consecutive CTAs share a weight tile, or,
+      tm = a.n_fastest ? t / a.tiles_n : t % a.tiles_m;   // when the activations outgrow L2, an activation tile
+    };
+    // a stage's barrier expects the bytes of both operands; the weight tile may be requested long before the
+    // activation tile
+    auto load_weights = [&](int stage, int c, int tn) {
+      const uint32_t full = full_target + 8 * stage;
+      const uint32_t bdst = b_tiles + stage * kBBytes;
+      if (PAIR) {
+        // own 128 weight rows (SiLU form: the leader holds the gate rows, the peer the up rows)
+        if (rank == 0) mbar_arrive_expect_tx_w(bar_full + 8 * stage, 2 * (kTcABytes + kBBytes));
+        const int brow = EPI == kTcSwiglu ? (rank == 0 ? tn * 128 : a.inter + tn * 128)
+                                          : tn * kTcBN + static_cast<int>(rank) * 128;
+        tma_load_2d_pair_w(bdst, &map_w, c * kTcBK, brow, full);
+      } else {
+        mbar_arrive_expect_tx_w(full, kTcABytes + kTcBBytes);
+        if (EPI == kTcSwiglu) {
+          tma_load_2d_w(bdst, &map_w, c * kTcBK, tn * 128, full);                             // 128 gate rows
+          tma_load_2d_w(bdst + kTcBBytes / 2, &map_w, c * kTcBK, a.inter + tn * 128, full);   // their up rows
+        } else {
+          tma_load_2d_w(bdst, &map_w, c * kTcBK, tn * kTcBN, full);
+        }
+      }
+    };
+    auto load_rows = [&](int stage, int c, int tm) {
+      const uint32_t full = full_target + 8 * stage;
+      const uint32_t adst = a_tiles + stage * kTcABytes;
+      if (PAIR) tma_load_2d_pair_w(adst, &map_x, c * kTcBK, tm * kRowsPerTile + static_cast<int>(rank) * kTcBM, full);
+      else tma_load_2d_w(adst, &map_x, c * kTcBK, tm * kTcBM, full);
+    };
+    // Weights are written by no kernel of a step: the first ring-full of weight tiles is requested before the
+    // dependency wait (the stages are fresh, nothing to wait for), the activation tiles follow after it.
+    int early = 0;
+    if (work0 < tiles) {
+      int tn, tm;
+      tile_of(work0, tn, tm);
+      early = c_end - c_begin < kStages ? c_end - c_begin : kStages;
+      for (int c = 0; c < early; ++c) load_weights(c, c_begin + c, tn);
+    }
+    pdl_wait();   // activations come from the preceding kernel
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
     for (int t = work0; t < tiles && ok; t += work_stride) {
-      const int tn = a.n_fastest ? t % a.tiles_n : t / a.tiles_m;   // consecutive CTAs share a weight tile, or,
-      const int tm = a.n_fastest ? t / a.tiles_n : t % a.tiles_m;   // when the activations outgrow L2, an activation tile
-      for (int c = 0; c < kchunks; ++c) {
-        if (!mbar_wait_w(bar_empty + 8 * stage, phase ^ 1)) { ok = false; break; }
-        const uint32_t full = full_target + 8 * stage;
-        const uint32_t adst = a_tiles + stage * kTcABytes;
-        const uint32_t bdst = b_tiles + stage * kBBytes;
-        if (PAIR) {
-          // own 128 step rows, own 128 weight rows (SiLU form: the leader holds the gate rows, the peer the up rows)
-          if (rank == 0) mbar_arrive_expect_tx_w(bar_full + 8 * stage, 2 * (kTcABytes + kBBytes));
-          tma_load_2d_pair_w(adst, &map_x, c * kTcBK, tm * kRowsPerTile + static_cast<int>(rank) * kTcBM, full);
-          const int brow = EPI == kTcSwiglu ? (rank == 0 ? tn * 128 : a.inter + tn * 128)
-                                            : tn * kTcBN + static_cast<int>(rank) * 128;
-          tma_load_2d_pair_w(bdst, &map_w, c * kTcBK, brow, full);
+      int tn, tm;
+      tile_of(t, tn, tm);
+      for (int c = c_begin; c < c_end; ++c) {
+        if (early > 0) {
+          --early;                       // weight tile of this stage already on its way
         } else {
-          mbar_arrive_expect_tx_w(full, kTcABytes + kTcBBytes);
-          tma_load_2d_w(adst, &map_x, c * kTcBK, tm * kTcBM, full);
-          if (EPI == kTcSwiglu) {
-            tma_load_2d_w(bdst, &map_w, c * kTcBK, tn * 128, full);                             // 128 gate rows
-            tma_load_2d_w(bdst + kTcBBytes / 2, &map_w, c * kTcBK, a.inter + tn * 128, full);   // their up rows
-          } else {
-            tma_load_2d_w(bdst, &map_w, c * kTcBK, tn * kTcBN, full);
-          }
+          if (!mbar_wait_w(bar_empty + 8 * stage, phase ^ 1)) { ok = false; break; }
+          load_weights(stage, c, tn);
         }
+        load_rows(stage, c, tm);
         if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
     }
@@ -257,15 +292,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         if (!mbar_wait_w(bar_acc_empty + 8 * acc, acc_phase ^ 1)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kTcBN;
-        for (int c = 0; c < kchunks; ++c) {
+        for (int c = c_begin; c < c_end; ++c) {
           if (!mbar_wait_w(bar_full + 8 * stage, phase)) { ok = false; break; }
           tc_fence_after();
           const uint64_t adesc = umma_desc_sw128(a_tiles + stage * kTcABytes);
           const uint64_t bdesc = umma_desc_sw128(b_tiles + stage * kBBytes);
 #pragma unroll
           for (int k16 = 0; k16 < kTcBK / 16; ++k16) {
-            if (PAIR) umma_bf16_pair_w(d_tmem, adesc + 2 * k16, bdesc + 2 * k16, idesc, (c > 0 || k16 > 0) ? 1u : 0u);
-            else umma_bf16_w(d_tmem, adesc + 2 * k16, bdesc + 2 * k16, idesc, (c > 0 || k16 > 0) ? 1u : 0u);
+            if (PAIR) umma_bf16_pair_w(d_tmem, adesc + 2 * k16, bdesc + 2 * k16, idesc, (c > c_begin || k16 > 0) ? 1u : 0u);
+            else umma_bf16_w(d_tmem, adesc + 2 * k16, bdesc + 2 * k16, idesc, (c > c_begin || k16 > 0) ? 1u : 0u);
           }
           if (PAIR) umma_commit_pair_w(bar_empty + 8 * stage);
           else umma_commit_w(bar_empty + 8 * stage);
@@ -327,15 +362,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       const int quarter = warp & 3;       // the 32 tensor-memory lanes this warp may read
       const uint32_t taddr = tmem_base + acc * kTcBN + (static_cast<uint32_t>(32 * quarter) << 16);
       const int row = tm * kRowsPerTile + static_cast<int>(rank) * kTcBM + 32 * quarter + lane;
+      if (EPI == kTcBf16 && ks > 1) {
+        // split-k cluster: every MMA of this CTA has completed, so the operand ring is idle (a cluster owns one
+        // tile, nothing more will be loaded): park the fp32 partial tile there, one row per thread
+        const uint32_t park = a_tiles + (32 * quarter + lane) * kTcParkStride + (warp >> 2) * (kTcBN / 2) * 4;
+#pragma unroll 1
+        for (int c = 0; c < kTcBN / 64; ++c) {
+          float v0[16], v1[16];
+          tmem_ld16(taddr + (warp >> 2) * (kTcBN / 2) + 32 * c, v0);
+          tmem_ld16(taddr + (warp >> 2) * (kTcBN / 2) + 32 * c + 16, v1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(park + (32 * c + 4 * i) * 4), "f"(v0[4 * i]),
+                         "f"(v0[4 * i + 1]), "f"(v0[4 * i + 2]), "f"(v0[4 * i + 3])
+                         : "memory");
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(park + (32 * c + 16 + 4 * i) * 4), "f"(v1[4 * i]),
+                         "f"(v1[4 * i + 1]), "f"(v1[4 * i + 2]), "f"(v1[4 * i + 3])
+                         : "memory");
+          }
+        }
+        parked_tile = t;
+        break;
+      }
       if (EPI == kTcBf16) {
         bf16* dst = a.y + static_cast<int64_t>(row) * a.ldy + tn * kTcBN;
         // Tensor-parallel pair: the copy for the peer is staged in shared memory, 32 rows x 64 columns per warp,
         // and leaves as 128-byte row segments (four rows per store instruction): over NVLink the 16-byte pieces
         // a thread holds of its own row would travel one by one.
         const bool peer_staged = a.y_peer != nullptr && (tn + 1) * kTcBN <= a.n;
-        const uint32_t stage_smem = base + bars_off + 256 + (warp & 3) * 4096;
+        const uint32_t stage_smem = base + bars_off + 256 + warp * 4096;
+        // two warps per quarter of tensor memory, 128 of the tile's 256 columns each
+        const int c0 = (warp >> 2) * (kTcBN / 64);
 #pragma unroll 1
-        for (int c = 0; c < kTcBN / 32; ++c) {
+        for (int c = c0; c < c0 + kTcBN / 64; ++c) {
           float v0[16], v1[16];
           tmem_ld16(taddr + 32 * c, v0);
           tmem_ld16(taddr + 32 * c + 16, v1);
@@ -658,8 +718,52 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
   }
 
+  if (EPI == kTcBf16 && ks > 1) {
+    // every CTA of the cluster has parked its partial tile; CTA kr sums rows [kr, kr + 1) * 128 / ks of all of
+    // them in CTA order (so the result does not depend on timing), rounds to bf16 and stores row segments
+    tc_fence_before();
+    cluster_sync_all();
+    if (warp < kEpiWarps) {
+      parked_tile = __shfl_sync(0xffffffffu, parked_tile, 0);
+      if (parked_tile >= 0) {
+        const int tn = a.n_fastest ? parked_tile % a.tiles_n : parked_tile / a.tiles_m;
+        const int tm = a.n_fastest ? parked_tile / a.tiles_n : parked_tile % a.tiles_m;
+        const int rows_per = kTcBM / ks;
+        const int r0 = static_cast<int>(kr) * rows_per;
+        for (int item = threadIdx.x; item < rows_per * (kTcBN / 4); item += kEpiWarps * 32) {
+          const int r = r0 + item / (kTcBN / 4), c4 = item % (kTcBN / 4);
+          // all remote loads of an element go out together (a remote read is several hundred cycles), the sum
+          // then runs in CTA order
+          float4 v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (j < ks)
+              asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                           : "=f"(v[j].x), "=f"(v[j].y), "=f"(v[j].z), "=f"(v[j].w)
+                           : "r"(map_to_cta(a_tiles + r * kTcParkStride + c4 * 16, static_cast<uint32_t>(j))));
+          }
+          float4 sum = v[0];
+#pragma unroll
+          for (int j = 1; j < 8; ++j)
+            if (j < ks) { sum.x += v[j].x; sum.y += v[j].y; sum.z += v[j].z; sum.w += v[j].w; }
+          const int grow = tm * kTcBM + r, col = tn * kTcBN + 4 * c4;
+          if (grow < a.m) {
+            bf16* dst = a.y + static_cast<int64_t>(grow) * a.ldy + col;
+            if (col + 4 <= a.n) {
+              *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16x2(sum.x, sum.y), pack_bf16x2(sum.z, sum.w));
+            } else {
+              const float e[4] = {sum.x, sum.y, sum.z, sum.w};
+              for (int i = 0; i < 4; ++i)
+                if (col + i < a.n) dst[i] = __float2bfloat16_rn(e[i]);
+            }
+          }
+        }
+      }
+    }
+  }
   tc_fence_before();
-  if (PAIR) cluster_sync_all();            // neither CTA leaves while the other may still read its shared memory
+  if (PAIR || ks > 1) cluster_sync_all();  // no CTA leaves while another may still read its shared memory
   else __syncthreads();
   if ((EPI == kTcBf16 || EPI == kTcLmHead) && threadIdx.x == 0) tp_signal(a.tp);   // all peer stores of this CTA were issued before the barrier
   if (warp == kMmaWarp) {
@@ -689,9 +793,9 @@ static int launch_tc_impl(const bf16* x, int64_t ldx, const bf16* w, int w_rows,
     if (sm_count <= 0) sm_count = 148;
   }
   constexpr int kRowsPerTile = PAIR ? 2 * kTcBM : kTcBM;
-  // after the barriers: sampler records (LM head), the peer's staged tile (bf16 form), or 4 KB per epilogue warp
-  // for the cos | sin rows (q/k-norm + rotation form)
-  constexpr int kTail = EPI == kTcQkvRope ? tc_epi_warps(EPI) * 4096 : kTcLmRecBytes;
+  // after the barriers: sampler records (LM head), or 4 KB per epilogue warp: the peer's staged tile (bf16 form),
+  // the cos | sin rows and the turned-around stores (q/k-norm + rotation form)
+  constexpr int kTail = (EPI == kTcQkvRope || EPI == kTcBf16) ? tc_epi_warps(EPI) * 4096 : kTcLmRecBytes;
   constexpr int kSmem = 1024 + (PAIR ? kTcPairStages * (kTcABytes + kTcBBytes / 2) : kTcStages * (kTcABytes + kTcBBytes)) +
                         256 + kTail;
   static_assert(kSmem <= 232448, "shared memory of the tile GEMM");
@@ -714,6 +818,46 @@ static int launch_tc_impl(const bf16* x, int64_t ldx, const bf16* w, int w_rows,
   }
   const int tiles = a.tiles_m * a.tiles_n;
   a.grid = tiles < sm_count ? tiles : sm_count;
+  a.ksplit = 1;
+  if (!PAIR && EPI == kTcBf16 && a.y_peer == nullptr && a.tp.peer_flags == nullptr) {
+    // Few tiles (a projection onto 2048 columns has 8 per 128 step rows): clusters of 2, 4 or 8 CTAs split k so
+    // that about every SM streams a share of the weight; at least eight 64-wide chunks per slice.
+    // A cluster lives inside one processing cluster of the GPU, so fewer clusters of 8 fit than SMs / 8: a split is
+    // only taken when all its clusters are resident at once (a second wave would double the time).
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(tc_threads(EPI));
+    cfg.dynamicSmemBytes = kSmem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    static int max_clusters[4] = {0, 0, 0, 0};     // resident clusters of 2, 4, 8 CTAs (index = log2)
+    int ksplit = 8, lg = 3;
+    for (; ksplit > 1; ksplit >>= 1, --lg) {
+      if (a.k / kTcBK < 8 * ksplit) continue;
+      if (max_clusters[lg] == 0) {
+        int n = 0;
+        cfg.gridDim = dim3(sm_count / ksplit * ksplit);
+        attr[0].val.clusterDim.x = ksplit;
+        cfg.numAttrs = 1;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<EPI, PAIR>, &cfg) != cudaSuccess || n <= 0) n = -1;
+        max_clusters[lg] = n;
+      }
+      if (tiles <= max_clusters[lg]) break;
+    }
+    if (ksplit > 1) {
+      a.ksplit = ksplit;
+      a.grid = tiles * ksplit;
+      cfg.gridDim = dim3(tiles * ksplit);
+      attr[0].val.clusterDim.x = ksplit;
+      cfg.numAttrs = g_opt_pdl ? 2 : 1;
+      return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<EPI, PAIR>, map_x, map_w, a) == cudaSuccess ? MDB_OK : MDB_ERR_CUDA;
+    }
+  }
   if (!PAIR)
     return mdb_launch(gemm_tc_kernel<EPI, PAIR>, dim3(tiles < sm_count ? tiles : sm_count), dim3(tc_threads(EPI)), kSmem,
                       st, map_x, map_w, a);

@@ -39,6 +39,8 @@ constexpr int kWsTileRows = 128;          // weight rows per tile = UMMA M
 constexpr int kWsBK = 64;                 // k per stage: one 128-byte swizzle atom of bf16
 constexpr int kWsWTileBytes = kWsTileRows * kWsBK * 2;   // 16 KB
 constexpr int kWsThreads = 192;           // warps 0-3 epilogue, 4 producer, 5 MMA
+constexpr int kWsMaxRows = 64;            // step rows of the fused epilogues (bf16, SiLU*mul, LM head)
+constexpr int kWsMaxRowsPartial = 256;    // step rows of the split-k slice form = the widest UMMA N
 constexpr int kWsEpiFloats = kWsTileRows * 33;           // staging tile [128][33] fp32
 
 struct WsArgs {
@@ -223,7 +225,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tasks = a.tiles_n * a.ksplit;
   if (threadIdx.x == 0) trace_event(EPI, 0);
-  const uint32_t tmem_cols = 2 * a.ntok <= 32 ? 32 : (2 * a.ntok <= 64 ? 64 : 128);
+  uint32_t tmem_cols = 32;          // two accumulator buffers of ntok columns, rounded up to a power of two
+  while (tmem_cols < 2u * a.ntok) tmem_cols <<= 1;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < a.stages; ++s) {
@@ -356,6 +359,37 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       if (threadIdx.x == 0) trace_event(EPI, 6);
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * a.ntok + (static_cast<uint32_t>(32 * warp) << 16);
+      if (EPI == kWsPartial && a.ntok > 64) {
+        // more than 64 step rows: the accumulator row of a thread is drained 64 columns at a time
+        const int row = tile * kWsTileRows + 32 * warp + lane;
+        float* dst = a.partials + static_cast<int64_t>(slice) * a.m * a.n + row;
+        for (int t0 = 0; t0 < a.ntok; t0 += 64) {
+          float v[64];
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            if (t0 + 16 * c < a.ntok) {
+              float t16[16];
+              tmem_ld16(taddr + t0 + 16 * c, t16);
+#pragma unroll
+              for (int i = 0; i < 16; ++i) v[16 * c + i] = t16[i];
+            }
+          tmem_ld_wait();
+          if (t0 + 64 >= a.ntok) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);   // accumulator buffer may be overwritten
+          }
+          if (!waited_deps) {
+            pdl_wait();
+            waited_deps = true;
+          }
+#pragma unroll
+          for (int t = 0; t < 64; ++t)
+            if (t0 + t < a.m) dst[static_cast<int64_t>(t0 + t) * a.n] = v[t];
+        }
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        continue;
+      }
       float v[64];
 #pragma unroll
       for (int c = 0; c < 4; ++c)
@@ -561,7 +595,7 @@ static int ws_smem_bytes(int stages, int ntok) {
 
 // Shapes the tensor-core streaming kernel takes; anything else goes to the register-streaming kernel.
 static bool ws_supported(int epi, int m, int n, int k, int64_t ldx) {
-  if (m < 1 || m > 64 || k % kWsBK != 0 || ldx % 8 != 0) return false;
+  if (m < 1 || m > (epi == kWsPartial ? kWsMaxRowsPartial : kWsMaxRows) || k % kWsBK != 0 || ldx % 8 != 0) return false;
   if (epi == kWsSwiglu) return (n / 2) % 64 == 0;
   return n % kWsTileRows == 0;
 }

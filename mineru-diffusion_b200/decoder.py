@@ -26,6 +26,11 @@ from .engine.context import Context
 
 PAGE = 256
 SKINNY_MAX_ROWS = 64
+# o_proj / down_proj keep the split-k slice form of the weight-streaming kernel up to 128 rows: it still beats the
+# tile GEMM there although that one splits k over clusters when it has few tiles.  Measured on B200 (projection +
+# the norm that follows, slice form against tile GEMM): o_proj 11.0 / 11.8 / 15.4 us against 12.9 / 12.9 / 13.4 at
+# 96 / 128 / 192 rows; down_proj 13.5 / 14.1 / 19.0 against 15.7 / 15.6 / 18.5.
+SLICE_MAX_ROWS = (128, 128)     # (o_proj, down_proj), one GPU; a tensor-parallel pair switches at SKINNY_MAX_ROWS
 
 
 @dataclass
@@ -138,7 +143,7 @@ class DecoderEngine:
         self.final = buf(t, h)
         self.lm_rows = buf(max_seqs * block_size, h)
         # weight-streaming path: fp32 split-k slices shared by all four GEMMs
-        rows = min(t, SKINNY_MAX_ROWS)
+        rows = min(t, max(SKINNY_MAX_ROWS, *SLICE_MAX_ROWS))
         self.ks_qkv = ops.pick_ksplit(rows, self.nqkv, h)
         self.ks_o = ops.pick_ksplit(rows, h, hq * d)
         self.ks_down = ops.pick_ksplit(rows, h, i)
@@ -233,7 +238,7 @@ class DecoderEngine:
         flag slots to wait on, their number, launch tag)."""
         h = self.cfg.hidden_size
         ks = self.ks_o if which == 0 else self.ks_down
-        if m <= SKINNY_MAX_ROWS:
+        if m <= SKINNY_MAX_ROWS or (self.tp is None and m <= SLICE_MAX_ROWS[which] and ks > 1):
             if self.tp is None:
                 parts = self.partials[:ks * m * h].view(ks, m, h)
                 ops.gemm_splitk_partials(x_in, w, ks, parts)

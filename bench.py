@@ -191,7 +191,10 @@ def timed_steps(engine, runner, steps: int, warmup: int, local_rank: int, world:
     for _ in range(warmup):
         engine.step()
     torch.cuda.synchronize()
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    # one event pair per step launched; with launch-ahead a step is launched during the call before the one that
+    # collects it, so the runner takes pairs from an iterator and names the pair of the step each call collected
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps + 2)]
+    used = []
     sampler = ClockSampler(local_rank) if sample_clocks else None
     if world > 1:
         torch.distributed.barrier()
@@ -202,13 +205,14 @@ def timed_steps(engine, runner, steps: int, warmup: int, local_rank: int, world:
     wall0 = time.perf_counter()
     e_all0, e_all1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e_all0.record(stream)
+    runner.step_events = iter(ev)
     for i in range(steps):
         if engine.is_finished():
             break
-        runner.step_events = ev[i]
         _, n = engine.step()
         tokens += -n if n < 0 else 0
         steps_done += 1
+        used.append(runner.last_step_events)
     e_all1.record(stream)
     torch.cuda.synchronize()
     wall = time.perf_counter() - wall0
@@ -216,7 +220,12 @@ def timed_steps(engine, runner, steps: int, warmup: int, local_rank: int, world:
         torch.distributed.barrier()
     clocks = sampler.stop() if sampler else None
     runner.step_events = None
-    dev_ms = sum(a.elapsed_time(b) for a, b in ev[:steps_done])
+    # the first timed call may collect a step launched (ahead) before the events were handed over: it is timed by
+    # the average of the others
+    timed = [p for p in used if p is not None]
+    dev_ms = sum(a.elapsed_time(b) for a, b in timed)
+    if timed and len(timed) < steps_done:
+        dev_ms *= steps_done / len(timed)
     e2e_ms = max(e_all0.elapsed_time(e_all1), wall * 1e3)
     return dict(tokens=tokens, steps=steps_done, dev_ms=dev_ms, e2e_ms=e2e_ms, clocks=clocks)
 

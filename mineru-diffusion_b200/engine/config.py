@@ -61,6 +61,12 @@ class Config:
     # and, in the same step, the first denoising pass of its next block (one pass per block saved; the tokens
     # are the ones the two separate passes would produce from the same noise).  Off: the reference's schedule.
     fuse_commit_pass: bool = False
+    # Not in the reference: after a decode step whose requests all stay on their blocks, the runner launches the
+    # next step at once (same requests, the block ids just produced) instead of waiting for the scheduler to ask
+    # for it; when the scheduler then asks for exactly that step, only its results are collected, otherwise they
+    # are thrown away and the step asked for runs.  Same tokens either way; the host's work between two steps
+    # overlaps with the GPU's.
+    launch_ahead: bool = True
 
     def __post_init__(self):
         if self.kvcache_block_size % 256 != 0:

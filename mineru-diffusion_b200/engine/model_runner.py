@@ -179,7 +179,15 @@ class ModelRunner:
         self.graph_bs: list[int] = []
         self.last: dict = {}
         self.keep_last = False        # tests: keep x0 / confidence / hidden of the last step
-        self.step_events = None       # benchmark: (start, end) CUDA events around the GPU work of a step
+        # benchmark: CUDA events around the GPU work of a step -- one (start, end) pair used for every step, or an
+        # iterator of pairs, one taken per step launched; last_step_events = the pair of the step last collected
+        self.step_events = None
+        self.last_step_events = None
+        # launch-ahead (Config.launch_ahead): the step launched before the scheduler asked for it
+        self.launch_ahead = bool(getattr(config, "launch_ahead", False))
+        self._ahead = None            # (requests, lengths key, block tensors, event pair)
+        self._pair = None             # event pair of the step being launched / collected
+        self.ahead_hits = self.ahead_misses = 0
         if not self.enforce_eager:
             self.capture_cudagraph()
 
@@ -352,8 +360,9 @@ class ModelRunner:
         bs = len(seqs)
         use_graph = (not self.enforce_eager) and self.noise != "explicit" and bs <= self.max_bs and self.graph_bs
         max_ctx = self.prepare_decode(seqs, copy=not use_graph)   # a graph starts with the copy of the packed inputs
-        if self.step_events is not None:
-            self.step_events[0].record()
+        self._pair = self._next_event_pair()
+        if self._pair is not None:
+            self._pair[0].record()
         if use_graph:
             gbs = next(x for x in self.graph_bs if x >= bs)
             graph, _ = self.graphs[gbs]
@@ -389,10 +398,19 @@ class ModelRunner:
         return rows
 
     # ------------------------------------------------------------------ entry point
-    def run(self, seqs: list[Sequence], is_prefill: bool) -> int:
+    def _next_event_pair(self):
+        ev = self.step_events
+        if ev is None:
+            return None
+        if isinstance(ev, (tuple, list)):
+            return ev
+        return next(ev, None)
+
+    def _launch(self, seqs: list[Sequence], is_prefill: bool):
+        """Everything of a step up to, not including, the wait for its results: forward pass, unmask rule, the
+        copy of the results to pinned memory.  Returns the (possibly extended) request list."""
         bs, b = len(seqs), self.block_size
-        if bs > self.max_bs:
-            raise AssertionError("batch larger than max_num_seqs")
+        self._pair = None
         if is_prefill:
             hidden = self.run_model_prefill(seqs)
         else:
@@ -422,35 +440,91 @@ class ModelRunner:
             ops.unmask_decide(d_ids, self.engine.x0[:m], self.engine.conf[:m], seqs[0].mask_token_id,
                               sp.dynamic_threshold, 1, transfer=d_transfer, counts=d_counts, quotas=quotas,
                               status_out=d_status)
-            if self.step_events is not None and not is_prefill:
-                self.step_events[1].record()
+            if self._pair is not None and not is_prefill:
+                self._pair[1].record()
             h_all.copy_(d_all, non_blocking=True)
             if self.keep_last:
                 self.last = dict(x0=self.engine.x0[:m].clone(), conf=self.engine.conf[:m].clone(),
                                  hidden=None if hidden is None else hidden.clone())
-            torch.cuda.current_stream().synchronize()
-        status = int(h_status[0])
+        return seqs
+
+    def _ahead_possible(self, seqs: list[Sequence], was_caching: bool) -> bool:
+        """May the step after this decode step be launched before the scheduler asks for it?  Only the plain case:
+        graph replay, the nano engine's unmask rule, one GPU, and no request that has just committed its block
+        (the scheduler gives those a new block or retires them, so the next step has other inputs)."""
+        if not self.launch_ahead or was_caching or self.keep_last or self.fuse_commit_pass or self.tp_pair is not None:
+            return False
+        if self.enforce_eager or self.noise == "explicit" or not self.graph_bs or len(seqs) > self.max_bs:
+            return False
+        return all(getattr(seq.sampling_params, "denoising_steps", None) is None for seq in seqs)
+
+    @staticmethod
+    def _ahead_matches(ahead, seqs: list[Sequence]) -> bool:
+        held, key, rows, _ = ahead
+        if len(seqs) != len(held) or not all(a is b for a, b in zip(seqs, held)):
+            return False
+        if key != (tuple(map(len, seqs)), tuple(len(seq.block_table) for seq in seqs)):
+            return False
+        return all(seq.current_denoising_block is rows[i] for i, seq in enumerate(seqs))
+
+    def _wait_results(self, bs: int):
+        torch.cuda.current_stream().synchronize()
+        views = self._result_views(bs)
+        status = int(views[-1][0])
         if status:
             # a kernel of this step skipped an access or gave up a wait (bad slot / page / token id / position,
             # or a bounded wait that ran out): the step's tokens cannot be trusted.  The word is already cleared.
             raise RuntimeError(f"decode step {self.step_index}: device status word {status:#x} "
                                "(1 bad slot, 2 bad page, 4 bad token id, 8 bad position, 16 wait timed out)")
+        return views
+
+    def run(self, seqs: list[Sequence], is_prefill: bool) -> int:
+        if len(seqs) > self.max_bs:
+            raise AssertionError("batch larger than max_num_seqs")
+        ahead, self._ahead = self._ahead, None
+        if ahead is not None and not is_prefill and self._ahead_matches(ahead, seqs):
+            # the step asked for is the one already on the GPU
+            self.ahead_hits += 1
+            self._pair = ahead[3]
+        else:
+            if ahead is not None:
+                # another step was asked for: let the one in flight finish (its K/V rows are tentative ones of the
+                # same blocks, its noise step number is reused by the step that now runs) and drop its results
+                self.ahead_misses += 1
+                self._wait_results(len(ahead[0]))
+            seqs = self._launch(seqs, is_prefill)
+        bs = len(seqs)
+        # requests on their commit pass get a new block (or retire) before the next step: nothing to launch ahead
+        was_caching = self.launch_ahead and not is_prefill and any(seq.is_caching for seq in seqs
+                                                                   if type(seq) is not _NextBlock)
+        (_, _, _, _, _, h_ids, h_counts, h_transfer, _, _) = self._wait_results(bs)
+        self.last_step_events = self._pair
         # one copy of the results for the whole batch; every request keeps a row of it
         blocks = h_ids.clone()
         rows = blocks.unbind(0)
         moved = h_transfer != 0
+        count = int(h_counts.sum())
+        for i, seq in enumerate(seqs):
+            if type(seq) is not _NextBlock:
+                seq.current_denoising_block = rows[i]
+        self._last_rows, self._last_blocks = rows, blocks.numpy()   # shares memory with the rows
+        self.step_index += 1
+        launched = not is_prefill and self._ahead_possible(seqs, was_caching)
+        if launched:
+            # the next step of these requests, on the blocks just handed out, goes to the GPU before the rest of
+            # this step's bookkeeping
+            self._launch(seqs, False)
+            key = (tuple(map(len, seqs)), tuple(len(seq.block_table) for seq in seqs))
+            self._ahead = (list(seqs), key, rows, self._pair)
         moved_any = moved.any(axis=1)
         for i, seq in enumerate(seqs):
             if type(seq) is _NextBlock:     # applied by Scheduler.postprocess once the block before it is appended
                 seq.seq.pending_first_step = (rows[i], moved[i].copy() if moved_any[i] else None)
                 continue
-            seq.current_denoising_block = rows[i]
             if moved_any[i]:
                 seq.current_step_map.numpy()[moved[i]] = seq.current_denoise_step
             seq.current_denoise_step += 1
-        self._last_rows, self._last_blocks = rows, blocks.numpy()   # shares memory with the rows
-        self.step_index += 1
-        return int(h_counts.sum())
+        return count
 
     def _step_quotas(self, seqs, is_prefill: bool):
         """Per-request quota of this pass, or None for the nano engine's rule (one token unless more pass the

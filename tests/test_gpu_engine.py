@@ -393,6 +393,50 @@ def test_reused_step_inputs_change_nothing(mdb):
     assert mdb._lib.device_status(clear=True) == 0
 
 
+def test_launch_ahead_changes_nothing(mdb):
+    """Config.launch_ahead: after a decode step whose requests stay on their blocks the runner launches the next
+    step before the scheduler asks for it, and collects it when it does.  Five requests of different lengths
+    (blocks finish at different times, requests retire, a sixth joins late and is prefilled in between): tokens,
+    step maps and step counts must equal those of a runner that never launches ahead; steps were collected from
+    launches made ahead, and launches that turned out not to be the step asked for were dropped."""
+    dcfg = _tiny_cfg(mdb, vocab=1024, layers=2, hkv=2)
+    weights = orc.make_weights(_oracle_cfg(dcfg), seed=17)
+    outs, counts = [], []
+    for ahead in (False, True):
+        cfg = mdb.Config(max_num_batched_tokens=2048, max_num_seqs=4, max_model_len=1024, enforce_eager=False,
+                         num_kvcache_blocks=12, decoder_config=dcfg, mask_token_id=500, launch_ahead=ahead)
+        runner = mdb.ModelRunner(cfg, weights=mdb.DecoderWeights.from_reference_layout(weights, DEV), noise="gumbel")
+        engine = mdb.LLMEngine(cfg, runner)
+        gen = torch.Generator().manual_seed(6)
+        seqs = []
+        for plen, new in [(100, 64), (300, 96), (31, 32), (250, 64), (64, 64), (40, 32)]:
+            sp = mdb.SamplingParams(temperature=0.05, max_new_tokens=new, ignore_eos=True)
+            seqs.append(mdb.Sequence(torch.randint(0, 490, (plen,), generator=gen).tolist(), sp,
+                                     denoising_block_size=32, mask_token_id=500))
+        for seq in seqs[:5]:
+            engine.add_sequence(seq)
+        done, steps = {}, 0
+        while not engine.is_finished():
+            if steps == 7:
+                engine.add_sequence(seqs[5])        # arrives while a step launched ahead is in flight
+            outputs, _ = engine.step()
+            steps += 1
+            for seq_id, toks, step_map in outputs:
+                done[seq_id] = (toks, step_map)
+        outs.append([done[s.seq_id] for s in seqs])
+        counts.append((steps, engine.num_decode_steps, runner.ahead_hits, runner.ahead_misses))
+        assert len(engine.scheduler.block_manager.free_block_ids) == 12
+        runner.exit()
+    for (tok_a, map_a), (tok_b, map_b) in zip(*outs):
+        assert tok_a == tok_b and map_a == map_b
+    assert counts[0][:2] == counts[1][:2]
+    assert counts[0][2:] == (0, 0)
+    assert counts[1][2] > counts[1][1] // 2 and counts[1][3] >= 1, counts
+    print(f"launch ahead: {counts[1][2]} of {counts[1][1]} decode steps collected from launches made ahead, "
+          f"{counts[1][3]} launches dropped")
+    assert mdb._lib.device_status(clear=True) == 0
+
+
 # --------------------------------------------------------------------- full-size decoder
 @pytest.fixture(scope="module")
 def full_size(mdb):

@@ -31,6 +31,20 @@ def mdb():
     return importlib.import_module("mineru-diffusion_b200")
 
 
+# Where the GPU tests leave their parity figures (one JSON object per line), if that folder exists.
+RECORD_DIR = os.environ.get("MDB200_RECORD_DIR", os.path.join(ROOT, "gpurun_out"))
+
+
+def record_parity(name: str, **figures) -> None:
+    """Parity figures of a test: printed, and appended to ``parity_tests.jsonl`` in the records folder."""
+    import json
+    line = json.dumps(dict(test=name, **figures))
+    print("PARITY " + line)
+    if os.path.isdir(RECORD_DIR):
+        with open(os.path.join(RECORD_DIR, "parity_tests.jsonl"), "a") as f:
+            f.write(line + "\n")
+
+
 def load_golden(name: str) -> dict:
     return dict(np.load(os.path.join(GOLDEN, name)))
 

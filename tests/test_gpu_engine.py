@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import bf16_from_bits, load_golden
+from conftest import bf16_from_bits, load_golden, record_parity
 from oracle import nano_oracle as orc
 
 pytestmark = pytest.mark.gpu
@@ -82,16 +82,7 @@ REF_PATH_FLOOR = 0.094  # what the reference's own prefill-form and decode-form 
                         # after 28 bf16 layers (measured with its modules on CPU); the yardstick for the full-size test
 
 
-def _record(name: str, **figures):
-    """Parity figures of a test: printed, and appended to gpurun_out/parity_tests.jsonl when that folder exists."""
-    import json
-    import os
-    line = json.dumps(dict(test=name, **figures))
-    print("PARITY " + line)
-    out = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
-    if os.path.isdir(out):
-        with open(os.path.join(out, "parity_tests.jsonl"), "a") as f:
-            f.write(line + "\n")
+_record = record_parity
 
 
 def _logits_err(hidden_got, hidden_ref, lm_head):

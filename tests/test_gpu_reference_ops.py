@@ -8,12 +8,10 @@ kernels of this repository are compared with the very calls the reference makes;
 or their first call raises, the test is skipped with the error text and the restatement stays the only pin.
 The library calls are also timed (CUDA events) as the "library through torch" bar for the same inputs.
 """
-import json
-import os
-
 import pytest
 import torch
 
+from conftest import record_parity
 from oracle import nano_oracle as orc
 
 pytestmark = pytest.mark.gpu
@@ -21,13 +19,7 @@ BF = torch.bfloat16
 DEV = "cuda"
 
 
-def _record(name: str, **figures):
-    line = json.dumps(dict(test=name, **figures))
-    print("PARITY " + line)
-    out = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
-    if os.path.isdir(out):
-        with open(os.path.join(out, "parity_tests.jsonl"), "a") as f:
-            f.write(line + "\n")
+_record = record_parity
 
 
 def _time_us(fn, reps=20):

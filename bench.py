@@ -190,6 +190,10 @@ def timed_steps(engine, runner, steps: int, warmup: int, local_rank: int, world:
         engine.step()
     for _ in range(warmup):
         engine.step()
+    # the timed region holds exactly the timed steps: a step launched ahead by the last warm-up call is dropped, and
+    # the last timed call launches none
+    ahead_setting = runner.launch_ahead
+    runner.cancel_ahead()
     torch.cuda.synchronize()
     # one event pair per step launched; with launch-ahead a step is launched during the call before the one that
     # collects it, so the runner takes pairs from an iterator and names the pair of the step each call collected
@@ -206,9 +210,12 @@ def timed_steps(engine, runner, steps: int, warmup: int, local_rank: int, world:
     e_all0, e_all1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e_all0.record(stream)
     runner.step_events = iter(ev)
+    hits0 = runner.ahead_hits
     for i in range(steps):
         if engine.is_finished():
             break
+        if i == steps - 1:
+            runner.launch_ahead = False
         _, n = engine.step()
         tokens += -n if n < 0 else 0
         steps_done += 1
@@ -220,14 +227,11 @@ def timed_steps(engine, runner, steps: int, warmup: int, local_rank: int, world:
         torch.distributed.barrier()
     clocks = sampler.stop() if sampler else None
     runner.step_events = None
-    # the first timed call may collect a step launched (ahead) before the events were handed over: it is timed by
-    # the average of the others
-    timed = [p for p in used if p is not None]
-    dev_ms = sum(a.elapsed_time(b) for a, b in timed)
-    if timed and len(timed) < steps_done:
-        dev_ms *= steps_done / len(timed)
+    runner.launch_ahead = ahead_setting
+    dev_ms = sum(p[0].elapsed_time(p[1]) for p in used if p is not None)   # a prefill step carries no pair
     e2e_ms = max(e_all0.elapsed_time(e_all1), wall * 1e3)
-    return dict(tokens=tokens, steps=steps_done, dev_ms=dev_ms, e2e_ms=e2e_ms, clocks=clocks)
+    return dict(tokens=tokens, steps=steps_done, dev_ms=dev_ms, e2e_ms=e2e_ms, clocks=clocks,
+                ahead_hits=runner.ahead_hits - hits0)
 
 
 def run_workload(pkg, wl: Workload, args, rank: int, world: int, local_rank: int, tp: int = 1):
@@ -243,7 +247,10 @@ def run_workload(pkg, wl: Workload, args, rank: int, world: int, local_rank: int
     seed = 2 if tp == 2 else 2 + rank
     cfg, runner, engine = build_engine(pkg, wl, device, tp, rank, seed, visual_rows)
     res = timed_steps(engine, runner, args.steps, args.warmup, local_rank, world)
-    res.update(h2d=runner.inputs.nbytes,             # the packed step inputs (first node of the step graph)
+    # the packed step inputs: a step collected from a launch made ahead took its block ids and step counters from
+    # the device and copied only the rest
+    ahead = res.get("ahead_hits", 0) / max(res["steps"], 1)
+    res.update(h2d=int(round(runner.inputs.nbytes - ahead * runner.inputs.o_pos)),
                d2h=nreq * (wl.block * 8 + wl.block + 4) + 4,
                launches=runner.launches_per_decode_step(nreq) * res["steps"],
                status=pkg._lib.device_status(clear=True))

@@ -37,21 +37,24 @@ class _StepInputs:
     """One pinned host buffer and its device twin holding every per-step input
     of the decode form, so a step costs a single host->device copy.
 
-    Layout (all offsets 16-byte aligned): ids int64 [bs*B] | positions int64
-    [bs*B] | slots int32 [bs*B] | ctx_lens int32 [bs] | block_tables int32
-    [bs*max_pages] | temperatures fp32 [bs] | step uint32 [4]."""
+    Layout (all offsets 16-byte aligned): ids int64 [bs*B] | step uint32 [4] |
+    positions int64 [bs*B] | slots int32 [bs*B] | ctx_lens int32 [bs] |
+    block_tables int32 [bs*max_pages] | temperatures fp32 [bs].  The first two
+    fields are what a step changes on the device itself (block ids handed on by
+    the unmask rule, step counters incremented): a step launched ahead of the
+    host copies only the rest (``o_pos`` onwards)."""
 
     def __init__(self, max_bs: int, block: int, max_pages: int, device):
         self.max_bs, self.block, self.max_pages = max_bs, block, max_pages
         n = max_bs * block
         off = 0
         self.o_ids = off; off += _round_up(n * 8, 16)
+        self.o_step = off; off += 16
         self.o_pos = off; off += _round_up(n * 8, 16)
         self.o_slots = off; off += _round_up(n * 4, 16)
         self.o_ctx = off; off += _round_up(max_bs * 4, 16)
         self.o_tab = off; off += _round_up(max_bs * max_pages * 4, 16)
         self.o_temp = off; off += _round_up(max_bs * 4, 16)
-        self.o_step = off; off += 16
         self.nbytes = off
         self.host = torch.zeros(off, dtype=torch.uint8, pin_memory=True)
         self.dev = torch.zeros(off, dtype=torch.uint8, device=device)
@@ -166,11 +169,17 @@ class ModelRunner:
         # sampler state: one flat device buffer and its pinned mirror, laid out per batch size as
         # ids int64 [bs, B] | counts int32 [bs] | transfer u8 [bs, B], so the results of a step come back in one copy
         # ... followed by the device status word of the step (4 bytes)
-        self.res_dev = torch.zeros(self.max_bs * (9 * b + 4) + 4, dtype=torch.uint8, device=self.device)
-        self.res_host = torch.zeros(self.max_bs * (9 * b + 4) + 4, dtype=torch.uint8, pin_memory=True)
+        # ... twice: a step launched ahead writes the other set while the host still reads this one
+        self.res_dev = [torch.zeros(self.max_bs * (9 * b + 4) + 4, dtype=torch.uint8, device=self.device)
+                        for _ in range(2)]
+        self.res_host = [torch.zeros(self.max_bs * (9 * b + 4) + 4, dtype=torch.uint8, pin_memory=True)
+                         for _ in range(2)]
+        self._done = [torch.cuda.Event(), torch.cuda.Event()]   # results of set p have reached pinned memory
+        self._parity = 0
+        self._tails: dict[tuple, torch.cuda.CUDAGraph] = {}     # (bs, set, mask id, threshold) -> graph
         self.quota_host = torch.ones(self.max_bs, dtype=torch.int32, pin_memory=True)
         self.quota_dev = torch.ones(self.max_bs, dtype=torch.int32, device=self.device)
-        self._res_views: dict[int, tuple] = {}
+        self._res_views: dict[tuple, tuple] = {}
         self._decode_key = None       # lengths and page counts the pinned step inputs were last built for
         self._decode_seqs: list = []  # ... and the requests themselves
         self._last_rows, self._last_blocks = None, None   # blocks handed to the requests after the last step
@@ -185,7 +194,7 @@ class ModelRunner:
         self.last_step_events = None
         # launch-ahead (Config.launch_ahead): the step launched before the scheduler asked for it
         self.launch_ahead = bool(getattr(config, "launch_ahead", False))
-        self._ahead = None            # (requests, lengths key, block tensors, event pair)
+        self._ahead = None            # record of the step launched ahead (see _launch_ahead)
         self._pair = None             # event pair of the step being launched / collected
         self.ahead_hits = self.ahead_misses = 0
         if not self.enforce_eager:
@@ -256,21 +265,22 @@ class ModelRunner:
                       self.block_size)
         return up(inp["input_ids"]), up(inp["positions"]), ctx, inp["cu_seqlens"].tolist()
 
-    def _result_views(self, bs: int):
-        """Views of the sampler-state buffers for a step of ``bs`` requests:
+    def _result_views(self, bs: int, p: int = 0):
+        """Views of result set ``p`` of the sampler-state buffers for a step of ``bs`` requests:
         (device bytes, pinned bytes, device ids/counts/transfer, pinned ids and numpy views of the pinned
         counts/transfer, device status word, numpy view of its pinned copy)."""
-        v = self._res_views.get(bs)
+        v = self._res_views.get((bs, p))
         if v is None:
             b = self.block_size
             o1, o2, o3 = bs * b * 8, bs * b * 8 + bs * 4, bs * (9 * b + 4)
+            dev, pinned = self.res_dev[p], self.res_host[p]
             def split(buf):
                 return (buf[:o1].view(torch.int64).view(bs, b), buf[o1:o2].view(torch.int32), buf[o2:o3].view(bs, b))
-            host = split(self.res_host)
-            v = ((self.res_dev[:o3 + 4], self.res_host[:o3 + 4]) + split(self.res_dev)
+            host = split(pinned)
+            v = ((dev[:o3 + 4], pinned[:o3 + 4]) + split(dev)
                  + (host[0], host[1].numpy(), host[2].numpy())
-                 + (self.res_dev[o3:o3 + 4].view(torch.int32), self.res_host[o3:o3 + 4].view(torch.int32).numpy()))
-            self._res_views[bs] = v
+                 + (dev[o3:o3 + 4].view(torch.int32), pinned[o3:o3 + 4].view(torch.int32).numpy()))
+            self._res_views[(bs, p)] = v
         return v
 
     def prepare_decode(self, seqs: list[Sequence], copy: bool = True):
@@ -364,6 +374,8 @@ class ModelRunner:
         if self._pair is not None:
             self._pair[0].record()
         if use_graph:
+            o = self.inputs.o_pos
+            self.inputs.dev[:o].copy_(self.inputs.host[:o], non_blocking=True)   # block ids, step counters
             gbs = next(x for x in self.graph_bs if x >= bs)
             graph, _ = self.graphs[gbs]
             graph.replay()
@@ -406,11 +418,39 @@ class ModelRunner:
             return ev
         return next(ev, None)
 
+    def _use_graph(self, bs: int) -> bool:
+        return bool((not self.enforce_eager) and self.noise != "explicit" and bs <= self.max_bs and self.graph_bs)
+
+    def _tail(self, bs: int, p: int, mask_id: int, threshold: float) -> torch.cuda.CUDAGraph:
+        """What follows the forward pass of a graph-launched decode step, as a graph of its own (captured on first
+        use: the mask id and the threshold are kernel arguments): the unmask rule on result set ``p``, the new
+        block ids handed on to the next step's input, the step counters advanced, the results copied to pinned
+        memory."""
+        key = (bs, p, int(mask_id), float(threshold))
+        graph = self._tails.get(key)
+        if graph is None:
+            (d_all, h_all, d_ids, d_counts, d_transfer, _, _, _, d_status, _) = self._result_views(bs, p)
+            m = bs * self.block_size
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                d_ids.copy_(self.dv["ids"][:bs], non_blocking=True)
+                ops.unmask_decide(d_ids, self.engine.x0[:m], self.engine.conf[:m], mask_id, threshold, 1,
+                                  transfer=d_transfer, counts=d_counts, status_out=d_status)
+                self.dv["ids"][:bs].copy_(d_ids, non_blocking=True)
+                self.dv["step"].add_(1)
+                h_all.copy_(d_all, non_blocking=True)
+            self._tails[key] = graph
+        return graph
+
     def _launch(self, seqs: list[Sequence], is_prefill: bool):
         """Everything of a step up to, not including, the wait for its results: forward pass, unmask rule, the
-        copy of the results to pinned memory.  Returns the (possibly extended) request list."""
+        copy of the results to pinned memory.  Returns the (possibly extended) request list and the record of
+        the launch (batch size, result set, event pair, whether it was a graph launch)."""
         bs, b = len(seqs), self.block_size
         self._pair = None
+        p = self._parity
+        self._parity ^= 1
         if is_prefill:
             hidden = self.run_model_prefill(seqs)
         else:
@@ -422,54 +462,85 @@ class ModelRunner:
                     bs = len(seqs)
             self.run_model_decode(seqs)
             hidden = self.engine.final[:bs * b]     # final-norm rows of the step (graph replays write here too)
+        sp = seqs[0].sampling_params
+        if sp.denoising_strategy != "low_confidence_dynamic":
+            raise NotImplementedError(f"Denoising strategy {sp.denoising_strategy} not implemented")
         with torch.inference_mode():
-            # sampler state: the host copy of each block is the source of truth, as in the reference
-            # (a decode step has just sent those ids down as its input)
-            (d_all, h_all, d_ids, d_counts, d_transfer, h_ids, h_counts, h_transfer, d_status,
-             h_status) = self._result_views(bs)
-            if is_prefill:
-                torch.stack([seq.current_denoising_block for seq in seqs], out=h_ids)
-                d_ids.copy_(h_ids, non_blocking=True)
-            else:
-                d_ids.copy_(self.dv["ids"][:bs], non_blocking=True)
-            sp = seqs[0].sampling_params
-            if sp.denoising_strategy != "low_confidence_dynamic":
-                raise NotImplementedError(f"Denoising strategy {sp.denoising_strategy} not implemented")
             quotas = self._step_quotas(seqs, is_prefill)
-            m = bs * b
-            ops.unmask_decide(d_ids, self.engine.x0[:m], self.engine.conf[:m], seqs[0].mask_token_id,
-                              sp.dynamic_threshold, 1, transfer=d_transfer, counts=d_counts, quotas=quotas,
-                              status_out=d_status)
-            if self._pair is not None and not is_prefill:
-                self._pair[1].record()
-            h_all.copy_(d_all, non_blocking=True)
-            if self.keep_last:
-                self.last = dict(x0=self.engine.x0[:m].clone(), conf=self.engine.conf[:m].clone(),
-                                 hidden=None if hidden is None else hidden.clone())
-        return seqs
+            graph_tail = (not is_prefill) and quotas is None and not self.keep_last and self._use_graph(bs)
+            if graph_tail:
+                self._tail(bs, p, seqs[0].mask_token_id, sp.dynamic_threshold).replay()
+                if self._pair is not None:
+                    self._pair[1].record()
+            else:
+                # sampler state: the host copy of each block is the source of truth, as in the reference
+                # (a decode step has just sent those ids down as its input)
+                (d_all, h_all, d_ids, d_counts, d_transfer, h_ids, h_counts, h_transfer, d_status,
+                 h_status) = self._result_views(bs, p)
+                if is_prefill:
+                    torch.stack([seq.current_denoising_block for seq in seqs], out=h_ids)
+                    d_ids.copy_(h_ids, non_blocking=True)
+                else:
+                    d_ids.copy_(self.dv["ids"][:bs], non_blocking=True)
+                m = bs * b
+                ops.unmask_decide(d_ids, self.engine.x0[:m], self.engine.conf[:m], seqs[0].mask_token_id,
+                                  sp.dynamic_threshold, 1, transfer=d_transfer, counts=d_counts, quotas=quotas,
+                                  status_out=d_status)
+                if self._pair is not None and not is_prefill:
+                    self._pair[1].record()
+                h_all.copy_(d_all, non_blocking=True)
+                if self.keep_last:
+                    self.last = dict(x0=self.engine.x0[:m].clone(), conf=self.engine.conf[:m].clone(),
+                                     hidden=None if hidden is None else hidden.clone())
+            self._done[p].record()
+        return seqs, dict(bs=bs, set=p, pair=self._pair, graph=graph_tail)
 
-    def _ahead_possible(self, seqs: list[Sequence], was_caching: bool) -> bool:
-        """May the step after this decode step be launched before the scheduler asks for it?  Only the plain case:
-        graph replay, the nano engine's unmask rule, one GPU, and no request that has just committed its block
-        (the scheduler gives those a new block or retires them, so the next step has other inputs)."""
-        if not self.launch_ahead or was_caching or self.keep_last or self.fuse_commit_pass or self.tp_pair is not None:
+    def _launch_ahead(self, seqs: list[Sequence], cur: dict) -> dict:
+        """The decode step after the graph-launched step ``cur`` of the same requests, put on the GPU before the
+        results of ``cur`` are known: its block ids are the ones the unmask rule of ``cur`` leaves on the device,
+        its step counters the incremented ones, everything else is unchanged in the pinned inputs."""
+        bs = cur["bs"]
+        p = self._parity
+        self._parity ^= 1
+        pair = self._next_event_pair()
+        sp = seqs[0].sampling_params
+        with torch.inference_mode():
+            if pair is not None:
+                pair[0].record()
+            gbs = next(x for x in self.graph_bs if x >= bs)
+            self.graphs[gbs][0].replay()
+            self._tail(bs, p, seqs[0].mask_token_id, sp.dynamic_threshold).replay()
+            if pair is not None:
+                pair[1].record()
+            self._done[p].record()
+        key = (tuple(map(len, seqs)), tuple(len(seq.block_table) for seq in seqs))
+        return dict(bs=bs, set=p, pair=pair, graph=True, seqs=list(seqs), key=key)
+
+    def _ahead_possible(self, seqs: list[Sequence]) -> bool:
+        """May the step after this decode step be launched before the scheduler asks for it, and before this
+        step's results are known?  Only the plain case: graph launches, the nano engine's unmask rule, one GPU,
+        and no request on its commit pass (the scheduler gives those a new block or retires them, so the next step
+        has other inputs).  Whatever this step unmasks, the next step of these requests has the same positions,
+        slots and pages: another denoising pass, or the commit pass of a block that has just lost its last mask."""
+        if not self.launch_ahead or self.keep_last or self.fuse_commit_pass or self.tp_pair is not None:
             return False
-        if self.enforce_eager or self.noise == "explicit" or not self.graph_bs or len(seqs) > self.max_bs:
+        if any(seq.is_caching for seq in seqs):
             return False
         return all(getattr(seq.sampling_params, "denoising_steps", None) is None for seq in seqs)
 
-    @staticmethod
-    def _ahead_matches(ahead, seqs: list[Sequence]) -> bool:
-        held, key, rows, _ = ahead
-        if len(seqs) != len(held) or not all(a is b for a, b in zip(seqs, held)):
+    def _ahead_matches(self, ahead: dict, seqs: list[Sequence]) -> bool:
+        held, rows = ahead["seqs"], self._last_rows
+        if len(seqs) != len(held) or rows is None or len(rows) != len(held):
             return False
-        if key != (tuple(map(len, seqs)), tuple(len(seq.block_table) for seq in seqs)):
+        if not all(a is b for a, b in zip(seqs, held)):
+            return False
+        if ahead["key"] != (tuple(map(len, seqs)), tuple(len(seq.block_table) for seq in seqs)):
             return False
         return all(seq.current_denoising_block is rows[i] for i, seq in enumerate(seqs))
 
-    def _wait_results(self, bs: int):
-        torch.cuda.current_stream().synchronize()
-        views = self._result_views(bs)
+    def _wait_results(self, rec: dict):
+        self._done[rec["set"]].synchronize()
+        views = self._result_views(rec["bs"], rec["set"])
         status = int(views[-1][0])
         if status:
             # a kernel of this step skipped an access or gave up a wait (bad slot / page / token id / position,
@@ -478,6 +549,14 @@ class ModelRunner:
                                "(1 bad slot, 2 bad page, 4 bad token id, 8 bad position, 16 wait timed out)")
         return views
 
+    def cancel_ahead(self) -> None:
+        """Waits for a step launched ahead, if one is in flight, and drops its results (the next ``run`` then
+        launches the step it is asked for from the host's state)."""
+        ahead, self._ahead = self._ahead, None
+        if ahead is not None:
+            self.ahead_misses += 1
+            self._wait_results(ahead)
+
     def run(self, seqs: list[Sequence], is_prefill: bool) -> int:
         if len(seqs) > self.max_bs:
             raise AssertionError("batch larger than max_num_seqs")
@@ -485,46 +564,35 @@ class ModelRunner:
         if ahead is not None and not is_prefill and self._ahead_matches(ahead, seqs):
             # the step asked for is the one already on the GPU
             self.ahead_hits += 1
-            self._pair = ahead[3]
+            cur = ahead
         else:
             if ahead is not None:
                 # another step was asked for: let the one in flight finish (its K/V rows are tentative ones of the
-                # same blocks, its noise step number is reused by the step that now runs) and drop its results
+                # same blocks; the step that now runs gets its block ids and step counters from the host again, so
+                # it also reuses the noise step number) and drop its results
                 self.ahead_misses += 1
-                self._wait_results(len(ahead[0]))
-            seqs = self._launch(seqs, is_prefill)
-        bs = len(seqs)
-        # requests on their commit pass get a new block (or retire) before the next step: nothing to launch ahead
-        was_caching = self.launch_ahead and not is_prefill and any(seq.is_caching for seq in seqs
-                                                                   if type(seq) is not _NextBlock)
-        (_, _, _, _, _, h_ids, h_counts, h_transfer, _, _) = self._wait_results(bs)
-        self.last_step_events = self._pair
+                self._wait_results(ahead)
+            seqs, cur = self._launch(seqs, is_prefill)
+        if cur["graph"] and self._ahead_possible(seqs):
+            self._ahead = self._launch_ahead(seqs, cur)
+        (_, _, _, _, _, h_ids, h_counts, h_transfer, _, _) = self._wait_results(cur)
+        self.last_step_events = cur["pair"]
         # one copy of the results for the whole batch; every request keeps a row of it
         blocks = h_ids.clone()
         rows = blocks.unbind(0)
         moved = h_transfer != 0
-        count = int(h_counts.sum())
-        for i, seq in enumerate(seqs):
-            if type(seq) is not _NextBlock:
-                seq.current_denoising_block = rows[i]
-        self._last_rows, self._last_blocks = rows, blocks.numpy()   # shares memory with the rows
-        self.step_index += 1
-        launched = not is_prefill and self._ahead_possible(seqs, was_caching)
-        if launched:
-            # the next step of these requests, on the blocks just handed out, goes to the GPU before the rest of
-            # this step's bookkeeping
-            self._launch(seqs, False)
-            key = (tuple(map(len, seqs)), tuple(len(seq.block_table) for seq in seqs))
-            self._ahead = (list(seqs), key, rows, self._pair)
         moved_any = moved.any(axis=1)
         for i, seq in enumerate(seqs):
             if type(seq) is _NextBlock:     # applied by Scheduler.postprocess once the block before it is appended
                 seq.seq.pending_first_step = (rows[i], moved[i].copy() if moved_any[i] else None)
                 continue
+            seq.current_denoising_block = rows[i]
             if moved_any[i]:
                 seq.current_step_map.numpy()[moved[i]] = seq.current_denoise_step
             seq.current_denoise_step += 1
-        return count
+        self._last_rows, self._last_blocks = rows, blocks.numpy()   # shares memory with the rows
+        self.step_index += 1
+        return int(h_counts.sum())
 
     def _step_quotas(self, seqs, is_prefill: bool):
         """Per-request quota of this pass, or None for the nano engine's rule (one token unless more pass the
@@ -581,8 +649,9 @@ class ModelRunner:
     @torch.inference_mode()
     def capture_cudagraph(self):
         """One graph per batch-size bucket covering the copy of the packed
-        step inputs from pinned memory, embedding gather, all layers, the LM
-        head and the sampler statistics.  Padded rows carry
+        step inputs (all but the block ids and the step counters) from pinned
+        memory, embedding gather, all layers, the LM head and the sampler
+        statistics.  Padded rows carry
         slot -1 and context length 0, which every kernel treats as a no-op."""
         if self.noise == "explicit":
             return
@@ -602,7 +671,10 @@ class ModelRunner:
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, pool):
-                self.inputs.dev.copy_(self.inputs.host, non_blocking=True)   # pinned buffer, read at replay time
+                # pinned buffer, read at replay time; block ids and step counters are not part of this copy: the
+                # launcher sends them, or the step before has left them on the device
+                o = self.inputs.o_pos
+                self.inputs.dev[o:].copy_(self.inputs.host[o:], non_blocking=True)
                 self._decode_body(bs, nsplit)
             if pool is None:
                 pool = graph.pool()

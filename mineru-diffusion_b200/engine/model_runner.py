@@ -422,10 +422,12 @@ class ModelRunner:
         return bool((not self.enforce_eager) and self.noise != "explicit" and bs <= self.max_bs and self.graph_bs)
 
     def _tail(self, bs: int, p: int, mask_id: int, threshold: float) -> torch.cuda.CUDAGraph:
-        """What follows the forward pass of a graph-launched decode step, as a graph of its own (captured on first
-        use: the mask id and the threshold are kernel arguments): the unmask rule on result set ``p``, the new
-        block ids handed on to the next step's input, the step counters advanced, the results copied to pinned
-        memory."""
+        """What follows the forward pass of a graph-launched decode step, as a graph of its own per batch-size
+        bucket ``bs`` (the mask id and the threshold are kernel arguments: the configuration's mask id with the
+        default threshold is captured with the forward graphs, anything else on first use): the unmask rule on
+        result set ``p``, the new block ids handed on to the next step's input, the step counters advanced, the
+        results copied to pinned memory.  Rows of the bucket beyond the step's requests carry whatever the padded
+        forward rows produced; nobody reads them."""
         key = (bs, p, int(mask_id), float(threshold))
         graph = self._tails.get(key)
         if graph is None:
@@ -468,8 +470,10 @@ class ModelRunner:
         with torch.inference_mode():
             quotas = self._step_quotas(seqs, is_prefill)
             graph_tail = (not is_prefill) and quotas is None and not self.keep_last and self._use_graph(bs)
+            vbs = bs          # rows of the result views
             if graph_tail:
-                self._tail(bs, p, seqs[0].mask_token_id, sp.dynamic_threshold).replay()
+                vbs = next(x for x in self.graph_bs if x >= bs)
+                self._tail(vbs, p, seqs[0].mask_token_id, sp.dynamic_threshold).replay()
                 if self._pair is not None:
                     self._pair[1].record()
             else:
@@ -493,7 +497,7 @@ class ModelRunner:
                     self.last = dict(x0=self.engine.x0[:m].clone(), conf=self.engine.conf[:m].clone(),
                                      hidden=None if hidden is None else hidden.clone())
             self._done[p].record()
-        return seqs, dict(bs=bs, set=p, pair=self._pair, graph=graph_tail)
+        return seqs, dict(bs=bs, vbs=vbs, set=p, pair=self._pair, graph=graph_tail)
 
     def _launch_ahead(self, seqs: list[Sequence], cur: dict) -> dict:
         """The decode step after the graph-launched step ``cur`` of the same requests, put on the GPU before the
@@ -507,14 +511,14 @@ class ModelRunner:
         with torch.inference_mode():
             if pair is not None:
                 pair[0].record()
-            gbs = next(x for x in self.graph_bs if x >= bs)
+            gbs = cur["vbs"]
             self.graphs[gbs][0].replay()
-            self._tail(bs, p, seqs[0].mask_token_id, sp.dynamic_threshold).replay()
+            self._tail(gbs, p, seqs[0].mask_token_id, sp.dynamic_threshold).replay()
             if pair is not None:
                 pair[1].record()
             self._done[p].record()
         key = (tuple(map(len, seqs)), tuple(len(seq.block_table) for seq in seqs))
-        return dict(bs=bs, set=p, pair=pair, graph=True, seqs=list(seqs), key=key)
+        return dict(bs=bs, vbs=cur["vbs"], set=p, pair=pair, graph=True, seqs=list(seqs), key=key)
 
     def _ahead_possible(self, seqs: list[Sequence]) -> bool:
         """May the step after this decode step be launched before the scheduler asks for it, and before this
@@ -540,7 +544,7 @@ class ModelRunner:
 
     def _wait_results(self, rec: dict):
         self._done[rec["set"]].synchronize()
-        views = self._result_views(rec["bs"], rec["set"])
+        views = self._result_views(rec["vbs"], rec["set"])
         status = int(views[-1][0])
         if status:
             # a kernel of this step skipped an access or gave up a wait (bad slot / page / token id / position,
@@ -577,10 +581,11 @@ class ModelRunner:
             self._ahead = self._launch_ahead(seqs, cur)
         (_, _, _, _, _, h_ids, h_counts, h_transfer, _, _) = self._wait_results(cur)
         self.last_step_events = cur["pair"]
+        bs = cur["bs"]            # the views may hold the rows of a whole batch-size bucket
         # one copy of the results for the whole batch; every request keeps a row of it
-        blocks = h_ids.clone()
+        blocks = h_ids[:bs].clone()
         rows = blocks.unbind(0)
-        moved = h_transfer != 0
+        moved = h_transfer[:bs] != 0
         moved_any = moved.any(axis=1)
         for i, seq in enumerate(seqs):
             if type(seq) is _NextBlock:     # applied by Scheduler.postprocess once the block before it is appended
@@ -592,7 +597,7 @@ class ModelRunner:
             seq.current_denoise_step += 1
         self._last_rows, self._last_blocks = rows, blocks.numpy()   # shares memory with the rows
         self.step_index += 1
-        return int(h_counts.sum())
+        return int(h_counts[:bs].sum())
 
     def _step_quotas(self, seqs, is_prefill: bool):
         """Per-request quota of this pass, or None for the nano engine's rule (one token unless more pass the
@@ -679,4 +684,7 @@ class ModelRunner:
             if pool is None:
                 pool = graph.pool()
             self.graphs[bs] = (graph, nsplit)
+        for bs in self.graph_bs:
+            for p in (0, 1):
+                self._tail(bs, p, self.config.mask_token_id, 0.9)     # SamplingParams' default threshold
         torch.cuda.synchronize()

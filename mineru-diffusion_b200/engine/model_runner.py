@@ -16,9 +16,6 @@ embeddings of the first prompt positions, which is what
 """
 from __future__ import annotations
 
-import os
-
-import numpy as np
 import torch
 
 from .. import ops

@@ -8,7 +8,7 @@ nano behaviour of a quota of one token per step.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 
 @dataclass

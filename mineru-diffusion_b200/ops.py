@@ -6,7 +6,6 @@ and none has a fallback.
 """
 from __future__ import annotations
 
-import math
 
 import torch
 

@@ -21,7 +21,7 @@ call site ``NV/layers/activation.py:15``).
 from __future__ import annotations
 
 import math
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 import torch
 

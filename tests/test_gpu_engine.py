@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import bf16_from_bits, load_golden, record_parity
+from conftest import load_golden, record_parity
 from oracle import nano_oracle as orc
 
 pytestmark = pytest.mark.gpu

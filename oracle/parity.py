@@ -74,7 +74,8 @@ def decode_parity(pkg, ocfg: "orc.DecoderConfig", weights: "orc.DecoderWeights",
       ``kv_exact_frac`` the share of identical bf16 values;
     * ``disagreements``: one record per differing decision with the oracle's noisy top-2 margin at that
       position and its confidence gap, next to the logits error of that pass (a tie within the error of the
-      path explains the difference).
+      path explains the difference); ``disagreements_unexplained`` counts those whose deciding margin is not
+      below twice that error over the temperature.
     """
     if native_linear:
         orc.use_native_linear(True)
@@ -224,4 +225,13 @@ def _decode_parity(pkg, ocfg, weights, context, passes, temperature, threshold, 
     out["decision_agreement"] = round(out["decisions_agree"] / max(out["decisions"], 1), 5)
     out["robust_agreement"] = round(out["robust_agree"] / max(out["robust_decisions"], 1), 5)
     out["floor_robust_agreement"] = round(out["floor_robust_agree"] / max(out["floor_robust_decisions"], 1), 5)
+    # a differing decision is explained when the margin that decided it (sampled token: the two best noisy logits;
+    # position: the two best confidences, in log) is below twice the logits error of that pass over T
+    unexplained = 0
+    for d in out["disagreements"]:
+        eps = 2 * max(d["pass_logits_err"], LOGIT_TOL) / temperature
+        gap = d["confidence_log_gap"] if d["confidence_log_gap"] is not None else float("inf")
+        if not (d["noisy_top2_margin"] <= eps or gap <= eps):
+            unexplained += 1
+    out["disagreements_unexplained"] = unexplained
     return out

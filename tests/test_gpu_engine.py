@@ -484,6 +484,7 @@ def test_full_size_decoder_teacher_forced(mdb, full_size, temperature):
         eps = 2 * max(d["pass_logits_err"], LOGIT_TOL) / temperature
         gap = d["confidence_log_gap"] if d["confidence_log_gap"] is not None else float("inf")
         assert d["noisy_top2_margin"] <= eps or gap <= eps, d
+    assert r["disagreements_unexplained"] == 0
     # sampled tokens over all rows (committed or not): at the low temperature the logits error is magnified
     # 200 times against the noise, so near-ties of the top two logits decide
     assert r["x0_agree"] / max(r["x0_total"], 1) >= (0.95 if temperature >= 0.5 else 0.8)

@@ -225,8 +225,10 @@ class ModelRunner:
         return getattr(self, method_name)(*args)
 
     def exit(self):
+        torch.cuda.synchronize(self.device)      # a step launched ahead may still be running
+        self._ahead = None
         self.graphs.clear()
-        torch.cuda.synchronize(self.device)
+        self._tails.clear()
         if self.tp_pair is not None:
             self.tp_pair.close()
             self.tp_pair = None

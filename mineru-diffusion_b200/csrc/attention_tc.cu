@@ -50,12 +50,16 @@ constexpr int kAtMaxRanked = 512;                     // batches above this are 
 // carries every row in two tensor-memory lanes, and the thread of lane r takes keys 0..63 of the tile while the
 // thread of lane r + 64 takes keys 64..127 of the same row.  The two exchange their row maximum through shared
 // memory, write their halves of the same P row, and add up their partial sums at the end of the unit.
-template <int ROWS, bool DUP = false>
+template <int ROWS, bool DUP = false, bool STAIR = false>
 struct AtPlan {
   static_assert(!DUP || ROWS == 64, "row duplication exists for the 64-row units");
   static constexpr int kQRows = DUP ? 128 : ROWS;     // rows of the Q operand tile
   static constexpr int kQBufs = (ROWS == 64 && !DUP) ? 2 : 1;
-  static constexpr int kKStages = 2;
+  // Staircase form: one P buffer is enough (the P V of a tile is long over when the next tile's softmax wants to
+  // write), which buys the K ring a third stage: 4 x 4096 tokens 407 -> 396 us, one sequence of 16384 tokens
+  // 1366 -> 1297 us.  (The paged form with 128-row units loses 3 % with the same trade and keeps two and two.)
+  static constexpr int kPBufs = STAIR ? 1 : 2;
+  static constexpr int kKStages = STAIR ? 3 : 2;
   static constexpr int kVStages = ROWS == 64 ? 3 : 2;
   static constexpr int kQBytes = 2 * kQRows * 128;    // two channel halves of [kQRows][128 B]
   static constexpr int kPBytes = 2 * ROWS * 128;      // two key halves of [ROWS][128 B]
@@ -65,7 +69,7 @@ struct AtPlan {
   static constexpr int kThreads = (kSoftmaxWarps + 2) * 32;
   static constexpr int kOffQ = 0;
   static constexpr int kOffP = kOffQ + kQBufs * kQBytes;
-  static constexpr int kOffK = kOffP + 2 * kPBytes;
+  static constexpr int kOffK = kOffP + kPBufs * kPBytes;
   static constexpr int kOffV = kOffK + kKStages * kAtTileBytes;
   static constexpr int kOffBars = kOffV + kVStages * kAtTileBytes;
   static constexpr int kMaxRanked = DUP ? 256 : kAtMaxRanked;          // batches above this are walked in request order
@@ -78,9 +82,9 @@ struct AtPlan {
 
 // barrier slots (8 bytes each) after the tiles
 enum {
-  kAtBarQFull = 0, kAtBarQEmpty = 2, kAtBarKFull = 4, kAtBarKEmpty = 6, kAtBarVFull = 8, kAtBarVEmpty = 11,
-  kAtBarSFull = 14, kAtBarSEmpty = 16, kAtBarPFull = 18, kAtBarPEmpty = 20, kAtBarOFull = 22, kAtBarOEmpty = 23,
-  kAtBarQReady = 24, kAtBarCount = 26
+  kAtBarQFull = 0, kAtBarQEmpty = 2, kAtBarKFull = 4, kAtBarKEmpty = 7, kAtBarVFull = 10, kAtBarVEmpty = 13,
+  kAtBarSFull = 16, kAtBarSEmpty = 18, kAtBarPFull = 20, kAtBarPEmpty = 22, kAtBarOFull = 24, kAtBarOEmpty = 25,
+  kAtBarQReady = 26, kAtBarCount = 28      // up to three K and three V stages
 };
 
 struct AtArgs {
@@ -258,10 +262,10 @@ __device__ __forceinline__ bool at_swap(volatile unsigned long long* xch, int la
 }
 
 template <int ROWS, bool STAIR, bool DUP = false>
-__global__ void __launch_bounds__(AtPlan<ROWS, DUP>::kThreads, 1)
+__global__ void __launch_bounds__(AtPlan<ROWS, DUP, STAIR>::kThreads, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const AtArgs a, const int units) {
-  using P = AtPlan<ROWS, DUP>;
+  using P = AtPlan<ROWS, DUP, STAIR>;
   static_assert(!(DUP && STAIR), "row duplication is a paged-form layout");
   extern __shared__ __align__(1024) unsigned char at_smem_raw[];
   const uint32_t raw = smem_u32(at_smem_raw);
@@ -455,7 +459,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
           umma_commit_w(bar(kAtBarPEmpty + pr.stage));
           if (j == w.ntiles - 1) umma_commit_w(bar(kAtBarOFull));
           vr.advance(P::kVStages);
-          pr.advance(2);
+          pr.advance(P::kPBufs);
         }
         qr.advance(P::kQBufs);
       }
@@ -650,7 +654,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         prev_p_stage = pr.stage;
         prev_p_phase = pr.phase;
         sr.advance(2);
-        pr.advance(2);
+        pr.advance(P::kPBufs);
         vr.advance(P::kVStages);
       }
       if (!ok) break;
@@ -773,7 +777,7 @@ static int at_sm_count() {
 template <int ROWS, bool STAIR, bool DUP = false>
 static int at_launch(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, const AtArgs& a,
                      int64_t units, cudaStream_t st) {
-  using P = AtPlan<ROWS, DUP>;
+  using P = AtPlan<ROWS, DUP, STAIR>;
   static PerDeviceOnce attr_once;
   const int dev = attr_once.slot();
   if (dev < 0) return MDB_ERR_CUDA;

@@ -141,14 +141,18 @@ int mdb_attn_staircase_varlen(const void* q, int64_t q_stride, const void* k, in
  * Activations, outputs and workspaces carry the usual stream order. */
 
 /* y[m,n] = x[m,k] * w[n,k]^T, bf16 in, fp32 accumulate, bf16 out: F.linear as
- * used by NV/layers/linear.py:72-73,153-154 and NV/layers/embed_head.py:67. */
+ * used by NV/layers/linear.py:72-73,153-154 and NV/layers/embed_head.py:67.
+ * m <= 64 with n % 128 == 0 streams the weight once; everything else runs the
+ * tcgen05 tile kernel (clusters of CTAs split k when the tiles are few, pairs
+ * of CTAs share a tile from 2048 rows on); k % 64 == 0 and n % 8 == 0. */
 int mdb_gemm_bf16(const void* x, int64_t ldx, const void* w, void* y, int64_t ldy, int m, int n, int k,
                   mdb_stream_t stream);
 
-/* Same product for m <= 64 as a weight-streaming kernel that cuts k into
+/* Same product for m <= 256 as a weight-streaming kernel that cuts k into
  * ksplit slices and writes fp32 partial sums partials[ksplit][m][n]; the
  * consumers below add the slices in index order, round to bf16 where F.linear
- * would, and apply the layer that follows. */
+ * would, and apply the layer that follows.  (n % 128 == 0, k % 64 == 0, no
+ * empty slice; the tensor-parallel form below takes m <= 64.) */
 int mdb_gemm_pick_ksplit(int m, int n, int k); /* a ksplit that suits the kernel these shapes will run on */
 int64_t mdb_gemm_splitk_workspace_bytes(int m, int n, int ksplit);
 int mdb_gemm_splitk_partials(const void* x, int64_t ldx, const void* w, float* partials, int m, int n, int k,

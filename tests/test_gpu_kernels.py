@@ -292,7 +292,8 @@ def test_gemm_gateup_swiglu_many_rows(mdb, m):
                                    (2048, 4096, 2048), (20, 136, 64),
                                    # few tiles: clusters of 8 / 4 / 2 CTAs split k and add their partial tiles
                                    (256, 2048, 2048), (512, 2048, 6144), (1024, 2048, 2048), (300, 520, 2048),
-                                   (70, 136, 1024)])
+                                   (70, 136, 1024), (129, 2048, 2048), (257, 2048, 6144), (1100, 2048, 2048),
+                                   (640, 4096, 1024)])
 def test_gemm_tile_kernel(mdb, m, n, k):
     gen = torch.Generator().manual_seed(m + n)
     x = torch.randn(m, k, generator=gen).to(BF)
